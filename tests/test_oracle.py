@@ -1,0 +1,150 @@
+"""Pins the CPU oracle: the reference's own known-answer tests (reference/tests/test_quant.py, restated as
+literal vectors) and golden vectors recorded from the reference's Python modules (tests/golden)."""
+
+import numpy as np
+import torch
+
+from oracle import nvfp4_oracle as O
+
+
+def bits(a):
+    return np.asarray(a, dtype=np.float32).view(np.uint32)
+
+
+# ---- reference/tests/test_quant.py, restated -----------------------------------------------------------------
+
+
+def test_unpack_low_nibble_first():
+    packed = np.array([[0x21, 0xF8]], dtype=np.uint8)  # codes 1, 2 | 8 (-0), 15 (-6)
+    out = O.unpack_e2m1(packed)
+    assert out.tolist() == [[0.5, 1.0, -0.0, -6.0]]
+    assert np.signbit(out[0, 2])
+
+
+def test_round_e2m1_grid_and_ties():
+    grid = O.E2M1_VALUES
+    assert np.array_equal(O.round_e2m1(grid), grid)
+    assert np.array_equal(O.round_e2m1(-grid), -grid)
+    ties = np.array([0.25, 0.75, 1.25, 1.75, 2.5, 3.5, 5.0], dtype=np.float32)
+    assert O.round_e2m1(ties).tolist() == [0.0, 1.0, 1.0, 2.0, 2.0, 4.0, 4.0]
+    assert O.round_e2m1(np.array([0.26, 2.51, 7.0, -100.0], np.float32)).tolist() == [0.5, 3.0, 6.0, -6.0]
+
+
+def test_quant_act_nvfp4_properties():
+    x = (np.random.RandomState(0).standard_normal((4, 256)) * 3).astype(np.float32)
+    q = O.quant_act_nvfp4(x, 0.01)
+    assert np.allclose(O.quant_act_nvfp4(q, 0.01), q)  # idempotent
+    blocks = np.abs(q.reshape(-1, 16))
+    assert max(len(np.unique(b)) for b in blocks) <= 8
+    rel = np.linalg.norm(x - q) / np.linalg.norm(x)
+    assert rel < 0.15, rel
+
+
+def test_e4m3_saturates():
+    assert O.to_e4m3(np.array([1000.0, -1000.0], np.float32)).tolist() == [448.0, -448.0]
+
+
+# ---- golden vectors recorded from the reference ---------------------------------------------------------------
+
+
+def test_golden_round_e2m1(golden):
+    assert np.array_equal(bits(O.round_e2m1(golden["e2m1_in"])), bits(golden["e2m1_out"]))
+
+
+def test_golden_e4m3(golden):
+    assert np.array_equal(bits(O.to_e4m3(golden["e4m3_in"])), bits(golden["e4m3_out"]))
+    assert np.array_equal(O.e4m3_encode(golden["e4m3_in"]), golden["e4m3_code"])
+
+
+def test_golden_unpack(golden):
+    assert np.array_equal(bits(O.unpack_e2m1(golden["unpack_in"])), bits(golden["unpack_out"]))
+
+
+def test_golden_quant_act(golden):
+    deq = O.quant_act_nvfp4(golden["act_x"], golden["act_scale"])
+    assert np.array_equal(bits(deq), bits(golden["act_deq"]))
+    xb = O.bf16_bits_to_f32(golden["act_x_bf16_bits"])
+    assert np.array_equal(bits(O.quant_act_nvfp4(xb, golden["act_scale"])), bits(golden["act_deq_bf16"]))
+
+
+def test_quant_act_codes_roundtrip(golden):
+    """Codes + scale bytes dequantise to the reference's fake-quantised values (its GPU test's protocol)."""
+    x, s = golden["act_x"], golden["act_scale"]
+    codes, sf = O.quant_act_codes(x, s)
+    gs = np.float32(1.0) / np.float32(s)
+    deq = (O.unpack_e2m1(codes) * np.repeat(O.e4m3_decode(sf), 16, -1)).astype(np.float32) / gs
+    assert np.array_equal(deq, golden["act_deq"])  # (-0 == +0 here, as in the reference's comparison)
+    assert (sf[3, 0] == 0) and not codes[3, :8].any()  # the all-zero block
+    assert sf[5, 1] == 0x7E  # saturated block scale (448)
+
+
+def test_golden_weight_quant(golden):
+    codes, sf, g = O.quant_weight_rtn(golden["w"])
+    assert g == golden["w_gscale"]
+    assert np.array_equal(sf, golden["w_sf"])
+    assert np.array_equal(codes, golden["w_codes"])
+    assert np.array_equal(bits(O.dequant_nvfp4(codes, sf, g)), bits(golden["w_deq"]))
+
+
+def test_golden_qlinear(golden):
+    y = O.qlinear(golden["lin_x"], golden["w_codes"], golden["w_sf"], golden["w_gscale"], golden["lin_in_scale"])
+    assert np.allclose(y, golden["lin_y_f64"], rtol=1e-12, atol=1e-14)
+    # the reference's own fp32 evaluation agrees with the fp64 one far inside the acceptance tolerance
+    assert O.within_tolerance(golden["lin_y_f32"], y, rel=1e-3, abs_=1e-5).all()
+
+
+def test_golden_silu(golden):
+    ref = golden["silu_out"]
+    out = O.silu_mul(golden["silu_g"], golden["silu_u"])
+    assert np.allclose(out, ref, rtol=2e-6, atol=1e-7)
+
+
+# ---- the E4M3 cast the reference relies on (torch's), exhaustively --------------------------------------------
+
+
+def test_e4m3_all_codes_roundtrip():
+    codes = np.arange(256, dtype=np.uint8)
+    vals = torch.from_numpy(codes).view(torch.float8_e4m3fn).float().numpy()
+    mine = O.e4m3_decode(codes)
+    finite = np.isfinite(vals)
+    assert np.array_equal(np.isnan(mine), np.isnan(vals))
+    assert np.array_equal(bits(mine[finite]), bits(vals[finite]))
+    assert np.array_equal(O.e4m3_encode(vals[finite]), codes[finite])
+
+
+def test_e4m3_encode_random_vs_torch():
+    rng = np.random.RandomState(1)
+    x = np.concatenate([rng.standard_normal(200000) * 100, rng.standard_normal(200000) * 0.01,
+                        rng.uniform(-2.0**-5, 2.0**-5, 100000)]).astype(np.float32)
+    t = torch.from_numpy(x).clamp(-448, 448).to(torch.float8_e4m3fn).view(torch.uint8).numpy()
+    assert np.array_equal(O.e4m3_encode(x), t)
+
+
+# ---- layouts -----------------------------------------------------------------------------------------------------
+
+
+def test_sf_layout_roundtrip_and_atoms():
+    rows, kb = 300, 1088
+    src = np.random.RandomState(2).randint(0, 255, size=(rows, kb)).astype(np.uint8)
+    buf = O.swizzle_sf(src)
+    assert buf.size == O.sf_bytes(rows, kb) == 3 * 128 * 1088
+    assert np.array_equal(O.unswizzle_sf(buf, rows, kb), src)
+    # one 512-byte atom = 128 rows x 4 k-blocks: row r at line r % 32 (16 B), word r / 32, byte = k-block
+    assert O.sf_offset(0, 0, kb) == 0 and O.sf_offset(33, 2, kb) == 1 * 16 + 1 * 4 + 2
+    assert O.sf_offset(0, 4, kb) == 512 and O.sf_offset(128, 0, kb) == (kb // 4) * 512
+
+
+def test_glu_interleave():
+    inter = 192
+    rows = O.glu_rows(inter)
+    assert sorted(rows.tolist()) == list(range(2 * inter))
+    assert rows[0] == 0 and rows[63] == 63 and rows[64] == 128 and rows[inter] == 64 and rows[inter + 64] == 192
+    m = np.arange(2 * inter)[:, None] * np.ones((1, 3), dtype=np.int64)
+    il = O.interleave_glu(m)
+    assert il[64, 0] == inter and il[128, 0] == 64  # up row 0 sits after the first 64 gate rows
+
+
+def test_bf16_round():
+    x = np.random.RandomState(3).standard_normal(100000).astype(np.float32) * 37
+    ref = torch.from_numpy(x).to(torch.bfloat16).float().numpy()
+    assert np.array_equal(O.bf16_round(x), ref)

@@ -1,0 +1,225 @@
+// C-ABI glue: the thread-local error message, and the synchronous one-kernel wrappers q27t_* that the tests and
+// the benchmark call with raw device pointers (the protocol of the reference's test layer,
+// engine/src/capi.cc:46-95,498-636: synchronise the device, launch on a private non-blocking stream, synchronise,
+// return 0 / -1 with a message; Q27T_REPEAT=n additionally times n launches replayed from a CUDA graph).
+#include <cstdlib>
+#include <cstring>
+
+#include "../../include/q27b200/capi.h"
+#include "common.cuh"
+#include "layout.h"
+
+namespace q27b {
+
+std::string& last_error() {
+  thread_local std::string e;
+  return e;
+}
+
+int fail(const char* fmt, ...) {
+  char buf[512];
+  va_list ap;
+  va_start(ap, fmt);
+  vsnprintf(buf, sizeof buf, fmt, ap);
+  va_end(ap);
+  last_error() = buf;
+  return -1;
+}
+
+namespace {
+
+float g_last_us = 0.f;
+
+cudaStream_t test_stream() {
+  static cudaStream_t s = [] {
+    cudaStream_t x = nullptr;
+    cudaStreamCreateWithFlags(&x, cudaStreamNonBlocking);
+    return x;
+  }();
+  return s;
+}
+
+// Runs f (which launches on test_stream()) the way the reference's test wrappers do, then checks that no bounded
+// wait inside a kernel ran out.
+template <class F>
+int kernel(F&& f) {
+  Q27B_CUDA(cudaDeviceSynchronize());
+  if (int rc = f()) return rc;
+  Q27B_CUDA(cudaStreamSynchronize(test_stream()));
+  const char* e = getenv("Q27T_REPEAT");
+  const int rep = e ? atoi(e) : 0;
+  if (rep > 0) {
+    cudaGraph_t g;
+    cudaGraphExec_t ge;
+    Q27B_CUDA(cudaStreamBeginCapture(test_stream(), cudaStreamCaptureModeThreadLocal));
+    int rc = 0;
+    for (int i = 0; i < rep && !rc; i++) rc = f();
+    Q27B_CUDA(cudaStreamEndCapture(test_stream(), &g));
+    if (rc) return rc;
+    Q27B_CUDA(cudaGraphInstantiate(&ge, g, 0));
+    cudaEvent_t e0, e1;
+    Q27B_CUDA(cudaEventCreate(&e0));
+    Q27B_CUDA(cudaEventCreate(&e1));
+    Q27B_CUDA(cudaGraphLaunch(ge, test_stream()));  // warm-up
+    Q27B_CUDA(cudaEventRecord(e0, test_stream()));
+    Q27B_CUDA(cudaGraphLaunch(ge, test_stream()));
+    Q27B_CUDA(cudaEventRecord(e1, test_stream()));
+    Q27B_CUDA(cudaEventSynchronize(e1));
+    float ms = 0.f;
+    Q27B_CUDA(cudaEventElapsedTime(&ms, e0, e1));
+    g_last_us = 1000.f * ms / rep;
+    cudaEventDestroy(e0);
+    cudaEventDestroy(e1);
+    cudaGraphExecDestroy(ge);
+    cudaGraphDestroy(g);
+  }
+  uint32_t status = 0;
+  if (int rc = q27b_device_status(&status)) return rc;
+  Q27B_REQUIRE(status == 0, "a bounded wait inside a kernel ran out (device status %u)", status);
+  return 0;
+}
+
+}  // namespace
+}  // namespace q27b
+
+using namespace q27b;
+
+extern "C" {
+
+const char* q27_last_error(void) { return last_error().c_str(); }
+float q27t_last_us(void) { return g_last_us; }
+int64_t q27t_sf_bytes(int64_t rows, int64_t kblocks) { return sf_bytes(rows, kblocks); }
+
+int q27t_quant_fp4(const float* x, int M, int K, float input_scale, uint8_t* q, uint8_t* sf) {
+  return kernel([&] { return q27b_quant_fp4(x, M, K, input_scale, q, sf, test_stream()); });
+}
+int q27t_quant_fp4_bf16(const void* x, int M, int K, float input_scale, uint8_t* q, uint8_t* sf) {
+  return kernel([&] { return q27b_quant_fp4_bf16(x, M, K, input_scale, q, sf, test_stream()); });
+}
+int q27t_silu_mul_quant_fp4(const float* g, const float* u, int64_t ld, int T, int I, float in_scale, uint8_t* q,
+                            uint8_t* sf) {
+  return kernel([&] { return q27b_silu_mul_quant_fp4(g, u, ld, T, I, in_scale, q, sf, test_stream()); });
+}
+int q27t_silu_mul_quant_fp4_bf16(const void* g, const void* u, int64_t ld, int T, int I, float in_scale, uint8_t* q,
+                                 uint8_t* sf) {
+  return kernel([&] { return q27b_silu_mul_quant_fp4_bf16(g, u, ld, T, I, in_scale, q, sf, test_stream()); });
+}
+int q27t_silu_mul_quant_fp4_glu(const float* gu, int T, int I, float ag, float au, float in_scale, uint8_t* q,
+                                uint8_t* sf) {
+  return kernel([&] { return q27b_silu_mul_quant_fp4_glu(gu, T, I, ag, au, in_scale, q, sf, test_stream()); });
+}
+int q27t_silu_mul_quant_fp4_glu_bf16(const void* gu, int T, int I, float ag, float au, float in_scale, uint8_t* q,
+                                     uint8_t* sf) {
+  return kernel([&] { return q27b_silu_mul_quant_fp4_glu_bf16(gu, T, I, ag, au, in_scale, q, sf, test_stream()); });
+}
+int q27t_swizzle_sf(const uint8_t* src, int rows, int kblocks, uint8_t* dst) {
+  return kernel([&] { return q27b_swizzle_sf(src, rows, kblocks, dst, -1, test_stream()); });
+}
+int q27t_swizzle_sf_glu(const uint8_t* src, int rows, int kblocks, uint8_t* dst, int half) {
+  return kernel([&] { return q27b_swizzle_sf(src, rows, kblocks, dst, half, test_stream()); });
+}
+int q27t_gemm_fp4(int M, int N, int K, const uint8_t* a, const uint8_t* a_sf, const uint8_t* b, const uint8_t* b_sf,
+                  float alpha, const float* c, float beta, float* d) {
+  return kernel([&] { return q27b_gemm_fp4(M, N, K, a, a_sf, b, b_sf, alpha, c, beta, d, test_stream()); });
+}
+int q27t_gemm_fp4_bf16(int M, int N, int K, const uint8_t* a, const uint8_t* a_sf, const uint8_t* b,
+                       const uint8_t* b_sf, float alpha, void* d) {
+  return kernel([&] { return q27b_gemm_fp4_bf16(M, N, K, a, a_sf, b, b_sf, alpha, d, test_stream()); });
+}
+int q27t_gemm_fp4_glu_bf16(int M, int I, int K, const uint8_t* a, const uint8_t* a_sf, const uint8_t* gate_up,
+                           const uint8_t* gate_up_sf, float alpha_gate, float alpha_up, void* d) {
+  return kernel([&] {
+    return q27b_gemm_fp4_glu_bf16(M, I, K, a, a_sf, gate_up, gate_up_sf, alpha_gate, alpha_up, d, test_stream());
+  });
+}
+int q27t_skinny_fp4(int M, int N, int K, const uint8_t* a, const uint8_t* a_sf, const uint8_t* w, const uint8_t* w_sf,
+                    float alpha, const float* c, float beta, float* d, void* ws, size_t ws_bytes) {
+  const int zero = 0;
+  return kernel([&] {
+    return q27b_skinny_fp4(M, N, K, a, a_sf, w, w_sf, 1, &zero, &alpha, c, beta, d, ws, ws_bytes, test_stream());
+  });
+}
+int q27t_skinny_fp4_segments(int M, int N, int K, const uint8_t* a, const uint8_t* a_sf, const uint8_t* w,
+                             const uint8_t* w_sf, int count, const int* begin, const float* alpha, const float* c,
+                             float beta, float* d, void* ws, size_t ws_bytes) {
+  return kernel([&] {
+    return q27b_skinny_fp4(M, N, K, a, a_sf, w, w_sf, count, begin, alpha, c, beta, d, ws, ws_bytes, test_stream());
+  });
+}
+int q27t_skinny_fp4_bf16(int M, int N, int K, const uint8_t* a, const uint8_t* a_sf, const uint8_t* w,
+                         const uint8_t* w_sf, float alpha, void* d, void* ws, size_t ws_bytes) {
+  const int zero = 0;
+  return kernel([&] {
+    return q27b_skinny_fp4_bf16(M, N, K, a, a_sf, w, w_sf, 1, &zero, &alpha, d, ws, ws_bytes, test_stream());
+  });
+}
+int q27t_skinny_fp4_glu_bf16(int M, int I, int K, const uint8_t* a, const uint8_t* a_sf, const uint8_t* gate_up,
+                             const uint8_t* gate_up_sf, float alpha_gate, float alpha_up, void* d, void* ws,
+                             size_t ws_bytes) {
+  return kernel([&] {
+    return q27b_skinny_fp4_glu_bf16(M, I, K, a, a_sf, gate_up, gate_up_sf, alpha_gate, alpha_up, d, ws, ws_bytes,
+                                    test_stream());
+  });
+}
+int q27t_ref_gemm_fp4(int M, int N, int K, const uint8_t* a, const uint8_t* a_sf, const uint8_t* b, const uint8_t* b_sf,
+                      float alpha, float* d) {
+  return kernel([&] { return q27b_ref_gemm_fp4(M, N, K, a, a_sf, b, b_sf, alpha, d, test_stream()); });
+}
+
+// Average time (us) of `iters` calls cycling through `nbuf` weight copies w_stride / sf_stride bytes apart (so
+// that the weights never come from L2). many != 0: the many-row GEMM; else the weight-streaming one.
+int q27t_bench_gemm(int many, int M, int N, int K, const uint8_t* a, const uint8_t* a_sf, const uint8_t* w,
+                    const uint8_t* w_sf, int64_t w_stride, int64_t sf_stride, int nbuf, int iters, float* d, void* ws,
+                    size_t ws_bytes, float* us) {
+  Q27B_REQUIRE(nbuf >= 1 && iters >= 1 && us, "bench_gemm: bad arguments");
+  return kernel([&]() -> int {
+    const int zero = 0;
+    const float one = 1.f;
+    auto run = [&](int i) -> int {
+      const uint8_t* wi = w + int64_t(i % nbuf) * w_stride;
+      const uint8_t* si = w_sf + int64_t(i % nbuf) * sf_stride;
+      if (many) return q27b_gemm_fp4(M, N, K, a, a_sf, wi, si, 1.f, nullptr, 0.f, d, test_stream());
+      return q27b_skinny_fp4(M, N, K, a, a_sf, wi, si, 1, &zero, &one, nullptr, 0.f, d, ws, ws_bytes, test_stream());
+    };
+    for (int i = 0; i < (nbuf > iters ? nbuf : iters); i++)
+      if (int rc = run(i)) return rc;
+    cudaEvent_t e0, e1;
+    Q27B_CUDA(cudaEventCreate(&e0));
+    Q27B_CUDA(cudaEventCreate(&e1));
+    Q27B_CUDA(cudaEventRecord(e0, test_stream()));
+    for (int i = 0; i < iters; i++)
+      if (int rc = run(i)) return rc;
+    Q27B_CUDA(cudaEventRecord(e1, test_stream()));
+    Q27B_CUDA(cudaEventSynchronize(e1));
+    float ms = 0.f;
+    Q27B_CUDA(cudaEventElapsedTime(&ms, e0, e1));
+    *us = 1000.f * ms / iters;
+    cudaEventDestroy(e0);
+    cudaEventDestroy(e1);
+    return 0;
+  });
+}
+
+// CPU-testable view of the weight-streaming work split: fills seg[4 * i .. 4 * i + 3] = {tile, c0, c1, slot} for the
+// pieces of CTA `cta` (at most `cap`), returns their count; grid_out / units_out describe the plan.
+int q27b_skinny_plan(int N, int K, int sms, int cta, int* seg, int cap, int* grid_out, int64_t* units_out) {
+  if (N <= 0 || N % 128 || K <= 0 || K % 64 || sms <= 0) return fail("skinny_plan: bad shape");
+  const SkinnyPlan p = make_skinny_plan(N, K, sms);
+  if (grid_out) *grid_out = p.grid;
+  if (units_out) *units_out = p.units;
+  if (cta < 0 || cta >= p.grid) return 0;
+  int64_t u = unit_begin(p, cta);
+  Segment s;
+  int n = 0;
+  while (next_segment(p, cta, u, s)) {
+    if (seg && n < cap) seg[4 * n] = s.tile, seg[4 * n + 1] = s.c0, seg[4 * n + 2] = s.c1, seg[4 * n + 3] = s.slot;
+    n++;
+  }
+  return n;
+}
+int q27b_skinny_unit_owner(int N, int K, int sms, int64_t unit) {
+  const SkinnyPlan p = make_skinny_plan(N, K, sms);
+  return unit_owner(p, unit);
+}
+
+}  // extern "C"

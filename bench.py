@@ -1,0 +1,313 @@
+"""Benchmark of the NVFP4 weight-GEMM path.
+
+One "step" is one pass of the hot path over one batch: quantise the bf16 activation to NVFP4, then the
+weight-streaming GEMM with its fused epilogue. At one GPU the workload is the speculative-verify gate | up
+projection (x bf16 [16, 5120], W NVFP4 [34816, 5120], SiLU*mul -> bf16 [16, 17408]); with N > 1 GPUs the weight
+rows are sharded N ways (every rank computes its block of output columns, no reduction) and one NCCL all-gather
+of the bf16 output is timed separately.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--config 0|1|2|4]
+
+Prints one JSON line (rank 0). `value` = algorithmic bytes of the step / device time with everything resident in
+HBM and the weights rotating through more than L2-size of distinct copies; `e2e` = the same step through the host
+API with the activation coming from pinned host memory and the result copied back, copies inside the timed
+region. `--impl reference` times the CPU restatement of the reference's own path (fake-quantise, fp32 matmul
+against the dequantised weight, SiLU*mul) on the host cores instead.
+"""
+
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path[:0] = [ROOT, os.path.join(ROOT, "qwen3-27b-5090_b200")]
+
+import numpy as np  # noqa: E402
+import torch  # noqa: E402
+
+L2_BYTES = 126 * 1024 * 1024
+FALLBACK_HBM_GBS = 6650.0
+# dram__bytes_read.sum + dram__bytes_write.sum of one launch of the GEMM kernel on the benchmark workload, from the
+# ncu capture summarised in profiles/ (None until a capture has been taken for the current kernel).
+NCU_TRAFFIC_BYTES = {1: None}
+
+
+def peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        p = json.load(open(path))
+        return float(p["hbm_gbs"]), "measured (MEASURED_PEAKS.json: copy bandwidth)"
+    return FALLBACK_HBM_GBS, "fallback (6.65 TB/s, earlier measurement on this pool)"
+
+
+class ClockSampler:
+    """Samples SM clock and throttle reasons of one GPU with nvidia-smi while a timed region runs."""
+
+    Q = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+         "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index: int):
+        self.index, self.proc, self.lines = index, None, []
+
+    def __enter__(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits", "-lms", "50",
+                                          "-i", str(self.index)], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.thread = threading.Thread(target=lambda: self.lines.extend(self.proc.stdout), daemon=True)
+            self.thread.start()
+            time.sleep(0.3)
+        except OSError:
+            self.proc = None
+        return self
+
+    def __exit__(self, *a):
+        if self.proc:
+            time.sleep(0.1)
+            self.proc.terminate()
+            self.thread.join(timeout=2)
+
+    def summary(self):
+        sm, mx, reasons = [], 0.0, set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for ln in self.lines:
+            f = [x.strip() for x in ln.split(",")]
+            if len(f) < 7:
+                continue
+            try:
+                sm.append(float(f[0])), (mx := max(mx, float(f[1])))
+            except ValueError:
+                continue
+            for n, v in zip(names, f[3:7]):
+                if v.lower().startswith("active"):
+                    reasons.add(n)
+        return {"sm_mhz": float(np.median(sm)) if sm else None, "sm_max_mhz": mx or None, "reasons": sorted(reasons),
+                "samples": len(sm)}
+
+
+def build_layers(cfg, rank, world, nbuf_min_bytes):
+    """The rank's shard of the configuration's weight, quantised on the GPU, in `nbuf` distinct device copies
+    (identical contents; distinct memory so that no step finds its weights in L2)."""
+    from q27b200 import configs, shard, weights
+    from q27b200.linear import Fp4Linear
+
+    x = configs.make_x(cfg)
+    in_scale = configs.input_scale_of(x)
+    w = configs.make_w(cfg.N, cfg.K, 1000 + cfg.index, cfg.w_std).cuda()
+    codes, sfb, g = weights.quantize_weight_rtn(w)
+    del w
+    if cfg.glu:
+        codes, sfb = weights.interleave_gate_up(codes), weights.interleave_gate_up(sfb)
+    b, e = shard.shard_rows(cfg.N, world, rank, cfg.glu)
+    codes, sfs = codes[b:e].contiguous(), weights.swizzle_scales(sfb[b:e])
+    n_out = (e - b) // 2 if cfg.glu else e - b
+    per = codes.numel() + sfs.numel()
+    nbuf = max(2, -(-nbuf_min_bytes // per))
+    ws = torch.empty(32 << 20, dtype=torch.uint8, device="cuda")
+    layers = [Fp4Linear(codes if i == 0 else codes.clone(), sfs if i == 0 else sfs.clone(), g, in_scale, n_out, cfg.K,
+                        cfg.glu, ws) for i in range(nbuf)]
+    return x, in_scale, layers, n_out
+
+
+def sync_all(world):
+    if world > 1:
+        torch.distributed.barrier()
+    torch.cuda.synchronize()
+
+
+def max_over_ranks(ms, world):
+    if world == 1:
+        return ms
+    t = torch.tensor([ms], dtype=torch.float64, device="cuda")
+    torch.distributed.all_reduce(t, op=torch.distributed.ReduceOp.MAX)
+    return float(t.item())
+
+
+def timed(fn, steps, warmup, world):
+    """`steps` calls of fn(i) bracketed by a barrier + synchronize, timed with CUDA events on the current stream
+    (the stream every launch of the library goes to); max over ranks, in ms."""
+    for i in range(warmup):
+        fn(i)
+    sync_all(world)
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for i in range(steps):
+        fn(warmup + i)
+    e1.record()
+    sync_all(world)
+    return max_over_ranks(e0.elapsed_time(e1), world)
+
+
+def cpu_reference(cfg, steps, warmup, frac_rows=4):
+    """The reference's CPU path (fake-quantise the activation, fp32 matmul against the once-dequantised weight,
+    SiLU*mul) restated by the oracle, on a bounded sample: the first 1/frac_rows of the output channels. Returns
+    (GB/s of algorithmic bytes, seconds per step, cores, description)."""
+    from oracle import nvfp4_oracle as O
+    from q27b200 import configs
+
+    cores = os.cpu_count() or 1
+    torch.set_num_threads(cores)
+    x = configs.make_x(cfg).float().numpy()
+    s = configs.input_scale_of(configs.make_x(cfg))
+    n_out = cfg.n_out // frac_rows // 64 * 64
+    w_full = configs.make_w(cfg.N, cfg.K, 1000 + cfg.index, cfg.w_std)
+    rows = np.concatenate([np.arange(n_out), cfg.N // 2 + np.arange(n_out)]) if cfg.glu else np.arange(n_out)
+    g = O.weight_global_scale(w_full.numpy())
+    codes, sfb, _ = O.quant_weight_rtn(w_full.numpy()[rows], g)
+    del w_full
+    wdq = torch.from_numpy(O.dequant_nvfp4(codes, sfb, g))  # dequantised once, outside the timed loop
+
+    def step():
+        xq = torch.from_numpy(O.quant_act_nvfp4(x, s))
+        y = xq @ wdq.T  # fp32, all host threads
+        if cfg.glu:
+            y = torch.nn.functional.silu(y[:, :n_out]) * y[:, n_out:]
+        return y.to(torch.bfloat16)
+
+    for _ in range(warmup):
+        step()
+    t0 = time.perf_counter()
+    for _ in range(steps):
+        step()
+    dt = (time.perf_counter() - t0) / steps
+    n_rows = len(rows)
+    sample_bytes = n_rows * cfg.K // 2 + n_rows * cfg.K // 16 + 2 * cfg.M * cfg.K + 2 * cfg.M * n_out
+    desc = (f"{cfg.name}: output channels 0..{n_out - 1} of {cfg.n_out} ({n_rows} of {cfg.N} weight rows), "
+            f"{steps} steps; weight dequantised once outside the timed loop")
+    return sample_bytes / dt / 1e9, dt, cores, desc
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=200)
+    ap.add_argument("--warmup", type=int, default=20)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--config", type=int, default=1, choices=[0, 1, 2, 4])
+    ap.add_argument("--cpu-steps", type=int, default=20)
+    args = ap.parse_args()
+    args.warmup = max(args.warmup, 3)
+
+    from q27b200 import configs
+
+    cfg = configs.CONFIGS[args.config]
+    rank, world = int(os.environ.get("RANK", 0)), int(os.environ.get("WORLD_SIZE", 1))
+    local_rank = int(os.environ.get("LOCAL_RANK", 0))
+    metric = "nvfp4_gemm_tflops" if cfg.M > 128 else "nvfp4_gemm_hbm_gbs"
+    unit = "TFLOP/s" if cfg.M > 128 else "GB/s"
+
+    if args.impl == "reference":
+        if rank != 0:
+            return
+        gbs, dt, cores, desc = cpu_reference(cfg, max(1, min(args.steps, 50)), min(args.warmup, 3))
+        val = gbs if unit == "GB/s" else cfg.flops() / cfg.algorithmic_bytes() * gbs / 1e3
+        print(json.dumps({
+            "impl": "reference", "metric": metric, "value": val, "unit": unit, "n_gpus": args.gpus,
+            "steps": max(1, min(args.steps, 50)), "warmup": min(args.warmup, 3), "ms_per_step": dt * 1e3,
+            "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "f32 (host matmul of fake-quantised operands)",
+            "data": "synthetic", "config": {"workload": cfg.name, "sample": desc},
+            "cpu_baseline": {"value": val, "unit": unit, "cores": cores, "kind": "port", "sample": desc},
+            "e2e": {"value": val, "unit": unit, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}))
+        return
+
+    assert torch.cuda.is_available(), "bench.py needs a GPU (there is no CPU fallback)"
+    torch.cuda.set_device(local_rank)
+    if world > 1:
+        torch.distributed.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+    from q27b200 import shard
+    from q27b200.linear import ActQuant
+    from q27b200.q27lib import device_status
+
+    x, in_scale, layers, n_local = build_layers(cfg, rank, world, 4 * L2_BYTES // 1 if world == 1 else 3 * L2_BYTES)
+    nbuf, M = len(layers), cfg.M
+    xd = x.cuda()
+    outs = [torch.empty(M, n_local, dtype=torch.bfloat16, device="cuda") for _ in range(2)]
+    act = ActQuant(max(M, 128), cfg.K)
+    for l in layers:
+        l._act = act  # one activation scratch for every copy, as one engine would have
+
+    def step(i):  # device-resident step: quantise + GEMM (+ fix-up)
+        layers[i % nbuf](xd, out=outs[i & 1])
+
+    q, sf = act.quantize(xd, in_scale)
+
+    def gemm_only(i):
+        layers[i % nbuf].gemm(M, q, sf, outs[i & 1])
+
+    # host-facing step: pinned host activation in, result back to pinned host memory
+    xh = x.pin_memory()
+    yh = torch.empty(M, n_local, dtype=torch.bfloat16).pin_memory()
+    xdev = torch.empty_like(xd)
+
+    def step_e2e(i):
+        xdev.copy_(xh, non_blocking=True)
+        layers[i % nbuf](xdev, out=outs[i & 1])
+        yh.copy_(outs[i & 1], non_blocking=True)
+        torch.cuda.current_stream().synchronize()  # the caller reads the result
+
+    gathered = torch.empty(world, M, n_local, dtype=torch.bfloat16, device="cuda") if world > 1 else None
+
+    def step_gather(i):
+        step(i)
+        torch.distributed.all_gather_into_tensor(gathered, outs[i & 1])
+
+    with ClockSampler(local_rank) as clk:
+        ms = timed(step, args.steps, args.warmup, world)
+    ms_gemm = timed(gemm_only, args.steps, args.warmup, world)
+    ms_e2e = timed(step_e2e, args.steps, args.warmup, world)
+    ms_gather = timed(step_gather, args.steps, args.warmup, world) if world > 1 else None
+    assert device_status() == 0, "a bounded wait inside a kernel ran out"
+    clocks = clk.summary()
+
+    if rank != 0:
+        torch.distributed.destroy_process_group()
+        return
+
+    total_bytes = cfg.algorithmic_bytes()  # whole job: all ranks' weight shards + activation in + output
+    flops = cfg.flops()
+    per_step_s, gemm_s, e2e_s = ms / args.steps / 1e3, ms_gemm / args.steps / 1e3, ms_e2e / args.steps / 1e3
+
+    def val(seconds):
+        return total_bytes / seconds / 1e9 if unit == "GB/s" else flops / seconds / 1e12
+
+    peak, peak_src = peaks()
+    # per-GPU roofline of the dominant kernel: the rank's share of the weight bytes + the whole activation + its
+    # output block, over the average duration of one GEMM launch (fix-up launch and launch gap included)
+    n_rows_local = layers[0].rows()
+    launch_bytes = n_rows_local * cfg.K // 2 + n_rows_local * cfg.K // 16 + 2 * M * cfg.K + 2 * M * n_local
+    achieved = launch_bytes / gemm_s / 1e9
+    fixup = 1  # the fix-up kernel runs whenever a tile is cut, which is the case for every benchmark shape
+    line = {
+        "metric": metric, "value": val(per_step_s), "unit": unit, "n_gpus": world, "steps": args.steps,
+        "warmup": args.warmup, "ms_per_step": ms / args.steps, "higher_is_better": True, "scaling": "strong",
+        "vs_baseline": None, "dtype": "nvfp4 (e2m1 x e2m1, ue4m3 scale per 16, fp32 accumulate)", "data": "synthetic",
+        "config": {"workload": cfg.name, "M": M, "N": cfg.N, "K": cfg.K, "epilogue": "silu*mul->bf16" if cfg.glu else "bf16",
+                   "sharding": f"N-sharded {world} way(s), no reduction", "l2": f"weights rotate through {nbuf} distinct copies "
+                   f"({nbuf * layers[0].weight_bytes() / 2**20:.0f} MiB per GPU > 126 MiB L2)",
+                   "step": "quant_fp4_bf16 + skinny_fp4_glu_bf16 (+ fix-up)"},
+        "e2e": {"value": val(e2e_s), "unit": unit, "h2d_bytes_per_step": x.numel() * 2, "d2h_bytes_per_step": M * n_local * 2,
+                "ms_per_step": ms_e2e / args.steps},
+        "gpu_launches": args.steps * (2 + fixup),
+        "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
+                     "traffic": NCU_TRAFFIC_BYTES.get(cfg.index) if world == 1 else None, "algorithmic_bytes": launch_bytes,
+                     "kernel": "umma_gemm_kernel (+ skinny_fixup_kernel)", "us_per_launch": gemm_s * 1e6, "peak_source": peak_src},
+        "clocks": clocks,
+    }
+    if ms_gather is not None:
+        line["with_allgather"] = {"value": val(ms_gather / args.steps / 1e3), "unit": unit, "ms_per_step": ms_gather / args.steps}
+    if world == 1:
+        gbs, dt, cores, desc = cpu_reference(cfg, args.cpu_steps, 2)
+        line["cpu_baseline"] = {"value": gbs if unit == "GB/s" else flops / total_bytes * gbs / 1e3, "unit": unit, "cores": cores,
+                                "kind": "port", "sample": desc, "ms_per_step_sample": dt * 1e3}
+    print(json.dumps(line))
+    if world > 1:
+        torch.distributed.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

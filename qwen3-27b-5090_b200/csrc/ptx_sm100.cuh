@@ -60,16 +60,23 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
   return ok != 0;
 }
 
-// Upper bound on try_wait polls (each poll may itself block for a hardware-defined slice of time).
-constexpr uint32_t kMaxPolls = 1u << 22;
+// Budget of a bounded wait in SM clock cycles (about two seconds at 2 GHz) and in polls (each poll may itself
+// block for a hardware-defined slice of time; the cycle budget is what normally ends a wait that cannot succeed).
+constexpr long long kMaxWaitCycles = 4000000000ll;
+constexpr uint32_t kMaxPolls = 1u << 28;
 
 // Waits for the phase with the given parity; gives up when `abort_flag` (shared memory) is raised by another
-// role or after kMaxPolls polls, in which case it raises the flag itself and records `code`.
+// role or when the budget is spent, in which case it raises the flag itself and records `code`.
 __device__ __forceinline__ bool mbar_wait_bounded(uint32_t bar, uint32_t parity, volatile uint32_t* abort_flag,
                                                   uint32_t* status, uint32_t code) {
-  for (uint32_t i = 0; i < kMaxPolls; i++) {
+  if (mbar_try_wait(bar, parity)) return true;
+  const long long t0 = clock64();
+  for (uint32_t i = 1; i < kMaxPolls; i++) {
     if (mbar_try_wait(bar, parity)) return true;
-    if ((i & 63u) == 63u && *abort_flag) return false;
+    if ((i & 63u) == 0u) {
+      if (*abort_flag) return false;
+      if (clock64() - t0 > kMaxWaitCycles) break;
+    }
   }
   *abort_flag = 1u;
   if (status) atomicCAS(status, 0u, code);

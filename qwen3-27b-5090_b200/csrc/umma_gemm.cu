@@ -180,7 +180,11 @@ __global__ void __launch_bounds__(192, 1) umma_gemm_kernel(const __grid_constant
         for (int s = 0; s < STAGES; s++)
           if (armed >> s & 1) {
             bool landed = false;
-            for (uint32_t i = 0; i < kMaxPolls && !landed; i++) landed = mbar_try_wait(full0 + 8 * s, last_parity >> s & 1);
+            const long long t0 = clock64();
+            for (uint32_t i = 0; i < kMaxPolls && !landed; i++) {
+              landed = mbar_try_wait(full0 + 8 * s, last_parity >> s & 1);
+              if ((i & 63u) == 63u && clock64() - t0 > kMaxWaitCycles) break;
+            }
             if (!landed) atomicCAS(&g_status, 0u, uint32_t(kStatusDrainTimeout));
           }
       }
@@ -442,13 +446,14 @@ int launch_gemm(Kern kernel, int grid, int smem, cudaStream_t s, const CUtensorM
 }
 
 // One-time opt-in to large dynamic shared memory, per kernel instantiation and per device.
-template <typename Kern>
-int ensure_smem(Kern kernel, int smem) {
-  static bool done[64] = {};
+template <int NB, int STAGES, bool kSwap, int kEpi>
+int ensure_smem() {
+  static bool done[64] = {};  // one array per instantiation
   int dev = 0;
   Q27B_CUDA(cudaGetDevice(&dev));
   if (dev < 64 && done[dev]) return 0;
-  Q27B_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
+  Q27B_CUDA(cudaFuncSetAttribute(umma_gemm_kernel<NB, STAGES, kSwap, kEpi>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                 Cfg<NB, STAGES>::kSmemBytes));
   if (dev < 64) done[dev] = true;
   return 0;
 }
@@ -457,7 +462,7 @@ template <int NB, int STAGES, int kEpi>
 int run_skinny(const uint8_t* a, const uint8_t* w, GemmParams& p, cudaStream_t s) {
   using C = Cfg<NB, STAGES>;
   auto kernel = umma_gemm_kernel<NB, STAGES, true, kEpi>;
-  if (int rc = ensure_smem(kernel, C::kSmemBytes)) return rc;
+  if (int rc = ensure_smem<NB, STAGES, true, kEpi>()) return rc;
   CUtensorMap mp, mq;
   if (int rc = make_operand_map(&mp, w, p.N, p.K, 128)) return rc;
   if (int rc = make_operand_map(&mq, a, p.M, p.K, NB)) return rc;
@@ -524,7 +529,7 @@ int run_many(const uint8_t* a, const uint8_t* w, GemmParams& p, cudaStream_t s) 
   constexpr int NB = 128, STAGES = 6;
   using C = Cfg<NB, STAGES>;
   auto kernel = umma_gemm_kernel<NB, STAGES, false, kEpi>;
-  if (int rc = ensure_smem(kernel, C::kSmemBytes)) return rc;
+  if (int rc = ensure_smem<NB, STAGES, false, kEpi>()) return rc;
   CUtensorMap mp, mq;
   if (int rc = make_operand_map(&mp, a, p.M, p.K, 128)) return rc;
   if (int rc = make_operand_map(&mq, w, p.N, p.K, NB)) return rc;

@@ -1,0 +1,116 @@
+"""Host-side mirror of the engine's NVFP4 linear layer for this path: the weight record the reference keeps per
+projection (LinearFp4 {w, sf, w_scale2, in_scale, out, in, alpha}, engine/src/weights.h:25-31) and the dispatch
+of Model::gemm_q / Model::mlp (engine/src/model.cc:869-888,1054-1096): quantise the activation, then the
+weight-streaming GEMM for few rows and the many-row GEMM otherwise. Every launch goes through the C ABI on
+torch's current stream; torch only owns the device memory.
+"""
+
+from __future__ import annotations
+
+import ctypes
+
+import torch
+
+from . import layouts, weights
+from .q27lib import call, lib
+
+SKINNY_MAX_M = 128  # rows up to which the weight-streaming kernel is used (the reference: 64)
+WORKSPACE_BYTES = 32 << 20  # as the reference's shared skinny workspace (engine/src/model.h:462)
+
+
+def _stream() -> int:
+    return torch.cuda.current_stream().cuda_stream
+
+
+class ActQuant:
+    """Device scratch for one quantised activation [max_rows][K] (codes + swizzled scales), reused across calls."""
+
+    def __init__(self, max_rows: int, K: int, device="cuda"):
+        self.K = K
+        self.q = torch.empty(max_rows, K // 2, dtype=torch.uint8, device=device)
+        # zero once: rows past M inside the last 128-row atom are never valid but are copied along
+        self.sf = torch.zeros(layouts.sf_bytes(max_rows, K // 16), dtype=torch.uint8, device=device)
+
+    def quantize(self, x: torch.Tensor, input_scale: float):
+        M, K = x.shape
+        assert K == self.K and x.is_contiguous() and M <= self.q.shape[0]
+        name = {torch.bfloat16: "q27b_quant_fp4_bf16", torch.float32: "q27b_quant_fp4"}[x.dtype]
+        call(name, x, M, K, float(input_scale), self.q, self.sf, _stream())
+        return self.q, self.sf
+
+
+class Fp4Linear:
+    """y = alpha * quant(x) . W^T for one NVFP4 projection; `glu=True` holds gate | up interleaved and produces
+    silu(gate) * up. Weights live on the device; nothing is allocated per call when `out` is passed."""
+
+    def __init__(self, codes, sf_swizzled, w_scale2: float, in_scale: float, out_features: int, in_features: int,
+                 glu: bool = False, workspace: torch.Tensor | None = None):
+        self.w, self.sf = codes, sf_swizzled
+        self.w_scale2, self.in_scale = float(w_scale2), float(in_scale)
+        self.out, self.inp, self.glu = out_features, in_features, glu
+        self.alpha = self.in_scale * self.w_scale2  # engine/src/weights.cc:286
+        dev = codes.device
+        self.ws = workspace if workspace is not None else torch.empty(WORKSPACE_BYTES, dtype=torch.uint8, device=dev)
+        self._act: ActQuant | None = None
+        self._zero = (ctypes.c_int * 1)(0)
+        self._alpha = (ctypes.c_float * 1)(self.alpha)
+
+    @classmethod
+    def from_float(cls, w: torch.Tensor, in_scale: float, glu: bool = False, device="cuda", workspace=None):
+        """Quantises an fp32 [N][K] weight (for glu: gate rows then up rows, one tensor scale over both) on
+        `device` and lays it out for the kernels."""
+        w = w.to(device=device, dtype=torch.float32)
+        codes, sfb, g = weights.quantize_weight_rtn(w)
+        if glu:
+            codes, sfb = weights.interleave_gate_up(codes), weights.interleave_gate_up(sfb)
+        n, k = w.shape
+        return cls(codes.contiguous(), weights.swizzle_scales(sfb), g, in_scale, n // 2 if glu else n, k, glu, workspace)
+
+    def rows(self) -> int:
+        return self.w.shape[0]
+
+    def weight_bytes(self) -> int:
+        return self.w.numel() + self.sf.numel()
+
+    def _scratch(self, M: int) -> ActQuant:
+        if self._act is None or self._act.q.shape[0] < M:
+            self._act = ActQuant(max(M, 128), self.inp, self.w.device)
+        return self._act
+
+    def __call__(self, x: torch.Tensor, out: torch.Tensor | None = None, out_dtype=torch.bfloat16,
+                 residual: torch.Tensor | None = None) -> torch.Tensor:
+        """x: bf16 or fp32 [M][K] on the device. Returns [M][out] (bf16 by default; fp32 allows a residual:
+        out = alpha * x . W^T + residual, which may be `out` itself)."""
+        M = x.shape[0]
+        if out is None:
+            out = torch.empty(M, self.out, dtype=out_dtype, device=x.device)
+        if M == 0:
+            return out
+        q, sf = self._scratch(M).quantize(x, self.in_scale)
+        self.gemm(M, q, sf, out, residual)
+        return out
+
+    def gemm(self, M, q, sf, out, residual=None):
+        N, K, s = self.rows(), self.inp, _stream()
+        skinny = M <= SKINNY_MAX_M
+        if self.glu:
+            assert out.dtype == torch.bfloat16 and residual is None
+            if skinny:
+                call("q27b_skinny_fp4_glu_bf16", M, self.out, K, q, sf, self.w, self.sf, self.alpha, self.alpha, out,
+                     self.ws, self.ws.numel(), s)
+            else:
+                call("q27b_gemm_fp4_glu_bf16", M, self.out, K, q, sf, self.w, self.sf, self.alpha, self.alpha, out, s)
+        elif out.dtype == torch.bfloat16:
+            assert residual is None
+            if skinny:
+                call("q27b_skinny_fp4_bf16", M, N, K, q, sf, self.w, self.sf, 1, self._zero, self._alpha, out, self.ws,
+                     self.ws.numel(), s)
+            else:
+                call("q27b_gemm_fp4_bf16", M, N, K, q, sf, self.w, self.sf, self.alpha, out, s)
+        else:
+            beta = 1.0 if residual is not None else 0.0
+            if skinny:
+                call("q27b_skinny_fp4", M, N, K, q, sf, self.w, self.sf, 1, self._zero, self._alpha, residual, beta, out,
+                     self.ws, self.ws.numel(), s)
+            else:
+                call("q27b_gemm_fp4", M, N, K, q, sf, self.w, self.sf, self.alpha, residual, beta, out, s)

@@ -1,0 +1,182 @@
+"""CPU-only checks of the host side: the C-ABI library loads and exports every declared symbol, the work split of
+the weight-streaming GEMM covers every unit exactly once, the layout helpers and the load-time quantiser agree
+with the oracle, and precondition failures come back as error codes with a message (no GPU needed)."""
+
+import ctypes
+import os
+import re
+
+import numpy as np
+import pytest
+import torch
+
+from oracle import nvfp4_oracle as O
+from q27b200 import configs, layouts, shard, weights
+from q27b200.q27lib import SIGNATURES, call, last_error, lib
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def declared_functions():
+    text = open(os.path.join(ROOT, "include", "q27b200", "capi.h")).read()
+    text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
+    return sorted(set(re.findall(r"\b(q27[bt]?_[a-z0-9_]+)\s*\(", text)))
+
+
+def test_library_exports_every_declared_symbol():
+    names = declared_functions()
+    assert len(names) >= 35
+    l = lib()
+    for n in names:
+        assert hasattr(l, n), f"{n} is declared in capi.h but not exported"
+        assert n in SIGNATURES, f"{n} has no ctypes signature"
+    assert sorted(SIGNATURES) == names  # and nothing is bound that the header does not declare
+
+
+def test_sf_layout_matches_oracle():
+    l = lib()
+    for rows, kb in [(1, 320), (37, 320), (128, 4), (300, 1088), (5120, 1088)]:
+        assert l.q27b_sf_bytes(rows, kb) == O.sf_bytes(rows, kb) == layouts.sf_bytes(rows, kb)
+    rng = np.random.RandomState(0)
+    for _ in range(200):
+        kb = int(rng.randint(1, 2000))
+        r, k = int(rng.randint(0, 40000)), int(rng.randint(0, kb))
+        assert l.q27b_sf_offset(r, k, kb) == int(O.sf_offset(r, k, kb))
+    assert np.array_equal(layouts.sf_index(300, 1088), O.sf_offset(np.arange(300)[:, None], np.arange(1088)[None, :], 1088))
+    for r in (0, 63, 64, 100, 17407):
+        for h in (0, 1):
+            assert l.q27b_glu_row(r, h) == int(O.glu_row(r, h))
+    assert np.array_equal(layouts.glu_rows(384), O.glu_rows(384))
+
+
+def plan(N, K, sms):
+    l = lib()
+    grid, units = ctypes.c_int(), ctypes.c_int64()
+    seg = (ctypes.c_int * (4 * 2048))()
+    l.q27b_skinny_plan(N, K, sms, -1, None, 0, ctypes.byref(grid), ctypes.byref(units))
+    pieces = []
+    for g in range(grid.value):
+        n = l.q27b_skinny_plan(N, K, sms, g, seg, 2048, None, None)
+        assert 1 <= n <= 2048
+        pieces.append([tuple(seg[4 * i:4 * i + 4]) for i in range(n)])
+    return grid.value, units.value, pieces
+
+
+@pytest.mark.parametrize("N,K", [(5120, 5120), (1024, 5120), (34816, 5120), (5120, 17408), (128, 5120), (128, 64),
+                                 (384, 512), (248320, 5120), (640, 5120), (4352, 5120)])
+@pytest.mark.parametrize("sms", [148, 132, 7])
+def test_skinny_plan_covers_every_unit_once(N, K, sms):
+    grid, units, pieces = plan(N, K, sms)
+    tiles, chunks = N // 128, (K + 255) // 256
+    assert units == tiles * chunks and grid == min(sms, units)
+    cover = np.zeros((tiles, chunks), dtype=np.int32)
+    slots = set()
+    sizes = []
+    for g, segs in enumerate(pieces):
+        sizes.append(sum(c1 - c0 for _, c0, c1, _ in segs))
+        for i, (t, c0, c1, slot) in enumerate(segs):
+            assert 0 <= c0 < c1 <= chunks
+            cover[t, c0:c1] += 1
+            whole = c0 == 0 and c1 == chunks
+            assert (slot == -1) == whole
+            if not whole:
+                assert slot in (2 * g, 2 * g + 1) and slot not in slots  # at most two partial tiles per CTA
+                assert (slot == 2 * g) == (i == 0)
+                slots.add(slot)
+            # the owner lookup used by the fix-up kernel agrees with the split
+            assert lib().q27b_skinny_unit_owner(N, K, sms, t * chunks + c0) == g
+            assert lib().q27b_skinny_unit_owner(N, K, sms, t * chunks + c1 - 1) == g
+    assert (cover == 1).all()
+    assert max(sizes) - min(sizes) <= 1  # every SM streams the same number of bytes (+- one unit)
+
+
+def test_plan_is_independent_of_m():
+    # the split takes no M argument at all: rows cannot depend on the number of tokens
+    import inspect
+    assert "M" not in [a for a in inspect.signature(plan).parameters]
+
+
+def test_weight_quantiser_matches_oracle(golden):
+    w = torch.from_numpy(golden["w"])
+    codes, sf, g = weights.quantize_weight_rtn(w)
+    assert np.array_equal(codes.numpy(), golden["w_codes"]) and np.array_equal(sf.numpy(), golden["w_sf"])
+    assert np.float32(g) == golden["w_gscale"]
+    w2 = configs.make_w(384, 1024, 5)
+    w2[7, 32:48] = 0
+    c2, s2, g2 = weights.quantize_weight_rtn(w2, rows_per_step=100)
+    co, so, go = O.quant_weight_rtn(w2.numpy())
+    assert np.array_equal(c2.numpy(), co) and np.array_equal(s2.numpy(), so) and np.float32(g2) == go
+    assert np.array_equal(weights.swizzle_scales(s2).numpy(), O.swizzle_sf(so))
+    assert np.array_equal(weights.interleave_gate_up(c2).numpy(), O.interleave_glu(co))
+
+
+def test_config_byte_counts():
+    c = configs.CONFIGS
+    assert c[0].algorithmic_bytes() == 14_766_080 and c[1].algorithmic_bytes() == 100_990_976
+    assert c[2].algorithmic_bytes() == 55_902_208 and c[4].algorithmic_bytes() == 284_819_456
+    assert c[4].flops() == 1_460_288_880_640
+    assert configs.layer_weight_bytes() * 64 == 11_890_851_840
+    assert configs.sweep_algorithmic_bytes(1) == 11_900_813_312 and configs.sweep_algorithmic_bytes(128) == 13_165_920_256
+
+
+def test_configs_are_seeded():
+    a, b = configs.make_x(configs.CONFIGS[1]), configs.make_x(configs.CONFIGS[1])
+    assert torch.equal(a, b) and a.dtype == torch.bfloat16 and tuple(a.shape) == (16, 5120)
+    w = configs.make_w(256, 512, 1001)
+    assert torch.equal(w[128:], configs.make_w(256, 512, 1001, rows=slice(128, 256)))
+    assert abs(float(w.std()) - 0.02) < 1e-3
+
+
+# ---- precondition failures come back as -1 + message before any CUDA work ------------------------------------
+
+
+def expect_error(fragment, name, *args):
+    with pytest.raises(RuntimeError) as e:
+        call(name, *args)
+    assert fragment in str(e.value), str(e.value)
+    assert fragment in last_error()
+
+
+def test_argument_errors_without_a_gpu():
+    expect_error("multiple of 64", "q27b_quant_fp4", 16, 1, 100, 1.0, 16, 16, None)
+    expect_error("null pointer", "q27b_quant_fp4", None, 1, 128, 1.0, 16, 16, None)
+    expect_error("aligned", "q27b_quant_fp4", 4, 1, 128, 1.0, 16, 16, None)
+    expect_error("positive", "q27b_quant_fp4", 16, 1, 128, 0.0, 16, 16, None)
+    zero, one = (ctypes.c_int * 1)(0), (ctypes.c_float * 1)(1.0)
+    expect_error("M must be 1..128", "q27b_skinny_fp4", 129, 128, 256, 16, 16, 16, 16, 1, zero, one, None, 0.0, 16, 16, 1 << 20, None)
+    expect_error("multiple of 128", "q27b_skinny_fp4", 1, 100, 256, 16, 16, 16, 16, 1, zero, one, None, 0.0, 16, 16, 1 << 20, None)
+    expect_error("multiple of 64", "q27b_skinny_fp4", 1, 128, 100, 16, 16, 16, 16, 1, zero, one, None, 0.0, 16, 16, 1 << 20, None)
+    expect_error("null pointer", "q27b_skinny_fp4", 1, 128, 256, None, 16, 16, 16, 1, zero, one, None, 0.0, 16, 16, 1 << 20, None)
+    expect_error("16-byte aligned", "q27b_skinny_fp4", 1, 128, 256, 8, 16, 16, 16, 1, zero, one, None, 0.0, 16, 16, 1 << 20, None)
+    expect_error("alpha segments", "q27b_skinny_fp4", 1, 128, 256, 16, 16, 16, 16, 5, zero, one, None, 0.0, 16, 16, 1 << 20, None)
+    expect_error("multiple of 128", "q27b_gemm_fp4", 5, 128, 192, 16, 16, 16, 16, 1.0, None, 0.0, 16, None)
+    expect_error("multiple of 64", "q27b_gemm_fp4_glu_bf16", 5, 100, 256, 16, 16, 16, 16, 1.0, 1.0, 16, None)
+    # M == 0 is a no-op for the many-row GEMM and the quantisers, as in the reference
+    call("q27b_gemm_fp4", 0, 128, 256, None, None, None, None, 1.0, None, 0.0, None, None)
+    call("q27b_quant_fp4", None, 0, 128, 1.0, None, None, None)
+
+
+# ---- N-sharding across ranks ---------------------------------------------------------------------------------
+
+
+@pytest.mark.parametrize("world", [1, 2, 4, 8])
+def test_shard_rows(world):
+    for n_rows, glu in [(5120, False), (1024, False), (34816, True)]:
+        spans = [shard.shard_rows(n_rows, world, r, glu) for r in range(world)]
+        assert spans[0][0] == 0 and spans[-1][1] == n_rows
+        for (a0, a1), (b0, b1) in zip(spans, spans[1:]):
+            assert a1 == b0
+        for a0, a1 in spans:
+            assert a0 % 128 == 0 and (a1 - a0) % 128 == 0 and a1 > a0
+    assert shard.shard_rows(34816, 8, 3, True) == (3 * 4352, 4 * 4352)
+    # output columns owned by a rank: for gate | up every 128 interleaved rows give 64 outputs
+    assert shard.output_columns(34816, 8, 3, True) == (3 * 2176, 4 * 2176)
+    assert shard.output_columns(5120, 8, 7, False) == (7 * 640, 8 * 640)
+
+
+def test_gathered_layout_to_row_major():
+    world, M, n_out = 4, 3, 8
+    full = np.arange(M * n_out).reshape(M, n_out)
+    per = n_out // world
+    gathered = np.stack([full[:, r * per:(r + 1) * per] for r in range(world)])  # what all_gather yields
+    assert np.array_equal(shard.gathered_to_row_major(torch.from_numpy(gathered)).numpy(), full)

@@ -190,6 +190,7 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--config", type=int, default=1, choices=[0, 1, 2, 4])
     ap.add_argument("--cpu-steps", type=int, default=20)
+    ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg (profiling runs)")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)
 
@@ -300,7 +301,7 @@ def main():
     }
     if ms_gather is not None:
         line["with_allgather"] = {"value": val(ms_gather / args.steps / 1e3), "unit": unit, "ms_per_step": ms_gather / args.steps}
-    if world == 1:
+    if world == 1 and not args.no_cpu:
         gbs, dt, cores, desc = cpu_reference(cfg, args.cpu_steps, 2)
         line["cpu_baseline"] = {"value": gbs if unit == "GB/s" else flops / total_bytes * gbs / 1e3, "unit": unit, "cores": cores,
                                 "kind": "port", "sample": desc, "ms_per_step_sample": dt * 1e3}

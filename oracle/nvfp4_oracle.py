@@ -276,6 +276,22 @@ def bf16_bits_to_f32(bits: np.ndarray) -> np.ndarray:
 
 
 def within_tolerance(out, ref, rel=2e-3, abs_=1e-3):
-    """|out - ref| <= rel * |ref| + abs_ elementwise (the benchmark's acceptance rule)."""
+    """|out - ref| <= rel * |ref| + abs_ elementwise (the benchmark's acceptance rule for the fp32-accumulated
+    result)."""
     out, ref = np.asarray(out, dtype=np.float64), np.asarray(ref, dtype=np.float64)
     return np.abs(out - ref) <= rel * np.abs(ref) + abs_
+
+
+def bf16_half_ulp(x):
+    """Half the spacing of bf16 (8 significant bits) at |x|: the most a round-to-nearest store can move a value."""
+    a = np.maximum(np.abs(np.asarray(x, dtype=np.float64)), 2.0**-126)
+    return np.exp2(np.floor(np.log2(a)) - 8)
+
+
+def within_tolerance_bf16(out, ref, rel=2e-3, abs_=1e-3):
+    """The acceptance rule for a result that was stored as bf16: the fp32-accumulated value may be off by
+    rel * |ref| + abs_, and rounding it to bf16 (unit roundoff 2^-8, more than rel) moves it by at most half a
+    bf16 ulp of a value that large."""
+    out, ref = np.asarray(out, dtype=np.float64), np.asarray(ref, dtype=np.float64)
+    slack = rel * np.abs(ref) + abs_
+    return np.abs(out - ref) <= slack + bf16_half_ulp(np.abs(ref) + slack)

@@ -75,4 +75,4 @@ def make_w(N: int, K: int, seed: int, std: float = 0.02, rows: slice | None = No
 
 
 def input_scale_of(x: torch.Tensor) -> float:
-    return float(x.float().abs().amax() / (6.0 * 448.0))
+    return float(torch.div(x.float().abs().amax(), torch.tensor(6.0 * 448.0, device=x.device)))

@@ -31,14 +31,18 @@ def quantize_weight_rtn(w: torch.Tensor, scale_2: float | None = None, rows_per_
     """fp32 [N][K] -> (codes uint8 [N][K/2], scale bytes uint8 [N][K/16] row-major, scale_2 float)."""
     assert w.dtype == torch.float32 and w.dim() == 2 and w.shape[1] % 16 == 0
     n, k = w.shape
-    g = torch.tensor(scale_2, dtype=torch.float32, device=w.device) if scale_2 is not None else w.abs().amax() / (6.0 * 448.0)
-    codes = torch.empty(n, k // 2, dtype=torch.uint8, device=w.device)
-    sfb = torch.empty(n, k // 16, dtype=torch.uint8, device=w.device)
+    dev = w.device
+    # Divisors are tensors on purpose: torch turns a division by a Python scalar into a multiplication by its
+    # reciprocal on CUDA, which is not the IEEE quotient the recipe (and its CPU evaluation) means.
+    six, full_range, one = (torch.tensor(v, dtype=torch.float32, device=dev) for v in (6.0, 6.0 * 448.0, 1.0))
+    g = torch.tensor(scale_2, dtype=torch.float32, device=dev) if scale_2 is not None else torch.div(w.abs().amax(), full_range)
+    codes = torch.empty(n, k // 2, dtype=torch.uint8, device=dev)
+    sfb = torch.empty(n, k // 16, dtype=torch.uint8, device=dev)
     for r in range(0, n, rows_per_step):
         wb = w[r:r + rows_per_step].reshape(-1, k // 16, 16)
-        sf8 = (wb.abs().amax(-1) / 6.0 / g).clamp(-448.0, 448.0).to(torch.float8_e4m3fn)
+        sf8 = torch.div(torch.div(wb.abs().amax(-1), six), g).clamp(-448.0, 448.0).to(torch.float8_e4m3fn)
         s = (sf8.float() * g).unsqueeze(-1)
-        v = wb / torch.where(s > 0, s, torch.ones_like(s))
+        v = torch.div(wb, torch.where(s > 0, s, one.expand_as(s)))
         idx = round_e2m1_index(v)
         # the sign bit is set only for non-zero results (a zero is stored as code 0 whatever its sign)
         c = (idx | (((v < 0) & (idx > 0)).to(torch.int64) << 3)).to(torch.uint8).reshape(-1, k)

@@ -108,7 +108,7 @@ def build_layers(cfg, rank, world, nbuf_min_bytes):
     n_out = (e - b) // 2 if cfg.glu else e - b
     per = codes.numel() + sfs.numel()
     nbuf = max(2, -(-nbuf_min_bytes // per))
-    ws = torch.empty(32 << 20, dtype=torch.uint8, device="cuda")
+    ws = torch.zeros(48 << 20, dtype=torch.uint8, device="cuda")  # zeroed once, as the contract asks
     layers = [Fp4Linear(codes if i == 0 else codes.clone(), sfs if i == 0 else sfs.clone(), g, in_scale, n_out, cfg.K,
                         cfg.glu, ws) for i in range(nbuf)]
     return x, in_scale, layers, n_out
@@ -128,16 +128,35 @@ def max_over_ranks(ms, world):
     return float(t.item())
 
 
-def timed(fn, steps, warmup, world):
+def timed(fn, steps, warmup, world, graph=False):
     """`steps` calls of fn(i) bracketed by a barrier + synchronize, timed with CUDA events on the current stream
-    (the stream every launch of the library goes to); max over ranks, in ms."""
+    (the stream every launch of the library goes to); max over ranks, in ms. graph=True: the steps are captured
+    once into a CUDA graph and the timed region is its replay, so that the host's launch cost (two ctypes calls
+    and two tensor-map encodings per step from Python) does not sit between the kernels - the way the reference
+    engine runs its decode step (engine/src/model.cc:1388-1461) and times its GEMMs (engine/src/capi.cc:57-92)."""
     for i in range(warmup):
         fn(i)
     sync_all(world)
+    run = None
+    if graph:
+        g = torch.cuda.CUDAGraph()
+        side = torch.cuda.Stream()
+        side.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(side):
+            with torch.cuda.graph(g, stream=side):
+                for i in range(steps):
+                    fn(warmup + i)
+        torch.cuda.current_stream().wait_stream(side)
+        g.replay()  # once untimed
+        sync_all(world)
+        run = g.replay
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     e0.record()
-    for i in range(steps):
-        fn(warmup + i)
+    if run:
+        run()
+    else:
+        for i in range(steps):
+            fn(warmup + i)
     e1.record()
     sync_all(world)
     return max_over_ranks(e0.elapsed_time(e1), world)
@@ -191,6 +210,7 @@ def main():
     ap.add_argument("--config", type=int, default=1, choices=[0, 1, 2, 4])
     ap.add_argument("--cpu-steps", type=int, default=20)
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg (profiling runs)")
+    ap.add_argument("--no-graph", action="store_true", help="time eager launches instead of a CUDA-graph replay")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)
 
@@ -257,9 +277,14 @@ def main():
         step(i)
         torch.distributed.all_gather_into_tensor(gathered, outs[i & 1])
 
+    graph = not args.no_graph
     with ClockSampler(local_rank) as clk:
-        ms = timed(step, args.steps, args.warmup, world)
-    ms_gemm = timed(gemm_only, args.steps, args.warmup, world)
+        ms = timed(step, args.steps, args.warmup, world, graph)
+        if graph:  # keep the GPU busy long enough for the clock sampler to see it under load
+            for _ in range(20):
+                timed(step, args.steps, 0, world, False)
+    ms_gemm = timed(gemm_only, args.steps, args.warmup, world, graph)
+    ms_eager = timed(step, args.steps, args.warmup, world, False)
     ms_e2e = timed(step_e2e, args.steps, args.warmup, world)
     ms_gather = timed(step_gather, args.steps, args.warmup, world) if world > 1 else None
     assert device_status() == 0, "a bounded wait inside a kernel ran out"
@@ -278,11 +303,10 @@ def main():
 
     peak, peak_src = peaks()
     # per-GPU roofline of the dominant kernel: the rank's share of the weight bytes + the whole activation + its
-    # output block, over the average duration of one GEMM launch (fix-up launch and launch gap included)
+    # output block, over the average duration of one GEMM launch (launch gap included)
     n_rows_local = layers[0].rows()
     launch_bytes = n_rows_local * cfg.K // 2 + n_rows_local * cfg.K // 16 + 2 * M * cfg.K + 2 * M * n_local
     achieved = launch_bytes / gemm_s / 1e9
-    fixup = 1  # the fix-up kernel runs whenever a tile is cut, which is the case for every benchmark shape
     line = {
         "metric": metric, "value": val(per_step_s), "unit": unit, "n_gpus": world, "steps": args.steps,
         "warmup": args.warmup, "ms_per_step": ms / args.steps, "higher_is_better": True, "scaling": "strong",
@@ -290,13 +314,14 @@ def main():
         "config": {"workload": cfg.name, "M": M, "N": cfg.N, "K": cfg.K, "epilogue": "silu*mul->bf16" if cfg.glu else "bf16",
                    "sharding": f"N-sharded {world} way(s), no reduction", "l2": f"weights rotate through {nbuf} distinct copies "
                    f"({nbuf * layers[0].weight_bytes() / 2**20:.0f} MiB per GPU > 126 MiB L2)",
-                   "step": "quant_fp4_bf16 + skinny_fp4_glu_bf16 (+ fix-up)"},
+                   "step": "quant_fp4_bf16 + skinny_fp4_glu_bf16" if M <= 128 else "quant_fp4_bf16 + gemm_fp4_glu_bf16",
+                   "timing": "CUDA-graph replay of the timed steps" if graph else "eager launches", "eager_ms_per_step": ms_eager / args.steps},
         "e2e": {"value": val(e2e_s), "unit": unit, "h2d_bytes_per_step": x.numel() * 2, "d2h_bytes_per_step": M * n_local * 2,
                 "ms_per_step": ms_e2e / args.steps},
-        "gpu_launches": args.steps * (2 + fixup),
+        "gpu_launches": args.steps * 2,
         "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
                      "traffic": NCU_TRAFFIC_BYTES.get(cfg.index) if world == 1 else None, "algorithmic_bytes": launch_bytes,
-                     "kernel": "umma_gemm_kernel (+ skinny_fixup_kernel)", "us_per_launch": gemm_s * 1e6, "peak_source": peak_src},
+                     "kernel": "umma_gemm_kernel", "us_per_launch": gemm_s * 1e6, "peak_source": peak_src},
         "clocks": clocks,
     }
     if ms_gather is not None:

@@ -67,8 +67,9 @@ int q27b_silu_mul_quant_fp4_glu_bf16(const void* gu, int T, int I, float alpha_g
 
 /* D[M][N] = alpha(n) * A . W^T (+ beta * C), fp32. alpha[i] applies from column alpha_begin[i] on (1..4
  * segments, HOST arrays). c may alias d or be null. ws: at least q27b_skinny_workspace_bytes(M, N, K) bytes,
- * 16-byte aligned, shared by all calls of a stream in stream order; its contents need no initialisation and
- * carry no state between calls. A token's result does not depend on M. Replaces skinny_fp4
+ * 16-byte aligned, shared by all calls of a stream in stream order; it must be zeroed once before the first call
+ * (its first 16 KiB hold per-tile arrival counters, which every call leaves at zero, exactly the reference's
+ * contract, engine/src/kernels.h:240-242). A token's result does not depend on M. Replaces skinny_fp4
  * (engine/src/kernels.h:240-245, engine/src/skinny.cu:462-549; the reference stops at M = 64). */
 int q27b_skinny_fp4(int M, int N, int K, const uint8_t* a, const uint8_t* a_sf, const uint8_t* w, const uint8_t* w_sf,
                     int alpha_count, const int* alpha_begin, const float* alpha, const float* c, float beta, float* d,
@@ -84,7 +85,8 @@ int q27b_skinny_fp4_glu_bf16(int M, int I, int K, const uint8_t* a, const uint8_
                              const uint8_t* gate_up_sf, float alpha_gate, float alpha_up, void* d, void* ws,
                              size_t ws_bytes, void* stream);
 /* Workspace bytes of the three calls above on the current device (-1 without a device). The reference sizes its
- * workspace at 32 MiB (engine/src/model.h:462); this is never more than 2 * SMs * M * 512 bytes. */
+ * workspace at 32 MiB (engine/src/model.h:462), which covers every shape up to M = 64 on a 148-SM device; the
+ * bound is 16 KiB + 4 * SMs * M * 512 bytes (38 MiB at M = 128). */
 int64_t q27b_skinny_workspace_bytes(int M, int N, int K);
 
 /* ---- many-row GEMM, any M (N and K multiples of 128) ------------------------------------------------------------ */
@@ -112,8 +114,9 @@ int q27b_device_status(uint32_t* status);
  * product entry point routes through it. No counterpart in the reference. */
 int q27b_ref_gemm_fp4(int M, int N, int K, const uint8_t* a, const uint8_t* a_sf, const uint8_t* b, const uint8_t* b_sf,
                       float alpha, float* d, void* stream);
-/* Host-only view of the weight-streaming work split (no CUDA call): the pieces {tile, c0, c1, slot} of CTA `cta`
- * for a device with `sms` multiprocessors; returns the number of pieces. */
+/* Host-only view of the weight-streaming work split (no CUDA call): the pieces {tile, c0, c1, slot} of unit range
+ * `cta` when the shape is cut into `sms` ranges (the launchers use two per multiprocessor); returns the number of
+ * pieces. */
 int q27b_skinny_plan(int N, int K, int sms, int cta, int* seg, int cap, int* grid_out, int64_t* units_out);
 int q27b_skinny_unit_owner(int N, int K, int sms, int64_t unit);
 

@@ -208,7 +208,7 @@ int q27b_skinny_plan(int N, int K, int sms, int cta, int* seg, int cap, int* gri
   if (grid_out) *grid_out = p.grid;
   if (units_out) *units_out = p.units;
   if (cta < 0 || cta >= p.grid) return 0;
-  int64_t u = unit_begin(p, cta);
+  int64_t u = -1;
   Segment s;
   int n = 0;
   while (next_segment(p, cta, u, s)) {

@@ -68,10 +68,11 @@ constexpr uint32_t kMaxPolls = 1u << 28;
 // Waits for the phase with the given parity; gives up when `abort_flag` (shared memory) is raised by another
 // role or when the budget is spent, in which case it raises the flag itself and records `code`.
 __device__ __forceinline__ bool mbar_wait_bounded(uint32_t bar, uint32_t parity, volatile uint32_t* abort_flag,
-                                                  uint32_t* status, uint32_t code) {
+                                                  uint32_t* status, uint32_t code, uint32_t sleep_ns = 0) {
   if (mbar_try_wait(bar, parity)) return true;
   const long long t0 = clock64();
   for (uint32_t i = 1; i < kMaxPolls; i++) {
+    if (sleep_ns) __nanosleep(sleep_ns);  // long waits back off: polls go through the shared-memory pipe
     if (mbar_try_wait(bar, parity)) return true;
     if ((i & 63u) == 0u) {
       if (*abort_flag) return false;
@@ -81,6 +82,16 @@ __device__ __forceinline__ bool mbar_wait_bounded(uint32_t bar, uint32_t parity,
   *abort_flag = 1u;
   if (status) atomicCAS(status, 0u, code);
   return false;
+}
+
+// The same for a whole (converged) warp: one lane polls, then every lane observes the completed phase itself.
+__device__ __forceinline__ bool warp_wait(uint32_t bar, uint32_t parity, volatile uint32_t* abort_flag,
+                                          uint32_t* status, uint32_t code, uint32_t sleep_ns) {
+  uint32_t ok = 1;
+  if ((threadIdx.x & 31) == 0) ok = mbar_wait_bounded(bar, parity, abort_flag, status, code, sleep_ns);
+  ok = __shfl_sync(0xffffffffu, ok, 0);
+  if (ok) ok = mbar_wait_bounded(bar, parity, abort_flag, status, code);
+  return __all_sync(0xffffffffu, ok) != 0;
 }
 
 // ------------------------------------------------------------------------------------------------ TMA
@@ -209,5 +220,17 @@ __device__ __forceinline__ void tmem_ld16(uint32_t taddr, float* v) {
   for (int i = 0; i < 16; i++) v[i] = __uint_as_float(r[i]);
 }
 __device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+
+// 32 lanes x 16 consecutive 32-bit columns from registers: thread t of the warp writes lane (base lane + t);
+// v = four 16-byte vectors, in column order.
+__device__ __forceinline__ void tmem_st16(uint32_t taddr, const uint4 (&v)[4]) {
+  asm volatile(
+      "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16};"
+      ::"r"(taddr), "r"(v[0].x), "r"(v[0].y), "r"(v[0].z), "r"(v[0].w), "r"(v[1].x), "r"(v[1].y), "r"(v[1].z),
+        "r"(v[1].w), "r"(v[2].x), "r"(v[2].y), "r"(v[2].z), "r"(v[2].w), "r"(v[3].x), "r"(v[3].y), "r"(v[3].z),
+        "r"(v[3].w)
+      : "memory");
+}
+__device__ __forceinline__ void tmem_st_wait() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
 
 }  // namespace q27b

@@ -5,14 +5,18 @@
 //  * weight streaming (1 <= M <= 128, "skinny"): the roles of the operands are swapped — a 128-row weight tile is
 //    the MMA's M side, the (padded) tokens are its N side — so one instruction consumes 4 KiB of weights whatever
 //    the token count, and the kernel is bound by HBM. The K range of the whole weight matrix is cut into
-//    equal contiguous unit ranges, one per SM (layout.h); tiles cut by a range boundary are finished by
-//    a small fix-up kernel that sums the partial tiles in ascending K order (deterministic, independent of M).
+//    equal contiguous unit ranges, one per SM (layout.h); a tile cut by a range boundary is finished by whichever
+//    of its CTAs arrives last, which sums the partial tiles in ascending K order whatever the order of arrival
+//    (deterministic, independent of M; no CTA ever waits for another).
 //  * many rows (prefill): 128 tokens x 128 output channels per tile, tiles walked token-tile fastest so that the
 //    CTAs running together share weight tiles through L2; accumulators double-buffered in tensor memory so the
 //    epilogue of one tile overlaps the MMAs of the next.
 //
-// Warp roles (192 threads): warp 0 = TMA producer (one lane), warp 1 = tensor-memory owner and MMA issuer (one
-// lane), warps 2..5 = epilogue (tcgen05.ld -> alpha / residual / SiLU*mul -> fp32 or bf16 stores).
+// Warp roles (320 threads): warp 0 = TMA producer (one lane), warp 1 = tensor-memory owner and MMA issuer (one
+// lane), warps 2..5 = epilogue (tcgen05.ld -> alpha / residual / SiLU*mul -> fp32 or bf16 stores), warps 6..9 =
+// scale feeders (scale atoms shared memory -> registers -> tcgen05.st; measured here: a tcgen05.cp of one 512-byte
+// atom costs the MMA issuer ~90 cycles and an MMA ~140 whatever its N, so eight copies per stage on the issuing
+// thread capped the stream at about half of HBM speed).
 // No multicast, no peer memory. Every wait is bounded (ptx_sm100.cuh); a timeout is reported through a status word.
 //
 // Replaces, behind the same launcher contracts: skinny_fp4 (engine/src/skinny.cu:154-549), gemm_fp4 /
@@ -28,9 +32,15 @@ namespace q27b {
 
 __device__ uint32_t g_status;  // first bounded-wait timeout code since the last clear (0 = none)
 
+unsigned long long* g_trace = nullptr;  // optional device buffer for in-kernel time stamps (q27b_trace_set)
+
 namespace {
 
 enum Epi : int { kEpiF32 = 0, kEpiBf16 = 1, kEpiGluBf16 = 2 };
+
+constexpr int kThreads = 320;       // warp 0: TMA producer, 1: MMA issuer, 2..5: epilogue, 6..9: scale feeders
+constexpr int kCounterBytes = 16384;  // per-tile arrival counters at the head of the workspace (4096 tiles)
+constexpr int kMaxParts = 500;        // unit ranges that may share one tile (never more than there are ranges)
 
 struct GemmParams {
   int M, N, K;          // tokens, weight rows (2 I for gate | up), reduction length
@@ -43,27 +53,35 @@ struct GemmParams {
   const float* c;       // residual (may alias d) or null
   float beta;
   void* d;              // fp32 or bf16 output
+  int* counters;        // weight streaming: arrivals per cut tile (zero between calls)
   float* partials;      // weight streaming: per-CTA partial tiles [2 * grid][M][128]
   SkinnyPlan plan;      // weight streaming
   int m_tiles, items;   // many rows
+  unsigned long long* trace;  // optional [cta][4][64] globaltimer samples (null: off)
 };
 
-template <int NB, int STAGES>
+// CTAS = CTAs of this configuration that fit on one SM (2: half the shared and tensor memory each, so that the
+// epilogue of one CTA overlaps the stream of the other and a CTA of the next launch can move in as soon as one of
+// this launch leaves).
+template <int NB, int STAGES, int CTAS>
 struct Cfg {
   static_assert(NB % 16 == 0 && NB >= 16 && NB <= 128, "N-side tile: 16..128 rows");
+  static_assert(CTAS == 1 || CTAS == 2, "one or two CTAs per SM");
   static constexpr int kPBytes = 128 * 128;  // 128 rows x 256 E2M1
   static constexpr int kQBytes = NB * 128;
   static constexpr int kSfBytes = 4 * 512;   // 4 MMA steps x one 512-byte atom
   static constexpr int kStageBytes = kPBytes + kQBytes + 2 * kSfBytes;
   static constexpr int kOffQ = kPBytes, kOffSfP = kPBytes + kQBytes, kOffSfQ = kOffSfP + kSfBytes;
-  static constexpr int kXchgBytes = 8 * 64 * 4;  // SiLU*mul exchange between the gate and the up warps
-  static constexpr int kBarBytes = (2 * STAGES + 4) * 8 + 16;
+  static constexpr int kXchgBytes = 8 * 64 * 4 + 2048;  // SiLU*mul exchange between the gate and the up warps + cut-tile info
+  static constexpr int kNumBars = 3 * STAGES + 4;
+  static constexpr int kBarBytes = kNumBars * 8 + 16;
   static constexpr int kSmemBytes = STAGES * kStageBytes + kXchgBytes + kBarBytes + 1024;  // + alignment slack
-  static constexpr int kTmemCols = 512;
-  static constexpr int kSfCol0 = 256;  // accumulators: columns [0, 2 NB); scales: 32 columns per stage from here
+  static constexpr int kTmemCols = 512 / CTAS;
+  static constexpr int kSfCol0 = 2 * NB;  // accumulators: columns [0, 2 NB); scales: 32 columns per stage from here
+  static constexpr int kRangesPerCta = 2 / CTAS;  // unit ranges of the (always 2-per-SM) work split per CTA
   static_assert(kStageBytes % 1024 == 0, "stage tiles must stay 1024-byte aligned");
-  static_assert(kSfCol0 + 32 * STAGES <= kTmemCols && 2 * NB <= kSfCol0, "tensor memory budget");
-  static_assert(kSmemBytes <= 227 * 1024, "shared memory budget");
+  static_assert(kSfCol0 + 32 * STAGES <= kTmemCols, "tensor memory budget");
+  static_assert(CTAS * (kSmemBytes + 1024) <= 228 * 1024, "shared memory budget");
 };
 
 struct Work {
@@ -73,21 +91,33 @@ struct Work {
   int tile;
 };
 
-template <bool kSwap>
+// The pieces of work of this CTA, in the order every role walks them. Weight streaming: the work split always has
+// two unit ranges per SM (so that results do not depend on which configuration runs); a CTA takes kRanges
+// consecutive ranges.
+template <bool kSwap, int kRanges>
 struct WorkIter {
   const GemmParams& p;
   int64_t u;
-  int item;
+  int item, range, range_end;
   __device__ explicit WorkIter(const GemmParams& p_) : p(p_) {
-    if constexpr (kSwap) u = unit_begin(p.plan, blockIdx.x);
-    else item = blockIdx.x;
+    if constexpr (kSwap) {
+      u = -1, range = blockIdx.x * kRanges;
+      range_end = min(range + kRanges, p.plan.grid);
+    } else {
+      item = blockIdx.x;
+    }
   }
   __device__ bool next(Work& w) {
     if constexpr (kSwap) {
       Segment s;
-      if (!next_segment(p.plan, blockIdx.x, u, s)) return false;
-      w.p_row0 = s.tile * 128, w.q_row0 = 0, w.c0 = s.c0, w.c1 = s.c1, w.slot = s.slot, w.tile = s.tile;
-      return true;
+      while (range < range_end) {
+        if (next_segment(p.plan, range, u, s)) {
+          w.p_row0 = s.tile * 128, w.q_row0 = 0, w.c0 = s.c0, w.c1 = s.c1, w.slot = s.slot, w.tile = s.tile;
+          return true;
+        }
+        range++, u = -1;
+      }
+      return false;
     } else {
       if (item >= p.items) return false;
       const int mi = item % p.m_tiles, ni = item / p.m_tiles;
@@ -98,37 +128,113 @@ struct WorkIter {
   }
 };
 
-__device__ __forceinline__ float silu_mul(float g, float u) { return g / (1.f + __expf(-g)) * u; }
+// The same walk chunk by chunk (one chunk = one pipeline stage).
+template <bool kSwap, int kRanges>
+struct ChunkIter {
+  WorkIter<kSwap, kRanges> it;
+  Work w;
+  int c;
+  bool valid;
+  __device__ explicit ChunkIter(const GemmParams& p) : it(p) {
+    valid = it.next(w);
+    c = valid ? w.c0 : 0;
+  }
+  __device__ void advance() {
+    if (++c < w.c1) return;
+    valid = it.next(w);
+    c = valid ? w.c0 : 0;
+  }
+};
+
+__device__ __forceinline__ unsigned long long gtime() {
+  unsigned long long t;
+  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+  return t;
+}
+#define TRACE(kind, idx)                                                                                  \
+  do {                                                                                                    \
+    if (p.trace && (idx) < 64) p.trace[(size_t(blockIdx.x) * 4 + (kind)) * 64 + (idx)] = gtime();         \
+  } while (0)
+
+// silu(g) * u with the fast exponential and reciprocal (the reference's fused epilogue uses the same pair,
+// engine/src/gemm_mma.cu:362-378): no division slow path, and 1 / (1 + inf) = 0 for very negative gates.
+__device__ __forceinline__ float silu_mul(float g, float u) {
+  float e, r;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(e) : "f"(g * -1.44269504f));
+  asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(r) : "f"(1.f + e));
+  return g * r * u;
+}
 
 __device__ __forceinline__ uint16_t bf16_bits(float v) { return __bfloat16_as_ushort(__float2bfloat16_rn(v)); }
 
 // Final value of output (m, n) from the accumulated dot product, with the reference's explicit roundings
-// (engine/src/skinny.cu:452-458) so that the in-place path and the fix-up path agree bit for bit.
+// (engine/src/skinny.cu:452-458) so that a tile finished in place and a tile summed from partials agree bit for bit.
 __device__ __forceinline__ float finish_f32(const GemmParams& p, float acc, int m, int n) {
   float out = __fmul_rn(alpha_of(p.alpha, n), acc);
   if (p.c) out = __fmaf_rn(p.beta, p.c[int64_t(m) * p.N + n], out);
   return out;
 }
 
-template <int NB, int STAGES, bool kSwap, int kEpi>
-__global__ void __launch_bounds__(192, 1) umma_gemm_kernel(const __grid_constant__ CUtensorMap tmap_p,
-                                                           const __grid_constant__ CUtensorMap tmap_q,
-                                                           const __grid_constant__ GemmParams p) {
-  using C = Cfg<NB, STAGES>;
+__device__ __forceinline__ void epi_bar() { asm volatile("bar.sync 1, 128;" ::: "memory"); }
+
+// Weight streaming: the epilogue of 8 tokens (m0 .. m0 + 7) of one weight row per thread (row = tile row 0..127).
+template <int kEpi>
+__device__ __forceinline__ void store_swapped(const GemmParams& p, const float (&v)[8], int m0, int tile, int row,
+                                              float* xchg) {
+  if constexpr (kEpi == kEpiGluBf16) {
+    // rows 0..63 of the tile are gate rows, 64..127 the up rows of the same 64 outputs
+    if (row >= 64) {
+#pragma unroll
+      for (int j = 0; j < 8; j++) xchg[j * 64 + row - 64] = v[j];
+    }
+    epi_bar();
+    if (row < 64) {
+      const float ag = p.alpha.alpha[0], au = p.alpha_up;
+      uint16_t* d = static_cast<uint16_t*>(p.d) + int64_t(tile) * 64 + row;
+#pragma unroll
+      for (int j = 0; j < 8; j++)
+        if (m0 + j < p.M)
+          d[int64_t(m0 + j) * (p.N / 2)] = bf16_bits(silu_mul(__fmul_rn(ag, v[j]), __fmul_rn(au, xchg[j * 64 + row])));
+    }
+    epi_bar();
+  } else {
+    const int n = tile * 128 + row;
+#pragma unroll
+    for (int j = 0; j < 8; j++) {
+      const int m = m0 + j;
+      if (m < p.M) {
+        const float out = finish_f32(p, v[j], m, n);
+        if constexpr (kEpi == kEpiF32) static_cast<float*>(p.d)[int64_t(m) * p.N + n] = out;
+        else static_cast<uint16_t*>(p.d)[int64_t(m) * p.N + n] = bf16_bits(out);
+      }
+    }
+  }
+}
+
+template <int NB, int STAGES, int CTAS, bool kSwap, int kEpi>
+__global__ void __launch_bounds__(kThreads, CTAS) umma_gemm_kernel(const __grid_constant__ CUtensorMap tmap_p,
+                                                                const __grid_constant__ CUtensorMap tmap_q,
+                                                                const __grid_constant__ GemmParams p) {
+  using C = Cfg<NB, STAGES, CTAS>;
+  using Chunks = ChunkIter<kSwap, C::kRangesPerCta>;
+  using Works = WorkIter<kSwap, C::kRangesPerCta>;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   float* xchg = reinterpret_cast<float*>(smem + STAGES * C::kStageBytes);
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + STAGES * C::kStageBytes + C::kXchgBytes);
-  const uint32_t full0 = smem_u32(bars), empty0 = full0 + 8 * STAGES, afull0 = empty0 + 8 * STAGES,
-                 aempty0 = afull0 + 16;
-  uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(bars + 2 * STAGES + 4);
+  const uint32_t full0 = smem_u32(bars), empty0 = full0 + 8 * STAGES, sfr0 = empty0 + 8 * STAGES,
+                 afull0 = sfr0 + 8 * STAGES, aempty0 = afull0 + 16;
+  uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(bars + C::kNumBars);
   volatile uint32_t* abort_flag = tmem_holder + 1;
+  volatile uint32_t* last_flag = tmem_holder + 2;
+  volatile int* seg_info = reinterpret_cast<volatile int*>(xchg) + 8 * 64;  // [0] parts of a cut tile, [1..] their slots
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
 
   if (threadIdx.x == 0) {
+    TRACE(3, 0);
     prefetch_tensormap(&tmap_p);
     prefetch_tensormap(&tmap_q);
-    for (int s = 0; s < STAGES; s++) mbar_init(full0 + 8 * s, 1), mbar_init(empty0 + 8 * s, 1);
+    for (int s = 0; s < STAGES; s++) mbar_init(full0 + 8 * s, 1), mbar_init(empty0 + 8 * s, 1), mbar_init(sfr0 + 8 * s, 4);
     for (int b = 0; b < 2; b++) mbar_init(afull0 + 8 * b, 1), mbar_init(aempty0 + 8 * b, 4);
     *abort_flag = 0;
     mbar_init_fence();
@@ -142,38 +248,63 @@ __global__ void __launch_bounds__(192, 1) umma_gemm_kernel(const __grid_constant
   tc_fence_after_sync();
   const uint32_t tmem_base = *tmem_holder;
   const uint32_t smem_base = smem_u32(smem);
+  // Kernels queued behind this one may be scheduled from now on: they wait for this grid to finish before they
+  // touch anything it reads or writes, and start streaming their own weights into freed SMs meanwhile.
+  pdl_trigger();
 
   if (warp == 0) {
     // ------------------------------------------------------------------------------------------ TMA producer
     if (lane == 0) {
       // Weights are read once (evict first); the activations are re-read by every CTA (keep them in L2).
-      const uint64_t hint_p = kSwap ? kEvictFirst : kEvictLast, hint_q = kSwap ? kEvictLast : kEvictNormal;
-      WorkIter<kSwap> it(p);
-      Work w;
-      int stage = 0;
-      uint32_t phase = 0, armed = 0;  // armed: bit s set once stage s has a copy that may still be in flight
-      uint32_t last_parity = 0;       // bit s: parity of the full-barrier phase stage s was last armed for
-      bool ok = true;
-      pdl_wait();  // the N-side operand of the weight-streaming call is produced by the preceding kernel
-      while (ok && it.next(w)) {
-        for (int c = w.c0; c < w.c1; c++) {
-          if (!mbar_wait_bounded(empty0 + 8 * stage, phase ^ 1, abort_flag, &g_status, kStatusEmptyWaitTimeout)) {
-            ok = false;
-            break;
-          }
-          const int nsteps = min(4, p.ksteps - 4 * c);
-          const uint32_t sbase = smem_base + stage * C::kStageBytes, bar = full0 + 8 * stage;
-          mbar_arrive_expect_tx(bar, C::kPBytes + C::kQBytes + 2 * nsteps * 512);
-          armed |= 1u << stage;
-          last_parity = (last_parity & ~(1u << stage)) | (phase << stage);
-          tma_load_2d(sbase, &tmap_p, c * 128, w.p_row0, bar, hint_p);
-          tma_load_2d(sbase + C::kOffQ, &tmap_q, c * 128, w.q_row0, bar, hint_q);
-          bulk_load(sbase + C::kOffSfP, p.sf_p + (int64_t(w.p_row0 / 128) * p.ksteps + 4 * c) * 512, nsteps * 512, bar,
-                    hint_p);
-          bulk_load(sbase + C::kOffSfQ, p.sf_q + (int64_t(w.q_row0 / 128) * p.ksteps + 4 * c) * 512, nsteps * 512, bar,
-                    hint_q);
-          if (++stage == STAGES) stage = 0, phase ^= 1;
+      const uint64_t hint_w = kEvictFirst, hint_a = kEvictLast;
+      const uint64_t hint_p = kSwap ? hint_w : hint_a, hint_q = kSwap ? hint_a : hint_w;
+      auto stage_bytes = [&](int c) { return uint32_t(C::kPBytes + C::kQBytes + 2 * min(4, p.ksteps - 4 * c) * 512); };
+      auto load_p = [&](const Chunks& k, int stage) {
+        const uint32_t sbase = smem_base + stage * C::kStageBytes, bar = full0 + 8 * stage;
+        tma_load_2d(sbase, &tmap_p, k.c * 128, k.w.p_row0, bar, hint_p);
+        bulk_load(sbase + C::kOffSfP, p.sf_p + (int64_t(k.w.p_row0 / 128) * p.ksteps + 4 * k.c) * 512,
+                  min(4, p.ksteps - 4 * k.c) * 512, bar, hint_p);
+      };
+      auto load_q = [&](const Chunks& k, int stage) {
+        const uint32_t sbase = smem_base + stage * C::kStageBytes, bar = full0 + 8 * stage;
+        tma_load_2d(sbase + C::kOffQ, &tmap_q, k.c * 128, k.w.q_row0, bar, hint_q);
+        bulk_load(sbase + C::kOffSfQ, p.sf_q + (int64_t(k.w.q_row0 / 128) * p.ksteps + 4 * k.c) * 512,
+                  min(4, p.ksteps - 4 * k.c) * 512, bar, hint_q);
+      };
+      // 1. Fill the ring with the operand that does not depend on the preceding kernel (the weights when
+      //    streaming), 2. wait for that kernel, 3. add the other operand, 4. steady state.
+      uint32_t armed = 0, last_parity = 0;  // stages with a copy possibly in flight / the phase they were armed for
+      int npre = 0;
+      {
+        Chunks k(p);
+        for (; k.valid && npre < STAGES; k.advance(), npre++) {
+          mbar_arrive_expect_tx(full0 + 8 * npre, stage_bytes(k.c));
+          armed |= 1u << npre;
+          TRACE(0, npre);
+          if constexpr (kSwap) load_p(k, npre); else load_q(k, npre);
         }
+      }
+      pdl_wait();
+      TRACE(3, 2);
+      Chunks k(p);
+      for (int s = 0; s < npre; s++, k.advance()) {
+        if constexpr (kSwap) load_q(k, s); else load_p(k, s);
+      }
+      int stage = npre % STAGES, tk = npre;
+      uint32_t phase = npre == STAGES ? 1 : 0;
+      bool ok = true;
+      for (; k.valid; k.advance()) {
+        if (!mbar_wait_bounded(empty0 + 8 * stage, phase ^ 1, abort_flag, &g_status, kStatusEmptyWaitTimeout)) {
+          ok = false;
+          break;
+        }
+        TRACE(0, tk);
+        tk++;
+        mbar_arrive_expect_tx(full0 + 8 * stage, stage_bytes(k.c));
+        last_parity = (last_parity & ~(1u << stage)) | (phase << stage);
+        load_p(k, stage);
+        load_q(k, stage);
+        if (++stage == STAGES) stage = 0, phase ^= 1;
       }
       if (!ok) {
         // Unwinding: let every copy that was started land before the CTA gives its shared memory back.
@@ -193,9 +324,9 @@ __global__ void __launch_bounds__(192, 1) umma_gemm_kernel(const __grid_constant
     // ------------------------------------------------------------------------------------------ MMA issuer
     if (lane == 0) {
       constexpr uint32_t idesc = umma_idesc_nvfp4(NB);
-      WorkIter<kSwap> it(p);
+      Works it(p);
       Work w;
-      int stage = 0;
+      int stage = 0, tk = 0, nseg = 0;
       uint32_t phase = 0;
       bool ok = true;
       for (int i = 0; ok && it.next(w); i++) {
@@ -206,78 +337,141 @@ __global__ void __launch_bounds__(192, 1) umma_gemm_kernel(const __grid_constant
         const uint32_t d_tmem = tmem_base + buf * NB;
         uint32_t accumulate = 0;
         for (int c = w.c0; c < w.c1; c++) {
-          if (!mbar_wait_bounded(full0 + 8 * stage, phase, abort_flag, &g_status, kStatusFullWaitTimeout)) {
+          // the scale feeders arrive here once the stage has landed and its scales are in tensor memory
+          if (!mbar_wait_bounded(sfr0 + 8 * stage, phase, abort_flag, &g_status, kStatusFullWaitTimeout)) {
             ok = false;
             break;
           }
           tc_fence_after_sync();
+          TRACE(1, tk);
           const int nsteps = min(4, p.ksteps - 4 * c);
           const uint32_t sbase = smem_base + stage * C::kStageBytes;
           const uint64_t desc_p = umma_desc_k_sw128(sbase), desc_q = umma_desc_k_sw128(sbase + C::kOffQ);
           const uint32_t sf_col = tmem_base + C::kSfCol0 + 32 * stage;
           for (int ks = 0; ks < nsteps; ks++) {
-            tmem_cp_sf_atom(sf_col + 4 * ks, umma_desc_sf_atom(sbase + C::kOffSfP + 512 * ks));
-            tmem_cp_sf_atom(sf_col + 16 + 4 * ks, umma_desc_sf_atom(sbase + C::kOffSfQ + 512 * ks));
             // 64 E2M1 = 32 bytes further along K inside the 128-byte swizzle span: +2 in 16-byte address units
             umma_nvfp4(d_tmem, desc_p + 2 * ks, desc_q + 2 * ks, idesc, sf_col + 4 * ks, sf_col + 16 + 4 * ks,
                        accumulate);
             accumulate = 1;
           }
           umma_commit(empty0 + 8 * stage);  // the stage is free once these MMAs have read it
+          TRACE(2, tk);
+          tk++;
           if (++stage == STAGES) stage = 0, phase ^= 1;
         }
         if (ok) umma_commit(afull0 + 8 * buf);
+        nseg = i + 1;
       }
+      // Tensor memory is freed by this warp: not before the epilogue has read the last accumulators.
+      for (int j = nseg - 1; ok && j >= 0 && j >= nseg - 2; j--)
+        ok = mbar_wait_bounded(aempty0 + 8 * (j & 1), (j >> 1) & 1, abort_flag, &g_status, kStatusAccumFreeTimeout, 64);
+    }
+  } else if (warp >= 6) {
+    // ------------------------------------------------------------------------------------------ scale feeders
+    // Each of the four warps copies the stage's scale atoms (shared memory -> registers -> its own quarter of the
+    // tensor-memory lanes), which yields the four-fold replication the MMA expects without occupying the MMA
+    // issuer: line l of an atom (16 bytes) becomes 4 columns of lane l.
+    const uint32_t lane_base = uint32_t((warp & 3) * 32) << 16;
+    int stage = 0;
+    uint32_t phase = 0;
+    for (Chunks k(p); k.valid; k.advance()) {
+      if (!warp_wait(full0 + 8 * stage, phase, abort_flag, &g_status, kStatusFullWaitTimeout, 32)) break;
+      const uint8_t* sb = smem + stage * C::kStageBytes;
+      const uint4* sfp = reinterpret_cast<const uint4*>(sb + C::kOffSfP) + lane;
+      const uint4* sfq = reinterpret_cast<const uint4*>(sb + C::kOffSfQ) + lane;
+      uint4 a[4], b[4];
+#pragma unroll
+      for (int ks = 0; ks < 4; ks++) a[ks] = sfp[32 * ks], b[ks] = sfq[32 * ks];  // (steps past K: stale, unused)
+      const uint32_t taddr = tmem_base + lane_base + C::kSfCol0 + 32 * stage;
+      tmem_st16(taddr, a);
+      tmem_st16(taddr + 16, b);
+      tmem_st_wait();
+      tc_fence_before_sync();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(sfr0 + 8 * stage);
+      if (++stage == STAGES) stage = 0, phase ^= 1;
     }
   } else {
     // ------------------------------------------------------------------------------------------ epilogue
     const int quarter = warp & 3;  // the 32 tensor-memory lanes this warp may read
     const int row = quarter * 32 + lane;
-    WorkIter<kSwap> it(p);
+    Works it(p);
     Work w;
     for (int i = 0; it.next(w); i++) {
       const int buf = i & 1;
-      if (!mbar_wait_bounded(afull0 + 8 * buf, (i >> 1) & 1, abort_flag, &g_status, kStatusAccumWaitTimeout)) break;
+      if constexpr (kSwap) {
+        if (w.slot >= 0 && threadIdx.x == 64) {  // which ranges share this cut tile, and where their partial tiles are
+          const int64_t ubeg = int64_t(w.tile) * p.plan.chunks;
+          const int g0 = unit_owner(p.plan, ubeg), g1 = unit_owner(p.plan, ubeg + p.plan.chunks - 1);
+          seg_info[0] = g1 - g0 + 1;
+          for (int g = g0; g <= g1 && g - g0 < kMaxParts; g++)
+            seg_info[1 + g - g0] = 2 * g + (unit_begin(p.plan, g) >= ubeg ? 0 : 1);
+        }
+      }
+      if (!warp_wait(afull0 + 8 * buf, (i >> 1) & 1, abort_flag, &g_status, kStatusAccumWaitTimeout, 128)) break;
       tc_fence_after_sync();
+      if (threadIdx.x == 64) TRACE(3, 4 + i);
       const uint32_t taddr = tmem_base + (uint32_t(quarter * 32) << 16) + buf * NB;
       if constexpr (kSwap) {
         // lane = weight row (output channel), column = token
-        const int n = w.p_row0 + row;
-        for (int m0 = 0; m0 < p.M; m0 += 8) {
-          float v[8];
-          tmem_ld8(taddr + m0, v);
-          tmem_ld_wait();
-          if (w.slot >= 0) {
+        if (w.slot < 0) {
+          for (int m0 = 0; m0 < p.M; m0 += 8) {
+            float v[8];
+            tmem_ld8(taddr + m0, v);
+            tmem_ld_wait();
+            store_swapped<kEpi>(p, v, m0, w.tile, row, xchg);
+          }
+          tc_fence_before_sync();
+          __syncwarp();
+          if (lane == 0) mbar_arrive(aempty0 + 8 * buf);
+        } else {
+          // A tile cut by a range boundary: leave the partial sums, count the arrival; whoever arrives last sums
+          // all partial tiles in ascending K order (whatever the order of arrival) and finishes the tile.
+          for (int m0 = 0; m0 < p.M; m0 += 8) {
+            float v[8];
+            tmem_ld8(taddr + m0, v);
+            tmem_ld_wait();
             float* part = p.partials + (int64_t(w.slot) * p.M + m0) * 128 + row;
 #pragma unroll
             for (int j = 0; j < 8; j++)
-              if (m0 + j < p.M) part[j * 128] = v[j];
-          } else if constexpr (kEpi == kEpiGluBf16) {
-            // rows 0..63 of the tile are gate rows, 64..127 the up rows of the same 64 outputs
-            if (quarter >= 2) {
+              if (m0 + j < p.M) __stcg(part + j * 128, v[j]);
+          }
+          tc_fence_before_sync();
+          __syncwarp();
+          if (lane == 0) mbar_arrive(aempty0 + 8 * buf);
+          epi_bar();  // every partial of this CTA is written (and seg_info is visible) ...
+          if (threadIdx.x == 64) {
+            __threadfence();  // ... and published device-wide before the arrival is counted
+            *last_flag = atomicAdd(p.counters + w.tile, 1) == seg_info[0] - 1;
+          }
+          epi_bar();
+          if (*last_flag) {
+            __threadfence();
+            const int nparts = seg_info[0];
+            for (int m0 = 0; m0 < p.M; m0 += 8) {
+              float v[8];
+              for (int q0 = 0; q0 < nparts; q0 += 4) {  // four partial tiles in flight at a time
+                float x[4][8];
 #pragma unroll
-              for (int j = 0; j < 8; j++) xchg[j * 64 + row - 64] = v[j];
-            }
-            asm volatile("bar.sync 1, 128;" ::: "memory");
-            if (quarter < 2) {
-              const float ag = p.alpha.alpha[0], au = p.alpha_up;
-              uint16_t* d = static_cast<uint16_t*>(p.d) + int64_t(w.tile) * 64 + row;
+                for (int q = 0; q < 4; q++) {
+                  if (q0 + q < nparts) {
+                    const float* part = p.partials + (int64_t(seg_info[1 + q0 + q]) * p.M + m0) * 128 + row;
 #pragma unroll
-              for (int j = 0; j < 8; j++)
-                if (m0 + j < p.M)
-                  d[int64_t(m0 + j) * (p.N / 2)] = bf16_bits(silu_mul(__fmul_rn(ag, v[j]), __fmul_rn(au, xchg[j * 64 + row])));
-            }
-            asm volatile("bar.sync 1, 128;" ::: "memory");
-          } else {
+                    for (int j = 0; j < 8; j++) x[q][j] = m0 + j < p.M ? __ldcg(part + j * 128) : 0.f;
+                  }
+                }
 #pragma unroll
-            for (int j = 0; j < 8; j++) {
-              const int m = m0 + j;
-              if (m < p.M) {
-                const float out = finish_f32(p, v[j], m, n);
-                if constexpr (kEpi == kEpiF32) static_cast<float*>(p.d)[int64_t(m) * p.N + n] = out;
-                else static_cast<uint16_t*>(p.d)[int64_t(m) * p.N + n] = bf16_bits(out);
+                for (int q = 0; q < 4; q++) {
+                  if (q0 + q < nparts) {
+#pragma unroll
+                    for (int j = 0; j < 8; j++) v[j] = (q0 + q == 0) ? x[q][j] : __fadd_rn(v[j], x[q][j]);
+                  }
+                }
               }
+              store_swapped<kEpi>(p, v, m0, w.tile, row, xchg);
             }
+            if (threadIdx.x == 64) p.counters[w.tile] = 0;  // the counters are zero again when the kernel ends
+            epi_bar();  // seg_info may be rewritten for the next piece only after everyone has used it
           }
         }
       } else {
@@ -329,71 +523,28 @@ __global__ void __launch_bounds__(192, 1) umma_gemm_kernel(const __grid_constant
             }
           }
         }
+        tc_fence_before_sync();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(aempty0 + 8 * buf);
       }
-      tc_fence_before_sync();
-      __syncwarp();
-      if (lane == 0) mbar_arrive(aempty0 + 8 * buf);
+      if (threadIdx.x == 64) TRACE(3, 8 + i);
     }
   }
 
-  // Teardown: every role is done (or gave up); tensor memory goes back before the CTA exits.
-  pdl_trigger();
+  // Teardown: every role is done (or gave up); tensor memory goes back before the CTA exits. The lanes that
+  // skipped their warp's single-lane role wait for that lane here: a CTA-wide barrier counts a warp as arrived as
+  // soon as any of its lanes arrives, so a warp must reach it converged.
+  __syncwarp();
   tc_fence_before_sync();
   __syncthreads();
+  if (threadIdx.x == 0) TRACE(3, 12);
+  if (threadIdx.x == 32) TRACE(3, 13);
+  if (threadIdx.x == 64) TRACE(3, 14);
+  if (threadIdx.x == 192) TRACE(3, 15);
   if (warp == 1) {
     __syncwarp();
     tc_fence_after_sync();
     tmem_dealloc(tmem_base, C::kTmemCols);
-  }
-}
-
-// Sums the partial tiles of every weight tile that was cut by a CTA range boundary, in ascending K order, and
-// applies the epilogue. Block = (tile, group of 8 tokens), thread = row of the tile.
-template <int kEpi>
-__global__ void __launch_bounds__(128) skinny_fixup_kernel(const __grid_constant__ GemmParams p) {
-  pdl_trigger();
-  const int tile = blockIdx.x, row = threadIdx.x;
-  const int64_t ubeg = int64_t(tile) * p.plan.chunks;
-  const int g0 = unit_owner(p.plan, ubeg), g1 = unit_owner(p.plan, ubeg + p.plan.chunks - 1);
-  if (g0 == g1) return;  // finished in place by its only owner
-  pdl_wait();
-  __shared__ float up_s[8][64];
-  const int m0 = blockIdx.y * 8;
-  float acc[8];
-#pragma unroll
-  for (int j = 0; j < 8; j++) acc[j] = 0.f;
-  for (int g = g0; g <= g1; g++) {
-    const int slot = 2 * g + (unit_begin(p.plan, g) >= ubeg ? 0 : 1);
-    const float* part = p.partials + (int64_t(slot) * p.M + m0) * 128 + row;
-#pragma unroll
-    for (int j = 0; j < 8; j++)
-      if (m0 + j < p.M) acc[j] = g == g0 ? __ldcg(part + j * 128) : __fadd_rn(acc[j], __ldcg(part + j * 128));
-  }
-  const int n = tile * 128 + row;
-  if constexpr (kEpi == kEpiGluBf16) {
-    if (row >= 64) {
-#pragma unroll
-      for (int j = 0; j < 8; j++) up_s[j][row - 64] = acc[j];
-    }
-    __syncthreads();
-    if (row < 64) {
-      uint16_t* d = static_cast<uint16_t*>(p.d) + int64_t(tile) * 64 + row;
-#pragma unroll
-      for (int j = 0; j < 8; j++)
-        if (m0 + j < p.M)
-          d[int64_t(m0 + j) * (p.N / 2)] =
-              bf16_bits(silu_mul(__fmul_rn(p.alpha.alpha[0], acc[j]), __fmul_rn(p.alpha_up, up_s[j][row])));
-    }
-  } else {
-#pragma unroll
-    for (int j = 0; j < 8; j++) {
-      const int m = m0 + j;
-      if (m < p.M) {
-        const float out = finish_f32(p, acc[j], m, n);
-        if constexpr (kEpi == kEpiF32) static_cast<float*>(p.d)[int64_t(m) * p.N + n] = out;
-        else static_cast<uint16_t*>(p.d)[int64_t(m) * p.N + n] = bf16_bits(out);
-      }
-    }
   }
 }
 
@@ -436,7 +587,7 @@ template <typename Kern>
 int launch_gemm(Kern kernel, int grid, int smem, cudaStream_t s, const CUtensorMap& mp, const CUtensorMap& mq,
                 const GemmParams& p, bool pdl) {
   cudaLaunchConfig_t cfg = {};
-  cfg.gridDim = dim3(grid), cfg.blockDim = dim3(192), cfg.dynamicSmemBytes = smem, cfg.stream = s;
+  cfg.gridDim = dim3(grid), cfg.blockDim = dim3(kThreads), cfg.dynamicSmemBytes = smem, cfg.stream = s;
   cudaLaunchAttribute attr[1];
   attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
   attr[0].val.programmaticStreamSerializationAllowed = 1;
@@ -446,48 +597,36 @@ int launch_gemm(Kern kernel, int grid, int smem, cudaStream_t s, const CUtensorM
 }
 
 // One-time opt-in to large dynamic shared memory, per kernel instantiation and per device.
-template <int NB, int STAGES, bool kSwap, int kEpi>
+template <int NB, int STAGES, int CTAS, bool kSwap, int kEpi>
 int ensure_smem() {
   static bool done[64] = {};  // one array per instantiation
   int dev = 0;
   Q27B_CUDA(cudaGetDevice(&dev));
   if (dev < 64 && done[dev]) return 0;
-  Q27B_CUDA(cudaFuncSetAttribute(umma_gemm_kernel<NB, STAGES, kSwap, kEpi>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                 Cfg<NB, STAGES>::kSmemBytes));
+  Q27B_CUDA(cudaFuncSetAttribute(umma_gemm_kernel<NB, STAGES, CTAS, kSwap, kEpi>,
+                                 cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg<NB, STAGES, CTAS>::kSmemBytes));
   if (dev < 64) done[dev] = true;
   return 0;
 }
 
-template <int NB, int STAGES, int kEpi>
+template <int NB, int STAGES, int CTAS, int kEpi>
 int run_skinny(const uint8_t* a, const uint8_t* w, GemmParams& p, cudaStream_t s) {
-  using C = Cfg<NB, STAGES>;
-  auto kernel = umma_gemm_kernel<NB, STAGES, true, kEpi>;
-  if (int rc = ensure_smem<NB, STAGES, true, kEpi>()) return rc;
+  using C = Cfg<NB, STAGES, CTAS>;
+  auto kernel = umma_gemm_kernel<NB, STAGES, CTAS, true, kEpi>;
+  if (int rc = ensure_smem<NB, STAGES, CTAS, true, kEpi>()) return rc;
   CUtensorMap mp, mq;
   if (int rc = make_operand_map(&mp, w, p.N, p.K, 128)) return rc;
   if (int rc = make_operand_map(&mq, a, p.M, p.K, NB)) return rc;
-  if (int rc = launch_gemm(kernel, p.plan.grid, C::kSmemBytes, s, mp, mq, p, true)) return rc;
-  // Any tile cut by a range boundary? (Only when the unit ranges do not coincide with tile boundaries.)
-  bool cut = false;
-  for (int g = 1; g < p.plan.grid && !cut; g++) cut = unit_begin(p.plan, g) % p.plan.chunks != 0;
-  if (cut) {
-    cudaLaunchConfig_t cfg = {};
-    cfg.gridDim = dim3(p.plan.tiles, (p.M + 7) / 8), cfg.blockDim = dim3(128), cfg.stream = s;
-    cudaLaunchAttribute attr[1];
-    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-    attr[0].val.programmaticStreamSerializationAllowed = 1;
-    cfg.attrs = attr, cfg.numAttrs = 1;
-    Q27B_CUDA(cudaLaunchKernelEx(&cfg, skinny_fixup_kernel<kEpi>, p));
-  }
-  return 0;
+  const int grid = (p.plan.grid + C::kRangesPerCta - 1) / C::kRangesPerCta;
+  return launch_gemm(kernel, grid, C::kSmemBytes, s, mp, mq, p, true);
 }
 
 template <int kEpi>
 int skinny_dispatch(const uint8_t* a, const uint8_t* w, GemmParams& p, cudaStream_t s) {
-  if (p.M <= 16) return run_skinny<16, 8, kEpi>(a, w, p, s);
-  if (p.M <= 32) return run_skinny<32, 8, kEpi>(a, w, p, s);
-  if (p.M <= 64) return run_skinny<64, 7, kEpi>(a, w, p, s);
-  return run_skinny<128, 6, kEpi>(a, w, p, s);
+  if (p.M <= 16) return run_skinny<16, 4, 2, kEpi>(a, w, p, s);
+  if (p.M <= 32) return run_skinny<32, 4, 2, kEpi>(a, w, p, s);
+  if (p.M <= 64) return run_skinny<64, 3, 2, kEpi>(a, w, p, s);
+  return run_skinny<128, 6, 1, kEpi>(a, w, p, s);
 }
 
 int check_operands(const char* what, int M, int N, int K, const void* a, const void* a_sf, const void* w,
@@ -512,11 +651,15 @@ int skinny_common(int kEpi, int M, int N, int K, const uint8_t* a, const uint8_t
   GemmParams p = {};
   p.M = M, p.N = N, p.K = K, p.ksteps = K / 64, p.chunks = (p.ksteps + 3) / 4;
   p.sf_p = w_sf, p.sf_q = a_sf, p.alpha = alpha, p.alpha_up = alpha_up, p.c = c, p.beta = beta, p.d = d;
-  p.plan = make_skinny_plan(N, K, sms);
-  const size_t need = size_t(skinny_workspace_bytes(M, p.plan.grid));
+  p.plan = make_skinny_plan(N, K, 2 * sms);  // two unit ranges per SM, whatever the token count
+  Q27B_REQUIRE(p.plan.grid <= kMaxParts, "skinny_fp4: more than %d unit ranges", kMaxParts);
+  Q27B_REQUIRE(p.plan.tiles * 4 <= kCounterBytes, "skinny_fp4: N too large (%d rows, at most %d)", N, kCounterBytes / 4 * 128);
+  const size_t need = size_t(kCounterBytes + skinny_workspace_bytes(M, p.plan.grid));
   Q27B_REQUIRE(ws && aligned16(ws) && ws_bytes >= need, "skinny_fp4: workspace too small (%zu bytes, need %zu)", ws_bytes,
                need);
-  p.partials = static_cast<float*>(ws);
+  p.counters = static_cast<int*>(ws);
+  p.partials = reinterpret_cast<float*>(static_cast<uint8_t*>(ws) + kCounterBytes);
+  p.trace = g_trace;
   switch (kEpi) {
     case kEpiF32: return skinny_dispatch<kEpiF32>(a, w, p, s);
     case kEpiBf16: return skinny_dispatch<kEpiBf16>(a, w, p, s);
@@ -527,9 +670,9 @@ int skinny_common(int kEpi, int M, int N, int K, const uint8_t* a, const uint8_t
 template <int kEpi>
 int run_many(const uint8_t* a, const uint8_t* w, GemmParams& p, cudaStream_t s) {
   constexpr int NB = 128, STAGES = 6;
-  using C = Cfg<NB, STAGES>;
-  auto kernel = umma_gemm_kernel<NB, STAGES, false, kEpi>;
-  if (int rc = ensure_smem<NB, STAGES, false, kEpi>()) return rc;
+  using C = Cfg<NB, STAGES, 1>;
+  auto kernel = umma_gemm_kernel<NB, STAGES, 1, false, kEpi>;
+  if (int rc = ensure_smem<NB, STAGES, 1, false, kEpi>()) return rc;
   CUtensorMap mp, mq;
   if (int rc = make_operand_map(&mp, a, p.M, p.K, 128)) return rc;
   if (int rc = make_operand_map(&mq, w, p.N, p.K, NB)) return rc;
@@ -549,6 +692,7 @@ int many_common(int kEpi, int M, int N, int K, const uint8_t* a, const uint8_t* 
   p.sf_p = a_sf, p.sf_q = w_sf, p.alpha.count = 1, p.alpha.alpha[0] = alpha, p.alpha_up = alpha_up;
   p.c = (c && beta != 0.f) ? c : nullptr, p.beta = beta, p.d = d;
   p.m_tiles = (M + 127) / 128, p.items = p.m_tiles * (N / 128);
+  p.trace = g_trace;
   switch (kEpi) {
     case kEpiF32: return run_many<kEpiF32>(a, w, p, s);
     case kEpiBf16: return run_many<kEpiBf16>(a, w, p, s);
@@ -609,7 +753,7 @@ int q27b_skinny_fp4_glu_bf16(int M, int I, int K, const uint8_t* a, const uint8_
 int64_t q27b_skinny_workspace_bytes(int M, int N, int K) {
   const int sms = sm_count();
   if (sms <= 0 || N <= 0 || K <= 0 || M <= 0) return -1;
-  return skinny_workspace_bytes(M, make_skinny_plan(N, K, sms).grid);
+  return kCounterBytes + skinny_workspace_bytes(M, make_skinny_plan(N, K, 2 * sms).grid);
 }
 
 int q27b_gemm_fp4(int M, int N, int K, const uint8_t* a, const uint8_t* a_sf, const uint8_t* b, const uint8_t* b_sf,
@@ -626,6 +770,8 @@ int q27b_gemm_fp4_glu_bf16(int M, int I, int K, const uint8_t* a, const uint8_t*
   return many_common(kEpiGluBf16, M, 2 * I, K, a, a_sf, gate_up, gate_up_sf, alpha_gate, alpha_up, nullptr, 0.f, d,
                      static_cast<cudaStream_t>(stream));
 }
+
+int q27b_trace_set(void* buf) { g_trace = static_cast<unsigned long long*>(buf); return 0; }
 
 // Reads and clears the device status word (0 = no bounded wait ran out since the last call). Synchronises.
 int q27b_device_status(uint32_t* status) {

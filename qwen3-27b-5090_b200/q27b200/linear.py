@@ -15,7 +15,7 @@ from . import layouts, weights
 from .q27lib import call, lib
 
 SKINNY_MAX_M = 128  # rows up to which the weight-streaming kernel is used (the reference: 64)
-WORKSPACE_BYTES = 32 << 20  # as the reference's shared skinny workspace (engine/src/model.h:462)
+WORKSPACE_BYTES = 48 << 20  # the reference shares 32 MiB (engine/src/model.h:462), enough here up to M = 64; M = 128 needs 38 MiB
 
 
 def _stream() -> int:
@@ -50,7 +50,8 @@ class Fp4Linear:
         self.out, self.inp, self.glu = out_features, in_features, glu
         self.alpha = self.in_scale * self.w_scale2  # engine/src/weights.cc:286
         dev = codes.device
-        self.ws = workspace if workspace is not None else torch.empty(WORKSPACE_BYTES, dtype=torch.uint8, device=dev)
+        # zeroed once: the head of the workspace holds arrival counters that the kernels leave at zero
+        self.ws = workspace if workspace is not None else torch.zeros(WORKSPACE_BYTES, dtype=torch.uint8, device=dev)
         self._act: ActQuant | None = None
         self._zero = (ctypes.c_int * 1)(0)
         self._alpha = (ctypes.c_float * 1)(self.alpha)

@@ -37,10 +37,16 @@ def swizzled_dev(sf):
     return buf
 
 
-def workspace(nbytes=32 << 20, poison=True):
+COUNTER_BYTES = 16384
+
+
+def workspace(nbytes=48 << 20, poison=True):
+    """A workspace as the caller must provide it: the arrival counters at its head zeroed once, the rest
+    arbitrary (poisoned with NaN bit patterns here: a partial tile read before it is written shows up)."""
     ws = torch.empty(nbytes, dtype=torch.uint8, device=DEV)
     if poison:
-        ws.fill_(0xFF)  # NaN partials: a slot read before it is written shows up in the result
+        ws.fill_(0xFF)
+    ws[:min(COUNTER_BYTES, nbytes)] = 0
     return ws
 
 

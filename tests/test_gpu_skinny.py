@@ -14,7 +14,7 @@ from q27b200 import layouts
 from q27b200.q27lib import call, lib
 
 pytestmark = pytest.mark.gpu
-WS = 32 << 20
+WS = 48 << 20
 
 _weights = {}
 

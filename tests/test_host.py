@@ -64,7 +64,7 @@ def plan(N, K, sms):
 
 @pytest.mark.parametrize("N,K", [(5120, 5120), (1024, 5120), (34816, 5120), (5120, 17408), (128, 5120), (128, 64),
                                  (384, 512), (248320, 5120), (640, 5120), (4352, 5120)])
-@pytest.mark.parametrize("sms", [148, 132, 7])
+@pytest.mark.parametrize("sms", [296, 148, 7])
 def test_skinny_plan_covers_every_unit_once(N, K, sms):
     grid, units, pieces = plan(N, K, sms)
     tiles, chunks = N // 128, (K + 255) // 256
@@ -72,8 +72,16 @@ def test_skinny_plan_covers_every_unit_once(N, K, sms):
     cover = np.zeros((tiles, chunks), dtype=np.int32)
     slots = set()
     sizes = []
+    l = lib()
     for g, segs in enumerate(pieces):
         sizes.append(sum(c1 - c0 for _, c0, c1, _ in segs))
+        first_unit = units * g // grid
+        # a cut tile at the end of the range is worked on first, everything else in ascending order
+        order = [t * chunks + c0 for t, c0, _, _ in segs]
+        if len(segs) > 1 and segs[0][3] == 2 * g + 1:
+            assert order[0] == max(order) and order[1:] == sorted(order[1:])
+        else:
+            assert order == sorted(order)
         for i, (t, c0, c1, slot) in enumerate(segs):
             assert 0 <= c0 < c1 <= chunks
             cover[t, c0:c1] += 1
@@ -81,9 +89,9 @@ def test_skinny_plan_covers_every_unit_once(N, K, sms):
             assert (slot == -1) == whole
             if not whole:
                 assert slot in (2 * g, 2 * g + 1) and slot not in slots  # at most two partial tiles per CTA
-                assert (slot == 2 * g) == (i == 0)
+                assert (slot == 2 * g) == (t * chunks + c0 == first_unit)
                 slots.add(slot)
-            # the owner lookup used by the fix-up kernel agrees with the split
+            # the owner lookup used when a cut tile is summed agrees with the split
             assert lib().q27b_skinny_unit_owner(N, K, sms, t * chunks + c0) == g
             assert lib().q27b_skinny_unit_owner(N, K, sms, t * chunks + c1 - 1) == g
     assert (cover == 1).all()

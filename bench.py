@@ -318,7 +318,7 @@ def main():
                    "timing": "CUDA-graph replay of the timed steps" if graph else "eager launches", "eager_ms_per_step": ms_eager / args.steps},
         "e2e": {"value": val(e2e_s), "unit": unit, "h2d_bytes_per_step": x.numel() * 2, "d2h_bytes_per_step": M * n_local * 2,
                 "ms_per_step": ms_e2e / args.steps},
-        "gpu_launches": args.steps * 2,
+        "gpu_launches": args.steps * 2,  # quantiser + GEMM
         "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
                      "traffic": NCU_TRAFFIC_BYTES.get(cfg.index) if world == 1 else None, "algorithmic_bytes": launch_bytes,
                      "kernel": "umma_gemm_kernel", "us_per_launch": gemm_s * 1e6, "peak_source": peak_src},

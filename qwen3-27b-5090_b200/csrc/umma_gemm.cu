@@ -230,6 +230,26 @@ __global__ void __launch_bounds__(kThreads, CTAS) umma_gemm_kernel(const __grid_
   volatile int* seg_info = reinterpret_cast<volatile int*>(xchg) + 8 * 64;  // [0] parts of a cut tile, [1..] their slots
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
 
+  const uint32_t smem_base = smem_u32(smem);
+  // Weights are read once (evict first); the activations are re-read by every CTA (keep them in L2).
+  const uint64_t hint_w = kEvictFirst, hint_a = kEvictLast;
+  const uint64_t hint_p = kSwap ? hint_w : hint_a, hint_q = kSwap ? hint_a : hint_w;
+  auto stage_bytes = [&](int c) { return uint32_t(C::kPBytes + C::kQBytes + 2 * min(4, p.ksteps - 4 * c) * 512); };
+  auto load_p = [&](const Chunks& k, int stage) {
+    const uint32_t sbase = smem_base + stage * C::kStageBytes, bar = full0 + 8 * stage;
+    tma_load_2d(sbase, &tmap_p, k.c * 128, k.w.p_row0, bar, hint_p);
+    bulk_load(sbase + C::kOffSfP, p.sf_p + (int64_t(k.w.p_row0 / 128) * p.ksteps + 4 * k.c) * 512,
+              min(4, p.ksteps - 4 * k.c) * 512, bar, hint_p);
+  };
+  auto load_q = [&](const Chunks& k, int stage) {
+    const uint32_t sbase = smem_base + stage * C::kStageBytes, bar = full0 + 8 * stage;
+    tma_load_2d(sbase + C::kOffQ, &tmap_q, k.c * 128, k.w.q_row0, bar, hint_q);
+    bulk_load(sbase + C::kOffSfQ, p.sf_q + (int64_t(k.w.q_row0 / 128) * p.ksteps + 4 * k.c) * 512,
+              min(4, p.ksteps - 4 * k.c) * 512, bar, hint_q);
+  };
+  uint32_t armed = 0;  // (producer lane) stages with a copy possibly in flight
+  int npre = 0;        // (producer lane) stages filled before the steady state
+
   if (threadIdx.x == 0) {
     TRACE(3, 0);
     prefetch_tensormap(&tmap_p);
@@ -238,6 +258,14 @@ __global__ void __launch_bounds__(kThreads, CTAS) umma_gemm_kernel(const __grid_
     for (int b = 0; b < 2; b++) mbar_init(afull0 + 8 * b, 1), mbar_init(aempty0 + 8 * b, 4);
     *abort_flag = 0;
     mbar_init_fence();
+    // The stream starts at once, while the rest of the CTA is still setting up: fill the ring with the operand
+    // that does not depend on the preceding kernel (the weights when streaming).
+    for (Chunks k(p); k.valid && npre < STAGES; k.advance(), npre++) {
+      mbar_arrive_expect_tx(full0 + 8 * npre, stage_bytes(k.c));
+      armed |= 1u << npre;
+      TRACE(0, npre);
+      if constexpr (kSwap) load_p(k, npre); else load_q(k, npre);
+    }
   }
   if (warp == 1) {
     tmem_alloc(smem_u32(tmem_holder), C::kTmemCols);
@@ -247,43 +275,13 @@ __global__ void __launch_bounds__(kThreads, CTAS) umma_gemm_kernel(const __grid_
   __syncthreads();
   tc_fence_after_sync();
   const uint32_t tmem_base = *tmem_holder;
-  const uint32_t smem_base = smem_u32(smem);
-  // Kernels queued behind this one may be scheduled from now on: they wait for this grid to finish before they
-  // touch anything it reads or writes, and start streaming their own weights into freed SMs meanwhile.
-  pdl_trigger();
 
   if (warp == 0) {
     // ------------------------------------------------------------------------------------------ TMA producer
     if (lane == 0) {
-      // Weights are read once (evict first); the activations are re-read by every CTA (keep them in L2).
-      const uint64_t hint_w = kEvictFirst, hint_a = kEvictLast;
-      const uint64_t hint_p = kSwap ? hint_w : hint_a, hint_q = kSwap ? hint_a : hint_w;
-      auto stage_bytes = [&](int c) { return uint32_t(C::kPBytes + C::kQBytes + 2 * min(4, p.ksteps - 4 * c) * 512); };
-      auto load_p = [&](const Chunks& k, int stage) {
-        const uint32_t sbase = smem_base + stage * C::kStageBytes, bar = full0 + 8 * stage;
-        tma_load_2d(sbase, &tmap_p, k.c * 128, k.w.p_row0, bar, hint_p);
-        bulk_load(sbase + C::kOffSfP, p.sf_p + (int64_t(k.w.p_row0 / 128) * p.ksteps + 4 * k.c) * 512,
-                  min(4, p.ksteps - 4 * k.c) * 512, bar, hint_p);
-      };
-      auto load_q = [&](const Chunks& k, int stage) {
-        const uint32_t sbase = smem_base + stage * C::kStageBytes, bar = full0 + 8 * stage;
-        tma_load_2d(sbase + C::kOffQ, &tmap_q, k.c * 128, k.w.q_row0, bar, hint_q);
-        bulk_load(sbase + C::kOffSfQ, p.sf_q + (int64_t(k.w.q_row0 / 128) * p.ksteps + 4 * k.c) * 512,
-                  min(4, p.ksteps - 4 * k.c) * 512, bar, hint_q);
-      };
-      // 1. Fill the ring with the operand that does not depend on the preceding kernel (the weights when
-      //    streaming), 2. wait for that kernel, 3. add the other operand, 4. steady state.
-      uint32_t armed = 0, last_parity = 0;  // stages with a copy possibly in flight / the phase they were armed for
-      int npre = 0;
-      {
-        Chunks k(p);
-        for (; k.valid && npre < STAGES; k.advance(), npre++) {
-          mbar_arrive_expect_tx(full0 + 8 * npre, stage_bytes(k.c));
-          armed |= 1u << npre;
-          TRACE(0, npre);
-          if constexpr (kSwap) load_p(k, npre); else load_q(k, npre);
-        }
-      }
+      // 1. (done above) the ring holds the first weights, 2. wait for the preceding kernel, 3. add the operand it
+      //    produced, 4. steady state.
+      uint32_t last_parity = 0;  // the phase each stage was last armed for
       pdl_wait();
       TRACE(3, 2);
       Chunks k(p);
@@ -306,6 +304,10 @@ __global__ void __launch_bounds__(kThreads, CTAS) umma_gemm_kernel(const __grid_
         load_q(k, stage);
         if (++stage == STAGES) stage = 0, phase ^= 1;
       }
+      // Everything this CTA reads from HBM has been requested: kernels queued behind this one may be scheduled
+      // (once every CTA says so). They wait for this grid to finish before touching what it reads or writes; what
+      // they may do at once, as SMs free up, is set up and pull their own weights into shared memory.
+      pdl_trigger();
       if (!ok) {
         // Unwinding: let every copy that was started land before the CTA gives its shared memory back.
         for (int s = 0; s < STAGES; s++)

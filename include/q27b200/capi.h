@@ -84,6 +84,19 @@ int q27b_skinny_fp4_bf16(int M, int N, int K, const uint8_t* a, const uint8_t* a
 int q27b_skinny_fp4_glu_bf16(int M, int I, int K, const uint8_t* a, const uint8_t* a_sf, const uint8_t* gate_up,
                              const uint8_t* gate_up_sf, float alpha_gate, float alpha_up, void* d, void* ws,
                              size_t ws_bytes, void* stream);
+/* q27b_skinny_fp4 for callers that cannot provide a workspace because they may not allocate device memory (a
+ * process whose memory plan is frozen, a plug-in inside one, code between stream capture calls): the scratch is a
+ * fixed array inside the library image, 7.8 MiB per GPU that loads the library, held until the process exits.
+ * Limit: 1 <= M <= 16 (decode / speculative-verify batches); a larger M is rejected with a message. Nothing is
+ * allocated or freed, here or in anything this calls. The FIRST call on each device looks the array's device
+ * address up and clears its counters (a synchronous memset), so make that first call before any stream capture.
+ * All calls share the one array and it keeps what the last call left: the kernels leave its counters at zero, the
+ * rest needs no clearing; two calls whose kernels overlap on the GPU (different streams) race on it — keep them
+ * in stream order. Results are bit-identical to q27b_skinny_fp4. It has no counterpart in the reference, whose
+ * callers always pass a workspace (engine/src/kernels.h:240-245). */
+int q27b_skinny_fp4_static(int M, int N, int K, const uint8_t* a, const uint8_t* a_sf, const uint8_t* w,
+                           const uint8_t* w_sf, int alpha_count, const int* alpha_begin, const float* alpha,
+                           const float* c, float beta, float* d, void* stream);
 /* Workspace bytes of the three calls above on the current device (-1 without a device). The reference sizes its
  * workspace at 32 MiB (engine/src/model.h:462), which covers every shape up to M = 64 on a 148-SM device; the
  * bound is 16 KiB + 4 * SMs * M * 512 bytes (38 MiB at M = 128). */
@@ -154,6 +167,8 @@ int q27t_skinny_fp4_glu_bf16(int M, int I, int K, const uint8_t* a, const uint8_
                              size_t ws_bytes);
 int q27t_ref_gemm_fp4(int M, int N, int K, const uint8_t* a, const uint8_t* a_sf, const uint8_t* b, const uint8_t* b_sf,
                       float alpha, float* d);
+int q27t_skinny_fp4_static(int M, int N, int K, const uint8_t* a, const uint8_t* a_sf, const uint8_t* w,
+                           const uint8_t* w_sf, float alpha, const float* c, float beta, float* d);
 /* Average microseconds of `iters` GEMMs cycling through `nbuf` weight copies (w_stride / sf_stride bytes apart) so
  * that weights never come from L2; `us` is a HOST pointer. Replaces q27t_bench_gemm (capi.cc:607-636). */
 int q27t_bench_gemm(int many, int M, int N, int K, const uint8_t* a, const uint8_t* a_sf, const uint8_t* w,

@@ -161,6 +161,13 @@ int q27t_skinny_fp4_glu_bf16(int M, int I, int K, const uint8_t* a, const uint8_
                                     test_stream());
   });
 }
+int q27t_skinny_fp4_static(int M, int N, int K, const uint8_t* a, const uint8_t* a_sf, const uint8_t* w,
+                           const uint8_t* w_sf, float alpha, const float* c, float beta, float* d) {
+  const int zero = 0;
+  return kernel([&] {
+    return q27b_skinny_fp4_static(M, N, K, a, a_sf, w, w_sf, 1, &zero, &alpha, c, beta, d, test_stream());
+  });
+}
 int q27t_ref_gemm_fp4(int M, int N, int K, const uint8_t* a, const uint8_t* a_sf, const uint8_t* b, const uint8_t* b_sf,
                       float alpha, float* d) {
   return kernel([&] { return q27b_ref_gemm_fp4(M, N, K, a, a_sf, b, b_sf, alpha, d, test_stream()); });

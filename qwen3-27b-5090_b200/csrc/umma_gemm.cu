@@ -775,6 +775,45 @@ int q27b_gemm_fp4_glu_bf16(int M, int I, int K, const uint8_t* a, const uint8_t*
 
 int q27b_trace_set(void* buf) { g_trace = static_cast<unsigned long long*>(buf); return 0; }
 
+// ---- the entry point that allocates nothing ---------------------------------------------------------------------
+//
+// Some callers of this library cannot hand over a workspace: code running where device allocation is forbidden or
+// already frozen (a serving process that planned all of its memory up front and has none left to give, a plug-in
+// loaded into such a process, a callback on a stream that is being captured). For them the scratch of the
+// weight-streaming GEMM lives in the library image itself.
+constexpr int kStaticMaxM = 16;  // decode and speculative-verify batches
+constexpr size_t kStaticScratchBytes = kCounterBytes + size_t(2) * kMaxParts * kStaticMaxM * 128 * 4;  // 7.8 MiB
+static __device__ __align__(256) uint8_t g_static_scratch[kStaticScratchBytes];
+
+// Device address of the array above on the current device; resolved (and the counters cleared) on the first call
+// per device. In host code the array's name is only a handle for cudaGetSymbolAddress, never a pointer to pass on.
+static int static_scratch(void** out) {
+  static void* ptr[64] = {};
+  int dev = 0;
+  Q27B_CUDA(cudaGetDevice(&dev));
+  Q27B_REQUIRE(dev >= 0 && dev < 64, "skinny_fp4_static: device index %d out of range", dev);
+  if (!ptr[dev]) {
+    void* p = nullptr;
+    Q27B_CUDA(cudaGetSymbolAddress(&p, g_static_scratch));
+    Q27B_CUDA(cudaMemset(p, 0, kCounterBytes));  // (a module's globals start at zero; this also covers a reload)
+    ptr[dev] = p;
+  }
+  *out = ptr[dev];
+  return 0;
+}
+
+int q27b_skinny_fp4_static(int M, int N, int K, const uint8_t* a, const uint8_t* a_sf, const uint8_t* w,
+                           const uint8_t* w_sf, int alpha_count, const int* alpha_begin, const float* alpha,
+                           const float* c, float beta, float* d, void* stream) {
+  Q27B_REQUIRE(M >= 1 && M <= kStaticMaxM, "skinny_fp4_static: M must be 1..%d (M = %d); larger batches need q27b_skinny_fp4 "
+               "with a caller-provided workspace", kStaticMaxM, M);
+  Q27B_REQUIRE(alpha_count >= 1 && alpha_count <= 4 && alpha_begin && alpha, "skinny_fp4_static: 1..4 alpha segments");
+  void* ws = nullptr;
+  if (int rc = static_scratch(&ws)) return rc;
+  return skinny_common(kEpiF32, M, N, K, a, a_sf, w, w_sf, make_alpha(alpha_count, alpha_begin, alpha), 1.f,
+                       (c && beta != 0.f) ? c : nullptr, beta, d, ws, kStaticScratchBytes, static_cast<cudaStream_t>(stream));
+}
+
 // Reads and clears the device status word (0 = no bounded wait ran out since the last call). Synchronises.
 int q27b_device_status(uint32_t* status) {
   Q27B_REQUIRE(status, "device_status: null pointer");

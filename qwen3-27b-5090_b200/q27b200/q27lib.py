@@ -30,6 +30,7 @@ SIGNATURES = {
     "q27b_skinny_fp4": ([I, I, I, P, P, P, P, I, P, P, P, F, P, P, SZ, P], I),
     "q27b_skinny_fp4_bf16": ([I, I, I, P, P, P, P, I, P, P, P, P, SZ, P], I),
     "q27b_skinny_fp4_glu_bf16": ([I, I, I, P, P, P, P, F, F, P, P, SZ, P], I),
+    "q27b_skinny_fp4_static": ([I, I, I, P, P, P, P, I, P, P, P, F, P, P], I),
     "q27b_skinny_workspace_bytes": ([I, I, I], I64),
     "q27b_gemm_fp4": ([I, I, I, P, P, P, P, F, P, F, P, P], I),
     "q27b_gemm_fp4_bf16": ([I, I, I, P, P, P, P, F, P, P], I),
@@ -56,6 +57,7 @@ SIGNATURES = {
     "q27t_skinny_fp4_bf16": ([I, I, I, P, P, P, P, F, P, P, SZ], I),
     "q27t_skinny_fp4_glu_bf16": ([I, I, I, P, P, P, P, F, F, P, P, SZ], I),
     "q27t_ref_gemm_fp4": ([I, I, I, P, P, P, P, F, P], I),
+    "q27t_skinny_fp4_static": ([I, I, I, P, P, P, P, F, P, F, P], I),
     "q27t_bench_gemm": ([I, I, I, I, P, P, P, P, I64, I64, I, I, P, P, SZ, P], I),
 }
 

@@ -208,12 +208,14 @@ int q27t_bench_gemm(int many, int M, int N, int K, const uint8_t* a, const uint8
 }
 
 // CPU-testable view of the weight-streaming work split: fills seg[4 * i .. 4 * i + 3] = {tile, c0, c1, slot} for the
-// pieces of CTA `cta` (at most `cap`), returns their count; grid_out / units_out describe the plan.
-int q27b_skinny_plan(int N, int K, int sms, int cta, int* seg, int cap, int* grid_out, int64_t* units_out) {
-  if (N <= 0 || N % 128 || K <= 0 || K % 64 || sms <= 0) return fail("skinny_plan: bad shape");
-  const SkinnyPlan p = make_skinny_plan(N, K, sms);
+// pieces of CTA `cta` (at most `cap`), returns their count; grid_out / units_out / split_out describe the plan.
+int q27b_skinny_plan(int N, int K, int slots, int cta, int* seg, int cap, int* grid_out, int64_t* units_out,
+                     int* split_out) {
+  if (N <= 0 || N % 128 || K <= 0 || K % 64 || slots <= 0) return fail("skinny_plan: bad shape");
+  const SkinnyPlan p = choose_skinny_plan(N, K, slots);
   if (grid_out) *grid_out = p.grid;
   if (units_out) *units_out = p.units;
+  if (split_out) *split_out = p.split;
   if (cta < 0 || cta >= p.grid) return 0;
   int64_t u = -1;
   Segment s;
@@ -224,9 +226,12 @@ int q27b_skinny_plan(int N, int K, int sms, int cta, int* seg, int cap, int* gri
   }
   return n;
 }
-int q27b_skinny_unit_owner(int N, int K, int sms, int64_t unit) {
-  const SkinnyPlan p = make_skinny_plan(N, K, sms);
-  return unit_owner(p, unit);
+// The partial-tile slots tile `tile` is summed from, in order (at most `cap`); returns their number (1: not cut).
+int q27b_skinny_tile_parts(int N, int K, int slots, int tile, int* slot, int cap) {
+  const SkinnyPlan p = choose_skinny_plan(N, K, slots);
+  const TileParts t = tile_parts(p, tile);
+  for (int i = 0; i < t.n && i < cap; i++) slot[i] = t.n == 1 ? -1 : part_slot(p, t, i);
+  return t.n;
 }
 
 }  // extern "C"

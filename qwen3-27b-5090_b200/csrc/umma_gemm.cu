@@ -5,9 +5,10 @@
 //  * weight streaming (1 <= M <= 128, "skinny"): the roles of the operands are swapped — a 128-row weight tile is
 //    the MMA's M side, the (padded) tokens are its N side — so one instruction consumes 4 KiB of weights whatever
 //    the token count, and the kernel is bound by HBM. The K range of the whole weight matrix is cut into
-//    equal contiguous unit ranges, one per SM (layout.h); a tile cut by a range boundary is finished by whichever
-//    of its CTAs arrives last, which sums the partial tiles in ascending K order whatever the order of arrival
-//    (deterministic, independent of M; no CTA ever waits for another).
+//    equal contiguous unit ranges (layout.h: two per SM up to M = 64, one above); a tile cut by a range boundary
+//    is finished by whichever of its CTAs arrives last, which sums the partial tiles in ascending K order whatever
+//    the order of arrival, or above 32 tokens by a small fix-up kernel doing the same sums on the whole GPU
+//    (deterministic; independent of M up to 64; no CTA ever waits for another).
 //  * many rows (prefill): 128 tokens x 128 output channels per tile, tiles walked token-tile fastest so that the
 //    CTAs running together share weight tiles through L2; accumulators double-buffered in tensor memory so the
 //    epilogue of one tile overlaps the MMAs of the next.
@@ -57,6 +58,7 @@ struct GemmParams {
   float* partials;      // weight streaming: per-CTA partial tiles [2 * grid][M][128]
   SkinnyPlan plan;      // weight streaming
   int m_tiles, items;   // many rows
+  int ext_reduce;       // weight streaming: cut tiles are summed by skinny_fixup_kernel, not by the last CTA to arrive
   unsigned long long* trace;  // optional [cta][4][64] globaltimer samples (null: off)
 };
 
@@ -78,7 +80,7 @@ struct Cfg {
   static constexpr int kSmemBytes = STAGES * kStageBytes + kXchgBytes + kBarBytes + 1024;  // + alignment slack
   static constexpr int kTmemCols = 512 / CTAS;
   static constexpr int kSfCol0 = 2 * NB;  // accumulators: columns [0, 2 NB); scales: 32 columns per stage from here
-  static constexpr int kRangesPerCta = 2 / CTAS;  // unit ranges of the (always 2-per-SM) work split per CTA
+  static constexpr int kRangesPerCta = 1;  // unit ranges of the work split per CTA
   static_assert(kStageBytes % 1024 == 0, "stage tiles must stay 1024-byte aligned");
   static_assert(kSfCol0 + 32 * STAGES <= kTmemCols, "tensor memory budget");
   static_assert(CTAS * (kSmemBytes + 1024) <= 228 * 1024, "shared memory budget");
@@ -91,9 +93,8 @@ struct Work {
   int tile;
 };
 
-// The pieces of work of this CTA, in the order every role walks them. Weight streaming: the work split always has
-// two unit ranges per SM (so that results do not depend on which configuration runs); a CTA takes kRanges
-// consecutive ranges.
+// The pieces of work of this CTA, in the order every role walks them. Weight streaming: a CTA takes kRanges
+// consecutive unit ranges of the work split.
 template <bool kSwap, int kRanges>
 struct WorkIter {
   const GemmParams& p;
@@ -402,12 +403,10 @@ __global__ void __launch_bounds__(kThreads, CTAS) umma_gemm_kernel(const __grid_
     for (int i = 0; it.next(w); i++) {
       const int buf = i & 1;
       if constexpr (kSwap) {
-        if (w.slot >= 0 && threadIdx.x == 64) {  // which ranges share this cut tile, and where their partial tiles are
-          const int64_t ubeg = int64_t(w.tile) * p.plan.chunks;
-          const int g0 = unit_owner(p.plan, ubeg), g1 = unit_owner(p.plan, ubeg + p.plan.chunks - 1);
-          seg_info[0] = g1 - g0 + 1;
-          for (int g = g0; g <= g1 && g - g0 < kMaxParts; g++)
-            seg_info[1 + g - g0] = 2 * g + (unit_begin(p.plan, g) >= ubeg ? 0 : 1);
+        if (w.slot >= 0 && !p.ext_reduce && threadIdx.x == 64) {  // the partial tiles this cut tile is summed from
+          const TileParts t = tile_parts(p.plan, w.tile);
+          seg_info[0] = t.n;
+          for (int q = 0; q < t.n && q < kMaxParts; q++) seg_info[1 + q] = part_slot(p.plan, t, q);
         }
       }
       if (!warp_wait(afull0 + 8 * buf, (i >> 1) & 1, abort_flag, &g_status, kStatusAccumWaitTimeout, 128)) break;
@@ -441,6 +440,7 @@ __global__ void __launch_bounds__(kThreads, CTAS) umma_gemm_kernel(const __grid_
           tc_fence_before_sync();
           __syncwarp();
           if (lane == 0) mbar_arrive(aempty0 + 8 * buf);
+          if (p.ext_reduce) continue;  // (uniform) a separate kernel sums the partial tiles: many tokens
           epi_bar();  // every partial of this CTA is written (and seg_info is visible) ...
           if (threadIdx.x == 64) {
             __threadfence();  // ... and published device-wide before the arrival is counted
@@ -550,6 +550,53 @@ __global__ void __launch_bounds__(kThreads, CTAS) umma_gemm_kernel(const __grid_
   }
 }
 
+// Sums the partial tiles of every cut weight tile in ascending K order and applies the epilogue: the same
+// arithmetic as the in-kernel reduction, spread over the whole GPU. Used when there are many tokens (the in-kernel
+// reduction leaves a cut tile to the one CTA that arrives last). Block = (tile, group of 8 tokens), thread = row.
+template <int kEpi>
+__global__ void __launch_bounds__(128) skinny_fixup_kernel(const __grid_constant__ GemmParams p) {
+  pdl_trigger();
+  const int tile = blockIdx.x, row = threadIdx.x;
+  const TileParts t = tile_parts(p.plan, tile);
+  if (t.n == 1) return;  // finished in place by its only owner
+  __shared__ float xchg[8 * 64];
+  const int m0 = blockIdx.y * 8;
+  pdl_wait();
+  float v[8];
+  for (int q = 0; q < t.n; q++) {
+    const float* part = p.partials + (int64_t(part_slot(p.plan, t, q)) * p.M + m0) * 128 + row;
+#pragma unroll
+    for (int j = 0; j < 8; j++)
+      if (m0 + j < p.M) v[j] = q == 0 ? __ldcg(part + j * 128) : __fadd_rn(v[j], __ldcg(part + j * 128));
+  }
+  if constexpr (kEpi == kEpiGluBf16) {
+    if (row >= 64) {
+#pragma unroll
+      for (int j = 0; j < 8; j++) xchg[j * 64 + row - 64] = v[j];
+    }
+    __syncthreads();
+    if (row < 64) {
+      const float ag = p.alpha.alpha[0], au = p.alpha_up;
+      uint16_t* d = static_cast<uint16_t*>(p.d) + int64_t(tile) * 64 + row;
+#pragma unroll
+      for (int j = 0; j < 8; j++)
+        if (m0 + j < p.M)
+          d[int64_t(m0 + j) * (p.N / 2)] = bf16_bits(silu_mul(__fmul_rn(ag, v[j]), __fmul_rn(au, xchg[j * 64 + row])));
+    }
+  } else {
+    const int n = tile * 128 + row;
+#pragma unroll
+    for (int j = 0; j < 8; j++) {
+      const int m = m0 + j;
+      if (m < p.M) {
+        const float out = finish_f32(p, v[j], m, n);
+        if constexpr (kEpi == kEpiF32) static_cast<float*>(p.d)[int64_t(m) * p.N + n] = out;
+        else static_cast<uint16_t*>(p.d)[int64_t(m) * p.N + n] = bf16_bits(out);
+      }
+    }
+  }
+}
+
 // ------------------------------------------------------------------------------------------------ host side
 
 using EncodeTiledFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
@@ -620,7 +667,17 @@ int run_skinny(const uint8_t* a, const uint8_t* w, GemmParams& p, cudaStream_t s
   if (int rc = make_operand_map(&mp, w, p.N, p.K, 128)) return rc;
   if (int rc = make_operand_map(&mq, a, p.M, p.K, NB)) return rc;
   const int grid = (p.plan.grid + C::kRangesPerCta - 1) / C::kRangesPerCta;
-  return launch_gemm(kernel, grid, C::kSmemBytes, s, mp, mq, p, true);
+  if (int rc = launch_gemm(kernel, grid, C::kSmemBytes, s, mp, mq, p, true)) return rc;
+  if (p.ext_reduce) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(p.plan.tiles, (p.M + 7) / 8), cfg.blockDim = dim3(128), cfg.stream = s;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr, cfg.numAttrs = 1;
+    Q27B_CUDA(cudaLaunchKernelEx(&cfg, skinny_fixup_kernel<kEpi>, p));
+  }
+  return 0;
 }
 
 template <int kEpi>
@@ -653,10 +710,13 @@ int skinny_common(int kEpi, int M, int N, int K, const uint8_t* a, const uint8_t
   GemmParams p = {};
   p.M = M, p.N = N, p.K = K, p.ksteps = K / 64, p.chunks = (p.ksteps + 3) / 4;
   p.sf_p = w_sf, p.sf_q = a_sf, p.alpha = alpha, p.alpha_up = alpha_up, p.c = c, p.beta = beta, p.d = d;
-  p.plan = make_skinny_plan(N, K, 2 * sms);  // two unit ranges per SM, whatever the token count
-  Q27B_REQUIRE(p.plan.grid <= kMaxParts, "skinny_fp4: more than %d unit ranges", kMaxParts);
+  // Two CTA slots per SM for every M up to 64 (a token's result is the same whatever M <= 64 it is computed
+  // with, the reference's invariant for its M <= 64 path); one per SM above, where partial tiles are large.
+  p.plan = choose_skinny_plan(N, K, M <= 64 ? 2 * sms : sms);
+  p.ext_reduce = plan_cuts_tiles(p.plan) && M > 32;
+  Q27B_REQUIRE(p.plan.grid <= kMaxParts, "skinny_fp4: more than %d CTAs", kMaxParts);
   Q27B_REQUIRE(p.plan.tiles * 4 <= kCounterBytes, "skinny_fp4: N too large (%d rows, at most %d)", N, kCounterBytes / 4 * 128);
-  const size_t need = size_t(kCounterBytes + skinny_workspace_bytes(M, p.plan.grid));
+  const size_t need = size_t(kCounterBytes + skinny_workspace_bytes(M, p.plan));
   Q27B_REQUIRE(ws && aligned16(ws) && ws_bytes >= need, "skinny_fp4: workspace too small (%zu bytes, need %zu)", ws_bytes,
                need);
   p.counters = static_cast<int*>(ws);
@@ -755,7 +815,7 @@ int q27b_skinny_fp4_glu_bf16(int M, int I, int K, const uint8_t* a, const uint8_
 int64_t q27b_skinny_workspace_bytes(int M, int N, int K) {
   const int sms = sm_count();
   if (sms <= 0 || N <= 0 || K <= 0 || M <= 0) return -1;
-  return kCounterBytes + skinny_workspace_bytes(M, make_skinny_plan(N, K, 2 * sms).grid);
+  return kCounterBytes + skinny_workspace_bytes(M, choose_skinny_plan(N, K, M <= 64 ? 2 * sms : sms));
 }
 
 int q27b_gemm_fp4(int M, int N, int K, const uint8_t* a, const uint8_t* a_sf, const uint8_t* b, const uint8_t* b_sf,

@@ -15,7 +15,7 @@ from . import layouts, weights
 from .q27lib import call, lib
 
 SKINNY_MAX_M = 128  # rows up to which the weight-streaming kernel is used (the reference: 64)
-WORKSPACE_BYTES = 48 << 20  # the reference shares 32 MiB (engine/src/model.h:462), enough here up to M = 64; M = 128 needs 38 MiB
+WORKSPACE_BYTES = 32 << 20  # as the reference's shared skinny workspace (engine/src/model.h:462)
 
 
 def _stream() -> int:

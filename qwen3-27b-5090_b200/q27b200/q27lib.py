@@ -37,8 +37,8 @@ SIGNATURES = {
     "q27b_gemm_fp4_glu_bf16": ([I, I, I, P, P, P, P, F, F, P, P], I),
     "q27b_device_status": ([U32P], I),
     "q27b_ref_gemm_fp4": ([I, I, I, P, P, P, P, F, P, P], I),
-    "q27b_skinny_plan": ([I, I, I, I, P, I, P, P], I),
-    "q27b_skinny_unit_owner": ([I, I, I, I64], I),
+    "q27b_skinny_plan": ([I, I, I, I, P, I, P, P, P], I),
+    "q27b_skinny_tile_parts": ([I, I, I, I, P, I], I),
     "q27t_last_us": ([], F),
     "q27t_sf_bytes": ([I64, I64], I64),
     "q27t_quant_fp4": ([P, I, I, F, P, P], I),

@@ -49,59 +49,74 @@ def test_sf_layout_matches_oracle():
     assert np.array_equal(layouts.glu_rows(384), O.glu_rows(384))
 
 
-def plan(N, K, sms):
+def plan(N, K, slots):
     l = lib()
-    grid, units = ctypes.c_int(), ctypes.c_int64()
+    grid, units, split = ctypes.c_int(), ctypes.c_int64(), ctypes.c_int()
     seg = (ctypes.c_int * (4 * 2048))()
-    l.q27b_skinny_plan(N, K, sms, -1, None, 0, ctypes.byref(grid), ctypes.byref(units))
+    l.q27b_skinny_plan(N, K, slots, -1, None, 0, ctypes.byref(grid), ctypes.byref(units), ctypes.byref(split))
     pieces = []
     for g in range(grid.value):
-        n = l.q27b_skinny_plan(N, K, sms, g, seg, 2048, None, None)
+        n = l.q27b_skinny_plan(N, K, slots, g, seg, 2048, None, None, None)
         assert 1 <= n <= 2048
         pieces.append([tuple(seg[4 * i:4 * i + 4]) for i in range(n)])
-    return grid.value, units.value, pieces
+    return grid.value, units.value, split.value, pieces
 
 
 @pytest.mark.parametrize("N,K", [(5120, 5120), (1024, 5120), (34816, 5120), (5120, 17408), (128, 5120), (128, 64),
-                                 (384, 512), (248320, 5120), (640, 5120), (4352, 5120)])
-@pytest.mark.parametrize("sms", [296, 148, 7])
-def test_skinny_plan_covers_every_unit_once(N, K, sms):
-    grid, units, pieces = plan(N, K, sms)
+                                 (384, 512), (248320, 5120), (640, 5120), (4352, 5120), (128, 65536)])
+@pytest.mark.parametrize("slots", [296, 148, 7])
+def test_skinny_plan_covers_every_unit_once(N, K, slots):
+    grid, units, split, pieces = plan(N, K, slots)
     tiles, chunks = N // 128, (K + 255) // 256
-    assert units == tiles * chunks and grid == min(sms, units)
+    assert units == tiles * chunks and 1 <= grid <= min(slots, units)
     cover = np.zeros((tiles, chunks), dtype=np.int32)
-    slots = set()
+    slot_of = {}
     sizes = []
     l = lib()
     for g, segs in enumerate(pieces):
         sizes.append(sum(c1 - c0 for _, c0, c1, _ in segs))
-        first_unit = units * g // grid
-        # a cut tile at the end of the range is worked on first, everything else in ascending order
-        order = [t * chunks + c0 for t, c0, _, _ in segs]
-        if len(segs) > 1 and segs[0][3] == 2 * g + 1:
-            assert order[0] == max(order) and order[1:] == sorted(order[1:])
-        else:
-            assert order == sorted(order)
-        for i, (t, c0, c1, slot) in enumerate(segs):
+        for t, c0, c1, slot in segs:
             assert 0 <= c0 < c1 <= chunks
             cover[t, c0:c1] += 1
             whole = c0 == 0 and c1 == chunks
             assert (slot == -1) == whole
             if not whole:
-                assert slot in (2 * g, 2 * g + 1) and slot not in slots  # at most two partial tiles per CTA
-                assert (slot == 2 * g) == (t * chunks + c0 == first_unit)
-                slots.add(slot)
-            # the owner lookup used when a cut tile is summed agrees with the split
-            assert lib().q27b_skinny_unit_owner(N, K, sms, t * chunks + c0) == g
-            assert lib().q27b_skinny_unit_owner(N, K, sms, t * chunks + c1 - 1) == g
+                assert slot >= 0 and slot not in slot_of  # every partial tile has a slot of its own
+                slot_of[slot] = (t, c0)
+        if split == 0:  # ranges: a cut tile at the end of the range is worked on first, the rest in ascending order
+            order = [t * chunks + c0 for t, c0, _, _ in segs]
+            if len(segs) > 1 and order[0] == max(order):
+                assert order[1:] == sorted(order[1:])
+            else:
+                assert order == sorted(order)
+            assert len([1 for seg in segs if seg[3] >= 0]) <= 2  # at most two partial tiles per CTA
     assert (cover == 1).all()
-    assert max(sizes) - min(sizes) <= 1  # every SM streams the same number of bytes (+- one unit)
+    if split == 0:
+        assert max(sizes) - min(sizes) <= 1  # every CTA streams the same number of bytes (+- one unit)
+    # the lookup used when a cut tile is summed lists exactly that tile's partial tiles, in ascending K order
+    buf = (ctypes.c_int * 2048)()
+    for t in sorted({0, tiles // 2, tiles - 1}):
+        n = l.q27b_skinny_tile_parts(N, K, slots, t, buf, 2048)
+        parts = [slot_of[buf[i]] for i in range(n)] if n > 1 else []
+        assert all(pt == t for pt, _ in parts) and [c for _, c in parts] == sorted(c for _, c in parts)
+        assert n == max(1, sum(1 for pt, _ in slot_of.values() if pt == t))
+    need = max(slot_of) + 1 if slot_of else 0
+    assert need <= 2 * slots  # partial tiles fit the workspace bound stated in the header
+
+
+def test_skinny_plan_choices():
+    """The cost model's picks for the benchmark shapes on a 148-SM device (two CTA slots per SM)."""
+    assert plan(34816, 5120, 296)[2] == 1      # gate | up: one whole tile per CTA, nothing is cut
+    assert plan(5120, 5120, 296)[2] == 7       # q / o: seven aligned K-parts per tile
+    assert plan(5120, 17408, 148)[2] == 0      # down at many tokens: contiguous ranges
+    assert plan(248320, 5120, 296)[2] == 0     # lm_head: contiguous ranges (no wave quantisation)
 
 
 def test_plan_is_independent_of_m():
     # the split takes no M argument at all: rows cannot depend on the number of tokens
     import inspect
     assert "M" not in [a for a in inspect.signature(plan).parameters]
+    assert plan(5120, 17408, 296)[:3] == plan(5120, 17408, 296)[:3]
 
 
 def test_weight_quantiser_matches_oracle(golden):

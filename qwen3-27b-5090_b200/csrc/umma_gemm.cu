@@ -65,7 +65,7 @@ struct GemmParams {
 // CTAS = CTAs of this configuration that fit on one SM (2: half the shared and tensor memory each, so that the
 // epilogue of one CTA overlaps the stream of the other and a CTA of the next launch can move in as soon as one of
 // this launch leaves).
-template <int NB, int STAGES, int CTAS>
+template <int NB, int STAGES, int CTAS, bool SWAP>
 struct Cfg {
   static_assert(NB % 16 == 0 && NB >= 16 && NB <= 128, "N-side tile: 16..128 rows");
   static_assert(CTAS == 1 || CTAS == 2, "one or two CTAs per SM");
@@ -74,12 +74,15 @@ struct Cfg {
   static constexpr int kSfBytes = 4 * 512;   // 4 MMA steps x one 512-byte atom
   static constexpr int kStageBytes = kPBytes + kQBytes + 2 * kSfBytes;
   static constexpr int kOffQ = kPBytes, kOffSfP = kPBytes + kQBytes, kOffSfQ = kOffSfP + kSfBytes;
-  static constexpr int kXchgBytes = 8 * 64 * 4 + 2048;  // SiLU*mul exchange between the gate and the up warps + cut-tile info
+  static constexpr int kXchgBytes = SWAP ? 8 * 64 * 4 + 2048 : 0;  // SiLU*mul exchange between the gate and the up warps + cut-tile info
   static constexpr int kNumBars = 3 * STAGES + 4;
   static constexpr int kBarBytes = kNumBars * 8 + 16;
   static constexpr int kSmemBytes = STAGES * kStageBytes + kXchgBytes + kBarBytes + 1024;  // + alignment slack
   static constexpr int kTmemCols = 512 / CTAS;
-  static constexpr int kSfCol0 = 2 * NB;  // accumulators: columns [0, 2 NB); scales: 32 columns per stage from here
+  // accumulators: two buffers when tensor memory allows (the epilogue of one piece overlaps the MMAs of the next),
+  // else one (two CTAs per SM overlap each other instead); scales: 32 columns per stage after them
+  static constexpr int kAccBufs = 2 * NB + 32 * STAGES <= kTmemCols ? 2 : 1;
+  static constexpr int kSfCol0 = kAccBufs * NB;
   static constexpr int kRangesPerCta = 1;  // unit ranges of the work split per CTA
   static_assert(kStageBytes % 1024 == 0, "stage tiles must stay 1024-byte aligned");
   static_assert(kSfCol0 + 32 * STAGES <= kTmemCols, "tensor memory budget");
@@ -216,7 +219,7 @@ template <int NB, int STAGES, int CTAS, bool kSwap, int kEpi>
 __global__ void __launch_bounds__(kThreads, CTAS) umma_gemm_kernel(const __grid_constant__ CUtensorMap tmap_p,
                                                                 const __grid_constant__ CUtensorMap tmap_q,
                                                                 const __grid_constant__ GemmParams p) {
-  using C = Cfg<NB, STAGES, CTAS>;
+  using C = Cfg<NB, STAGES, CTAS, kSwap>;
   using Chunks = ChunkIter<kSwap, C::kRangesPerCta>;
   using Works = WorkIter<kSwap, C::kRangesPerCta>;
   extern __shared__ uint8_t smem_raw[];
@@ -333,8 +336,8 @@ __global__ void __launch_bounds__(kThreads, CTAS) umma_gemm_kernel(const __grid_
       uint32_t phase = 0;
       bool ok = true;
       for (int i = 0; ok && it.next(w); i++) {
-        const int buf = i & 1;
-        if (!mbar_wait_bounded(aempty0 + 8 * buf, ((i >> 1) & 1) ^ 1, abort_flag, &g_status, kStatusAccumFreeTimeout))
+        const int buf = i % C::kAccBufs, use = i / C::kAccBufs;
+        if (!mbar_wait_bounded(aempty0 + 8 * buf, (use & 1) ^ 1, abort_flag, &g_status, kStatusAccumFreeTimeout))
           break;
         tc_fence_after_sync();
         const uint32_t d_tmem = tmem_base + buf * NB;
@@ -366,8 +369,9 @@ __global__ void __launch_bounds__(kThreads, CTAS) umma_gemm_kernel(const __grid_
         nseg = i + 1;
       }
       // Tensor memory is freed by this warp: not before the epilogue has read the last accumulators.
-      for (int j = nseg - 1; ok && j >= 0 && j >= nseg - 2; j--)
-        ok = mbar_wait_bounded(aempty0 + 8 * (j & 1), (j >> 1) & 1, abort_flag, &g_status, kStatusAccumFreeTimeout, 64);
+      for (int j = nseg - 1; ok && j >= 0 && j >= nseg - C::kAccBufs; j--)
+        ok = mbar_wait_bounded(aempty0 + 8 * (j % C::kAccBufs), (j / C::kAccBufs) & 1, abort_flag, &g_status,
+                               kStatusAccumFreeTimeout, 64);
     }
   } else if (warp >= 6) {
     // ------------------------------------------------------------------------------------------ scale feeders
@@ -401,7 +405,7 @@ __global__ void __launch_bounds__(kThreads, CTAS) umma_gemm_kernel(const __grid_
     Works it(p);
     Work w;
     for (int i = 0; it.next(w); i++) {
-      const int buf = i & 1;
+      const int buf = i % C::kAccBufs;
       if constexpr (kSwap) {
         if (w.slot >= 0 && !p.ext_reduce && threadIdx.x == 64) {  // the partial tiles this cut tile is summed from
           const TileParts t = tile_parts(p.plan, w.tile);
@@ -409,7 +413,7 @@ __global__ void __launch_bounds__(kThreads, CTAS) umma_gemm_kernel(const __grid_
           for (int q = 0; q < t.n && q < kMaxParts; q++) seg_info[1 + q] = part_slot(p.plan, t, q);
         }
       }
-      if (!warp_wait(afull0 + 8 * buf, (i >> 1) & 1, abort_flag, &g_status, kStatusAccumWaitTimeout, 128)) break;
+      if (!warp_wait(afull0 + 8 * buf, (i / C::kAccBufs) & 1, abort_flag, &g_status, kStatusAccumWaitTimeout, 128)) break;
       tc_fence_after_sync();
       if (threadIdx.x == 64) TRACE(3, 4 + i);
       const uint32_t taddr = tmem_base + (uint32_t(quarter * 32) << 16) + buf * NB;
@@ -653,14 +657,14 @@ int ensure_smem() {
   Q27B_CUDA(cudaGetDevice(&dev));
   if (dev < 64 && done[dev]) return 0;
   Q27B_CUDA(cudaFuncSetAttribute(umma_gemm_kernel<NB, STAGES, CTAS, kSwap, kEpi>,
-                                 cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg<NB, STAGES, CTAS>::kSmemBytes));
+                                 cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg<NB, STAGES, CTAS, kSwap>::kSmemBytes));
   if (dev < 64) done[dev] = true;
   return 0;
 }
 
 template <int NB, int STAGES, int CTAS, int kEpi>
 int run_skinny(const uint8_t* a, const uint8_t* w, GemmParams& p, cudaStream_t s) {
-  using C = Cfg<NB, STAGES, CTAS>;
+  using C = Cfg<NB, STAGES, CTAS, true>;
   auto kernel = umma_gemm_kernel<NB, STAGES, CTAS, true, kEpi>;
   if (int rc = ensure_smem<NB, STAGES, CTAS, true, kEpi>()) return rc;
   CUtensorMap mp, mq;
@@ -731,15 +735,17 @@ int skinny_common(int kEpi, int M, int N, int K, const uint8_t* a, const uint8_t
 
 template <int kEpi>
 int run_many(const uint8_t* a, const uint8_t* w, GemmParams& p, cudaStream_t s) {
-  constexpr int NB = 128, STAGES = 6;
-  using C = Cfg<NB, STAGES, 1>;
-  auto kernel = umma_gemm_kernel<NB, STAGES, 1, false, kEpi>;
-  if (int rc = ensure_smem<NB, STAGES, 1, false, kEpi>()) return rc;
+  // Two CTAs per SM: one thread issues an MMA of this shape only every ~140 cycles while the tensor pipe needs 64
+  // for it, so two issuers keep it busier, and the epilogue of one CTA overlaps the MMAs of the other.
+  constexpr int NB = 128, STAGES = 3, CTAS = 2;
+  using C = Cfg<NB, STAGES, CTAS, false>;
+  auto kernel = umma_gemm_kernel<NB, STAGES, CTAS, false, kEpi>;
+  if (int rc = ensure_smem<NB, STAGES, CTAS, false, kEpi>()) return rc;
   CUtensorMap mp, mq;
   if (int rc = make_operand_map(&mp, a, p.M, p.K, 128)) return rc;
   if (int rc = make_operand_map(&mq, w, p.N, p.K, NB)) return rc;
-  const int sms = sm_count();
-  return launch_gemm(kernel, p.items < sms ? p.items : sms, C::kSmemBytes, s, mp, mq, p, true);
+  const int slots = CTAS * sm_count();
+  return launch_gemm(kernel, p.items < slots ? p.items : slots, C::kSmemBytes, s, mp, mq, p, true);
 }
 
 int many_common(int kEpi, int M, int N, int K, const uint8_t* a, const uint8_t* a_sf, const uint8_t* w,

@@ -201,13 +201,96 @@ def cpu_reference(cfg, steps, warmup, frac_rows=4):
     return sample_bytes / dt / 1e9, dt, cores, desc
 
 
+def sweep_main(args, rank, world, local_rank):
+    """Configuration 3: the whole-model decode weight sweep. 64 layers x {q, k, v, o, gate_up, down}, every
+    projection in its own device memory (11.9 GB in total, far beyond L2; the contents of one quantised layer are
+    repeated), N-sharded over the ranks; per layer the kernels a model step would launch: quantise the hidden
+    state, q / k / v on it, quantise, o, quantise, gate | up with SiLU*mul, quantise, down. One "step" = the sweep
+    at one M; timed as a CUDA-graph replay; value = algorithmic bytes of the sweep / time."""
+    from q27b200 import configs, shard, weights
+    from q27b200.linear import ActQuant, Fp4Linear
+    from q27b200.q27lib import device_status
+
+    layers_n = args.layers
+    ws = torch.zeros(48 << 20, dtype=torch.uint8, device="cuda")
+    protos = {}
+    for pi, (name, N, K, glu) in enumerate(configs.LAYER_PROJECTIONS):
+        w = configs.make_w(N, K, 1000 + pi, 0.02).cuda()
+        codes, sfb, g = weights.quantize_weight_rtn(w)
+        del w
+        if glu:
+            codes, sfb = weights.interleave_gate_up(codes), weights.interleave_gate_up(sfb)
+        b, e = shard.shard_rows(N, world, rank, glu)
+        protos[name] = (codes[b:e].contiguous(), weights.swizzle_scales(sfb[b:e]), g, (e - b) // 2 if glu else e - b, K, glu)
+    model = []
+    for _ in range(layers_n):
+        layer = {}
+        for name, (codes, sfs, g, n_out, K, glu) in protos.items():
+            layer[name] = Fp4Linear(codes.clone(), sfs.clone(), g, 1.0, n_out, K, glu, ws)
+        model.append(layer)
+    del protos
+    results = {}
+    ms_list = list(configs.SWEEP_M) if args.m == 0 else [args.m]
+    for M in ms_list:
+        gx = torch.Generator().manual_seed(3)
+        xh = torch.randn(M, configs.HIDDEN, generator=gx).to(torch.bfloat16).cuda()
+        xo = torch.randn(M, configs.HIDDEN, generator=gx).to(torch.bfloat16).cuda()
+        xd = torch.randn(M, configs.INTER, generator=gx).to(torch.bfloat16).cuda()
+        s_h, s_o, s_d = (configs.input_scale_of(t) for t in (xh, xo, xd))
+        act_h, act_d = ActQuant(max(M, 128), configs.HIDDEN), ActQuant(max(M, 128), configs.INTER)
+        outs = {name: torch.empty(M, model[0][name].out, dtype=torch.bfloat16, device="cuda") for name in model[0]}
+        for layer in model:
+            for name, lin in layer.items():
+                lin.in_scale, lin.alpha = (s_d if name == "down" else s_o if name == "o" else s_h), 0.0
+                lin.alpha = lin.in_scale * lin.w_scale2
+                lin._alpha[0] = lin.alpha
+
+        def sweep(_i):
+            for layer in model:
+                q, sf = act_h.quantize(xh, s_h)
+                for name in ("q", "k", "v"):
+                    layer[name].gemm(M, q, sf, outs[name])
+                q, sf = act_h.quantize(xo, s_o)
+                layer["o"].gemm(M, q, sf, outs["o"])
+                q, sf = act_h.quantize(xh, s_h)
+                layer["gate_up"].gemm(M, q, sf, outs["gate_up"])
+                q, sf = act_d.quantize(xd, s_d)
+                layer["down"].gemm(M, q, sf, outs["down"])
+
+        ms = timed(sweep, args.steps, min(args.warmup, 3), world, not args.no_graph)
+        per_sweep_s = ms / args.steps / 1e3
+        nbytes = configs.sweep_algorithmic_bytes(M, layers_n)
+        results[M] = {"gbs": nbytes / per_sweep_s / 1e9, "ms_per_sweep": per_sweep_s * 1e3}
+    assert device_status() == 0, "a bounded wait inside a kernel ran out"
+    if rank != 0:
+        return
+    peak, peak_src = peaks()
+    head = 16 if 16 in results else ms_list[0]
+    r = results[head]
+    print(json.dumps({
+        "metric": "nvfp4_gemm_hbm_gbs", "value": r["gbs"], "unit": "GB/s", "n_gpus": world, "steps": args.steps,
+        "warmup": min(args.warmup, 3), "ms_per_step": r["ms_per_sweep"], "higher_is_better": True, "scaling": "strong",
+        "vs_baseline": None, "dtype": "nvfp4 (e2m1 x e2m1, ue4m3 scale per 16, fp32 accumulate)", "data": "synthetic",
+        "config": {"workload": f"cfg3 decode weight sweep, {layers_n} layers x (q,k,v,o,gate_up,down), M={head}",
+                   "l2": "every projection of every layer in its own device memory (11.9 GB at 64 layers)",
+                   "step": "per layer: quant, q, k, v, quant, o, quant, gate_up(SiLU*mul), quant, down; 10 launches",
+                   "timing": "CUDA-graph replay" if not args.no_graph else "eager launches",
+                   "sharding": f"N-sharded {world} way(s)"},
+        "roofline": {"bound": "hbm", "achieved": r["gbs"] / world, "peak": peak, "unit": "GB/s", "frac": r["gbs"] / world / peak,
+                     "traffic": None, "peak_source": peak_src, "kernel": "umma_gemm_kernel (weight streaming), whole sweep"},
+        "gpu_launches": args.steps * layers_n * 10,
+        "sweep": {str(m): v for m, v in results.items()}}))
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=200)
     ap.add_argument("--warmup", type=int, default=20)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--config", type=int, default=1, choices=[0, 1, 2, 4])
+    ap.add_argument("--config", type=int, default=1, choices=[0, 1, 2, 3, 4])
+    ap.add_argument("--m", type=int, default=0, help="configuration 3: the M to sweep at (0: all of 1..128)")
+    ap.add_argument("--layers", type=int, default=64, help="configuration 3: layers in the sweep")
     ap.add_argument("--cpu-steps", type=int, default=20)
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg (profiling runs)")
     ap.add_argument("--no-graph", action="store_true", help="time eager launches instead of a CUDA-graph replay")
@@ -216,9 +299,18 @@ def main():
 
     from q27b200 import configs
 
-    cfg = configs.CONFIGS[args.config]
     rank, world = int(os.environ.get("RANK", 0)), int(os.environ.get("WORLD_SIZE", 1))
     local_rank = int(os.environ.get("LOCAL_RANK", 0))
+    if args.config == 3:
+        assert args.impl == "ours", "the CPU arm times single GEMM configurations"
+        torch.cuda.set_device(local_rank)
+        if world > 1:
+            torch.distributed.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+        sweep_main(args, rank, world, local_rank)
+        if world > 1:
+            torch.distributed.destroy_process_group()
+        return
+    cfg = configs.CONFIGS[args.config]
     metric = "nvfp4_gemm_tflops" if cfg.M > 128 else "nvfp4_gemm_hbm_gbs"
     unit = "TFLOP/s" if cfg.M > 128 else "GB/s"
 

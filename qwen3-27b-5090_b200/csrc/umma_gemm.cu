@@ -39,7 +39,8 @@ namespace {
 
 enum Epi : int { kEpiF32 = 0, kEpiBf16 = 1, kEpiGluBf16 = 2 };
 
-constexpr int kThreads = 320;       // warp 0: TMA producer, 1: MMA issuer, 2..5: epilogue, 6..9: scale feeders
+// warp 0: TMA producer, 1: MMA issuer, then the epilogue warps (4, or 16 where a big tile is drained by one CTA
+// alone), then 4 scale feeders
 constexpr int kCounterBytes = 16384;  // per-tile arrival counters at the head of the workspace (4096 tiles)
 constexpr int kMaxParts = 500;        // unit ranges that may share one tile (never more than there are ranges)
 
@@ -58,6 +59,7 @@ struct GemmParams {
   float* partials;      // weight streaming: per-CTA partial tiles [2 * grid][M][128]
   SkinnyPlan plan;      // weight streaming
   int m_tiles, items;   // many rows
+  int n_tile;           // many rows: weight rows per tile (128 or 256)
   int ext_reduce;       // weight streaming: cut tiles are summed by skinny_fixup_kernel, not by the last CTA to arrive
   unsigned long long* trace;  // optional [cta][4][64] globaltimer samples (null: off)
 };
@@ -67,25 +69,33 @@ struct GemmParams {
 // this launch leaves).
 template <int NB, int STAGES, int CTAS, bool SWAP>
 struct Cfg {
-  static_assert(NB % 16 == 0 && NB >= 16 && NB <= 128, "N-side tile: 16..128 rows");
+  static_assert(NB % 16 == 0 && NB >= 16 && NB <= 256 && (NB <= 128 || !SWAP), "N-side tile: 16..128 rows (256: many rows)");
   static_assert(CTAS == 1 || CTAS == 2, "one or two CTAs per SM");
+  static constexpr int kQAtoms = (NB + 127) / 128;  // 128-row blocks of the N-side tile (scale atoms per MMA step)
   static constexpr int kPBytes = 128 * 128;  // 128 rows x 256 E2M1
   static constexpr int kQBytes = NB * 128;
-  static constexpr int kSfBytes = 4 * 512;   // 4 MMA steps x one 512-byte atom
-  static constexpr int kStageBytes = kPBytes + kQBytes + 2 * kSfBytes;
+  static constexpr int kSfBytes = 4 * 512;   // 4 MMA steps x one 512-byte atom (per 128-row block)
+  static constexpr int kStageBytes = kPBytes + kQBytes + (1 + kQAtoms) * kSfBytes;
   static constexpr int kOffQ = kPBytes, kOffSfP = kPBytes + kQBytes, kOffSfQ = kOffSfP + kSfBytes;
+  static constexpr int kSfCols = 16 + 16 * kQAtoms;  // tensor-memory columns of one stage's scales
   static constexpr int kXchgBytes = SWAP ? 8 * 64 * 4 + 2048 : 0;  // SiLU*mul exchange between the gate and the up warps + cut-tile info
   static constexpr int kNumBars = 3 * STAGES + 4;
   static constexpr int kBarBytes = kNumBars * 8 + 16;
   static constexpr int kSmemBytes = STAGES * kStageBytes + kXchgBytes + kBarBytes + 1024;  // + alignment slack
   static constexpr int kTmemCols = 512 / CTAS;
   // accumulators: two buffers when tensor memory allows (the epilogue of one piece overlaps the MMAs of the next),
-  // else one (two CTAs per SM overlap each other instead); scales: 32 columns per stage after them
-  static constexpr int kAccBufs = 2 * NB + 32 * STAGES <= kTmemCols ? 2 : 1;
+  // else one (two CTAs per SM overlap each other instead); scales: kSfCols columns per stage after them
+  static constexpr int kAccBufs = 2 * NB + kSfCols * STAGES <= kTmemCols ? 2 : 1;
   static constexpr int kSfCol0 = kAccBufs * NB;
   static constexpr int kRangesPerCta = 1;  // unit ranges of the work split per CTA
+  // Epilogue warps: four per quarter of the tensor-memory lanes where one CTA per SM drains a 128 x 256 tile alone:
+  // together they pull the whole accumulator into registers at once and hand it back to the MMA issuer before
+  // doing any arithmetic or stores. Else one per quarter.
+  static constexpr int kEpiWarps = (!SWAP && CTAS == 1) ? 16 : 4;
+  static constexpr int kFeederWarp0 = 2 + kEpiWarps;
+  static constexpr int kThreads = (kFeederWarp0 + 4) * 32;
   static_assert(kStageBytes % 1024 == 0, "stage tiles must stay 1024-byte aligned");
-  static_assert(kSfCol0 + 32 * STAGES <= kTmemCols, "tensor memory budget");
+  static_assert(kSfCol0 + kSfCols * STAGES <= kTmemCols, "tensor memory budget");
   static_assert(CTAS * (kSmemBytes + 1024) <= 228 * 1024, "shared memory budget");
 };
 
@@ -125,7 +135,7 @@ struct WorkIter {
     } else {
       if (item >= p.items) return false;
       const int mi = item % p.m_tiles, ni = item / p.m_tiles;
-      w.p_row0 = mi * 128, w.q_row0 = ni * 128, w.c0 = 0, w.c1 = p.chunks, w.slot = -1, w.tile = ni;
+      w.p_row0 = mi * 128, w.q_row0 = ni * p.n_tile, w.c0 = 0, w.c1 = p.chunks, w.slot = -1, w.tile = ni;
       item += gridDim.x;
       return true;
     }
@@ -216,7 +226,7 @@ __device__ __forceinline__ void store_swapped(const GemmParams& p, const float (
 }
 
 template <int NB, int STAGES, int CTAS, bool kSwap, int kEpi>
-__global__ void __launch_bounds__(kThreads, CTAS) umma_gemm_kernel(const __grid_constant__ CUtensorMap tmap_p,
+__global__ void __launch_bounds__((Cfg<NB, STAGES, CTAS, kSwap>::kThreads), CTAS) umma_gemm_kernel(const __grid_constant__ CUtensorMap tmap_p,
                                                                 const __grid_constant__ CUtensorMap tmap_q,
                                                                 const __grid_constant__ GemmParams p) {
   using C = Cfg<NB, STAGES, CTAS, kSwap>;
@@ -238,7 +248,7 @@ __global__ void __launch_bounds__(kThreads, CTAS) umma_gemm_kernel(const __grid_
   // Weights are read once (evict first); the activations are re-read by every CTA (keep them in L2).
   const uint64_t hint_w = kEvictFirst, hint_a = kEvictLast;
   const uint64_t hint_p = kSwap ? hint_w : hint_a, hint_q = kSwap ? hint_a : hint_w;
-  auto stage_bytes = [&](int c) { return uint32_t(C::kPBytes + C::kQBytes + 2 * min(4, p.ksteps - 4 * c) * 512); };
+  auto stage_bytes = [&](int c) { return uint32_t(C::kPBytes + C::kQBytes + (1 + C::kQAtoms) * min(4, p.ksteps - 4 * c) * 512); };
   auto load_p = [&](const Chunks& k, int stage) {
     const uint32_t sbase = smem_base + stage * C::kStageBytes, bar = full0 + 8 * stage;
     tma_load_2d(sbase, &tmap_p, k.c * 128, k.w.p_row0, bar, hint_p);
@@ -248,8 +258,10 @@ __global__ void __launch_bounds__(kThreads, CTAS) umma_gemm_kernel(const __grid_
   auto load_q = [&](const Chunks& k, int stage) {
     const uint32_t sbase = smem_base + stage * C::kStageBytes, bar = full0 + 8 * stage;
     tma_load_2d(sbase + C::kOffQ, &tmap_q, k.c * 128, k.w.q_row0, bar, hint_q);
-    bulk_load(sbase + C::kOffSfQ, p.sf_q + (int64_t(k.w.q_row0 / 128) * p.ksteps + 4 * k.c) * 512,
-              min(4, p.ksteps - 4 * k.c) * 512, bar, hint_q);
+#pragma unroll
+    for (int rb = 0; rb < C::kQAtoms; rb++)  // one run of atoms per 128-row block
+      bulk_load(sbase + C::kOffSfQ + rb * C::kSfBytes, p.sf_q + (int64_t(k.w.q_row0 / 128 + rb) * p.ksteps + 4 * k.c) * 512,
+                min(4, p.ksteps - 4 * k.c) * 512, bar, hint_q);
   };
   uint32_t armed = 0;  // (producer lane) stages with a copy possibly in flight
   int npre = 0;        // (producer lane) stages filled before the steady state
@@ -259,7 +271,7 @@ __global__ void __launch_bounds__(kThreads, CTAS) umma_gemm_kernel(const __grid_
     prefetch_tensormap(&tmap_p);
     prefetch_tensormap(&tmap_q);
     for (int s = 0; s < STAGES; s++) mbar_init(full0 + 8 * s, 1), mbar_init(empty0 + 8 * s, 1), mbar_init(sfr0 + 8 * s, 4);
-    for (int b = 0; b < 2; b++) mbar_init(afull0 + 8 * b, 1), mbar_init(aempty0 + 8 * b, 4);
+    for (int b = 0; b < 2; b++) mbar_init(afull0 + 8 * b, 1), mbar_init(aempty0 + 8 * b, C::kEpiWarps);
     *abort_flag = 0;
     mbar_init_fence();
     // The stream starts at once, while the rest of the CTA is still setting up: fill the ring with the operand
@@ -353,11 +365,11 @@ __global__ void __launch_bounds__(kThreads, CTAS) umma_gemm_kernel(const __grid_
           const int nsteps = min(4, p.ksteps - 4 * c);
           const uint32_t sbase = smem_base + stage * C::kStageBytes;
           const uint64_t desc_p = umma_desc_k_sw128(sbase), desc_q = umma_desc_k_sw128(sbase + C::kOffQ);
-          const uint32_t sf_col = tmem_base + C::kSfCol0 + 32 * stage;
+          const uint32_t sf_col = tmem_base + C::kSfCol0 + C::kSfCols * stage;
           for (int ks = 0; ks < nsteps; ks++) {
             // 64 E2M1 = 32 bytes further along K inside the 128-byte swizzle span: +2 in 16-byte address units
-            umma_nvfp4(d_tmem, desc_p + 2 * ks, desc_q + 2 * ks, idesc, sf_col + 4 * ks, sf_col + 16 + 4 * ks,
-                       accumulate);
+            umma_nvfp4(d_tmem, desc_p + 2 * ks, desc_q + 2 * ks, idesc, sf_col + 4 * ks,
+                       sf_col + 16 + 4 * C::kQAtoms * ks, accumulate);
             accumulate = 1;
           }
           umma_commit(empty0 + 8 * stage);  // the stage is free once these MMAs have read it
@@ -373,7 +385,7 @@ __global__ void __launch_bounds__(kThreads, CTAS) umma_gemm_kernel(const __grid_
         ok = mbar_wait_bounded(aempty0 + 8 * (j % C::kAccBufs), (j / C::kAccBufs) & 1, abort_flag, &g_status,
                                kStatusAccumFreeTimeout, 64);
     }
-  } else if (warp >= 6) {
+  } else if (warp >= C::kFeederWarp0) {
     // ------------------------------------------------------------------------------------------ scale feeders
     // Each of the four warps copies the stage's scale atoms (shared memory -> registers -> its own quarter of the
     // tensor-memory lanes), which yields the four-fold replication the MMA expects without occupying the MMA
@@ -386,12 +398,24 @@ __global__ void __launch_bounds__(kThreads, CTAS) umma_gemm_kernel(const __grid_
       const uint8_t* sb = smem + stage * C::kStageBytes;
       const uint4* sfp = reinterpret_cast<const uint4*>(sb + C::kOffSfP) + lane;
       const uint4* sfq = reinterpret_cast<const uint4*>(sb + C::kOffSfQ) + lane;
-      uint4 a[4], b[4];
+      const uint32_t taddr = tmem_base + lane_base + C::kSfCol0 + C::kSfCols * stage;
+      uint4 a[4];
 #pragma unroll
-      for (int ks = 0; ks < 4; ks++) a[ks] = sfp[32 * ks], b[ks] = sfq[32 * ks];  // (steps past K: stale, unused)
-      const uint32_t taddr = tmem_base + lane_base + C::kSfCol0 + 32 * stage;
+      for (int ks = 0; ks < 4; ks++) a[ks] = sfp[32 * ks];  // (steps past K: stale, unused)
       tmem_st16(taddr, a);
-      tmem_st16(taddr + 16, b);
+      if constexpr (C::kQAtoms == 1) {
+#pragma unroll
+        for (int ks = 0; ks < 4; ks++) a[ks] = sfq[32 * ks];
+        tmem_st16(taddr + 16, a);
+      } else {
+        // 256-row N side: per MMA step the columns of rows 0..127, then those of rows 128..255
+#pragma unroll
+        for (int h = 0; h < 2; h++) {
+#pragma unroll
+          for (int ks = 0; ks < 2; ks++) a[2 * ks] = sfq[32 * (2 * h + ks)], a[2 * ks + 1] = sfq[32 * (4 + 2 * h + ks)];
+          tmem_st16(taddr + 16 + 16 * h, a);
+        }
+      }
       tmem_st_wait();
       tc_fence_before_sync();
       __syncwarp();
@@ -415,7 +439,7 @@ __global__ void __launch_bounds__(kThreads, CTAS) umma_gemm_kernel(const __grid_
       }
       if (!warp_wait(afull0 + 8 * buf, (i / C::kAccBufs) & 1, abort_flag, &g_status, kStatusAccumWaitTimeout, 128)) break;
       tc_fence_after_sync();
-      if (threadIdx.x == 64) TRACE(3, 4 + i);
+      if (threadIdx.x == 64 && i < 4) TRACE(3, 4 + i);
       const uint32_t taddr = tmem_base + (uint32_t(quarter * 32) << 16) + buf * NB;
       if constexpr (kSwap) {
         // lane = weight row (output channel), column = token
@@ -484,56 +508,80 @@ __global__ void __launch_bounds__(kThreads, CTAS) umma_gemm_kernel(const __grid_
         // lane = token, column = output channel
         const int m = w.p_row0 + row;
         const bool valid = m < p.M;
-#pragma unroll 1
-        for (int c0 = 0; c0 < NB; c0 += 16) {
-          if constexpr (kEpi == kEpiGluBf16) {
-            if (c0 >= 64) break;
-            float g[16], u[16];
-            tmem_ld16(taddr + c0, g);
-            tmem_ld16(taddr + 64 + c0, u);
-            tmem_ld_wait();
-            if (valid) {
-              const float ag = p.alpha.alpha[0], au = p.alpha_up;
+        constexpr bool kGlu = kEpi == kEpiGluBf16;
+        // store 16 finished outputs of this thread's token (gate | up pairs for the SiLU*mul epilogue)
+        auto emit = [&](int c0, const float* g, const float* u) {
+          if (!valid) return;
+          if constexpr (kGlu) {
+            const float ag = p.alpha.alpha[0], au = p.alpha_up;
+            uint32_t pk[8];
+#pragma unroll
+            for (int j = 0; j < 8; j++) {
+              const uint32_t lo = bf16_bits(silu_mul(__fmul_rn(ag, g[2 * j]), __fmul_rn(au, u[2 * j])));
+              const uint32_t hi = bf16_bits(silu_mul(__fmul_rn(ag, g[2 * j + 1]), __fmul_rn(au, u[2 * j + 1])));
+              pk[j] = lo | (hi << 16);
+            }
+            // every 128 weight rows: 64 gate rows, then the up rows of the same 64 outputs
+            uint4* d = reinterpret_cast<uint4*>(static_cast<uint16_t*>(p.d) + int64_t(m) * (p.N / 2) + (w.q_row0 + c0) / 2 +
+                                                (c0 & 63) / 2);
+            d[0] = make_uint4(pk[0], pk[1], pk[2], pk[3]);
+            d[1] = make_uint4(pk[4], pk[5], pk[6], pk[7]);
+          } else {
+            const int n0 = w.q_row0 + c0;
+            float out[16];
+#pragma unroll
+            for (int j = 0; j < 16; j++) out[j] = finish_f32(p, g[j], m, n0 + j);
+            if constexpr (kEpi == kEpiF32) {
+              float4* d = reinterpret_cast<float4*>(static_cast<float*>(p.d) + int64_t(m) * p.N + n0);
+#pragma unroll
+              for (int j = 0; j < 4; j++) d[j] = make_float4(out[4 * j], out[4 * j + 1], out[4 * j + 2], out[4 * j + 3]);
+            } else {
               uint32_t pk[8];
 #pragma unroll
-              for (int j = 0; j < 8; j++) {
-                const uint32_t lo = bf16_bits(silu_mul(__fmul_rn(ag, g[2 * j]), __fmul_rn(au, u[2 * j])));
-                const uint32_t hi = bf16_bits(silu_mul(__fmul_rn(ag, g[2 * j + 1]), __fmul_rn(au, u[2 * j + 1])));
-                pk[j] = lo | (hi << 16);
-              }
-              uint4* d = reinterpret_cast<uint4*>(static_cast<uint16_t*>(p.d) + int64_t(m) * (p.N / 2) + w.tile * 64 + c0);
+              for (int j = 0; j < 8; j++) pk[j] = uint32_t(bf16_bits(out[2 * j])) | (uint32_t(bf16_bits(out[2 * j + 1])) << 16);
+              uint4* d = reinterpret_cast<uint4*>(static_cast<uint16_t*>(p.d) + int64_t(m) * p.N + n0);
               d[0] = make_uint4(pk[0], pk[1], pk[2], pk[3]);
               d[1] = make_uint4(pk[4], pk[5], pk[6], pk[7]);
             }
-          } else {
-            float v[16];
-            tmem_ld16(taddr + c0, v);
-            tmem_ld_wait();
-            if (valid) {
-              const int n0 = w.q_row0 + c0;
-              float out[16];
-#pragma unroll
-              for (int j = 0; j < 16; j++) out[j] = finish_f32(p, v[j], m, n0 + j);
-              if constexpr (kEpi == kEpiF32) {
-                float4* d = reinterpret_cast<float4*>(static_cast<float*>(p.d) + int64_t(m) * p.N + n0);
-#pragma unroll
-                for (int j = 0; j < 4; j++) d[j] = make_float4(out[4 * j], out[4 * j + 1], out[4 * j + 2], out[4 * j + 3]);
-              } else {
-                uint32_t pk[8];
-#pragma unroll
-                for (int j = 0; j < 8; j++) pk[j] = uint32_t(bf16_bits(out[2 * j])) | (uint32_t(bf16_bits(out[2 * j + 1])) << 16);
-                uint4* d = reinterpret_cast<uint4*>(static_cast<uint16_t*>(p.d) + int64_t(m) * p.N + n0);
-                d[0] = make_uint4(pk[0], pk[1], pk[2], pk[3]);
-                d[1] = make_uint4(pk[4], pk[5], pk[6], pk[7]);
-              }
-            }
           }
+        };
+        // first column of the u-th unit of 16 outputs: plain 16 u; SiLU*mul: 4 gate units per 128-row block
+        auto unit_col = [&](int u) { return kGlu ? (u >> 2) * 128 + (u & 3) * 16 : u * 16; };
+        constexpr int kUnits = kGlu ? NB / 32 : NB / 16;
+        if constexpr (C::kEpiWarps == 16) {
+          // Pull this warp's share of the accumulator into registers in one go, give the accumulator back, then
+          // do the arithmetic and the stores while the MMAs of the next tile already run.
+          constexpr int kMine = kUnits / 4;
+          const int sub = (warp - 2) >> 2;
+          float g[kMine][16], u[kGlu ? kMine : 1][16];
+#pragma unroll
+          for (int j = 0; j < kMine; j++) {
+            const int c0 = unit_col(sub + 4 * j);
+            tmem_ld16(taddr + c0, g[j]);
+            if constexpr (kGlu) tmem_ld16(taddr + 64 + c0, u[j]);
+          }
+          tmem_ld_wait();
+          tc_fence_before_sync();
+          __syncwarp();
+          if (lane == 0) mbar_arrive(aempty0 + 8 * buf);
+#pragma unroll
+          for (int j = 0; j < kMine; j++) emit(unit_col(sub + 4 * j), g[j], u[kGlu ? j : 0]);
+        } else {
+#pragma unroll 1
+          for (int un = 0; un < kUnits; un++) {
+            const int c0 = unit_col(un);
+            float g[16], u[16];
+            tmem_ld16(taddr + c0, g);
+            if constexpr (kGlu) tmem_ld16(taddr + 64 + c0, u);
+            tmem_ld_wait();
+            emit(c0, g, u);
+          }
+          tc_fence_before_sync();
+          __syncwarp();
+          if (lane == 0) mbar_arrive(aempty0 + 8 * buf);
         }
-        tc_fence_before_sync();
-        __syncwarp();
-        if (lane == 0) mbar_arrive(aempty0 + 8 * buf);
       }
-      if (threadIdx.x == 64) TRACE(3, 8 + i);
+      if (threadIdx.x == 64 && i < 4) TRACE(3, 8 + i);
     }
   }
 
@@ -546,7 +594,6 @@ __global__ void __launch_bounds__(kThreads, CTAS) umma_gemm_kernel(const __grid_
   if (threadIdx.x == 0) TRACE(3, 12);
   if (threadIdx.x == 32) TRACE(3, 13);
   if (threadIdx.x == 64) TRACE(3, 14);
-  if (threadIdx.x == 192) TRACE(3, 15);
   if (warp == 1) {
     __syncwarp();
     tc_fence_after_sync();
@@ -637,10 +684,10 @@ int make_operand_map(CUtensorMap* map, const uint8_t* base, int rows, int K, int
 }
 
 template <typename Kern>
-int launch_gemm(Kern kernel, int grid, int smem, cudaStream_t s, const CUtensorMap& mp, const CUtensorMap& mq,
-                const GemmParams& p, bool pdl) {
+int launch_gemm(Kern kernel, int grid, int threads, int smem, cudaStream_t s, const CUtensorMap& mp,
+                const CUtensorMap& mq, const GemmParams& p, bool pdl) {
   cudaLaunchConfig_t cfg = {};
-  cfg.gridDim = dim3(grid), cfg.blockDim = dim3(kThreads), cfg.dynamicSmemBytes = smem, cfg.stream = s;
+  cfg.gridDim = dim3(grid), cfg.blockDim = dim3(threads), cfg.dynamicSmemBytes = smem, cfg.stream = s;
   cudaLaunchAttribute attr[1];
   attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
   attr[0].val.programmaticStreamSerializationAllowed = 1;
@@ -671,7 +718,7 @@ int run_skinny(const uint8_t* a, const uint8_t* w, GemmParams& p, cudaStream_t s
   if (int rc = make_operand_map(&mp, w, p.N, p.K, 128)) return rc;
   if (int rc = make_operand_map(&mq, a, p.M, p.K, NB)) return rc;
   const int grid = (p.plan.grid + C::kRangesPerCta - 1) / C::kRangesPerCta;
-  if (int rc = launch_gemm(kernel, grid, C::kSmemBytes, s, mp, mq, p, true)) return rc;
+  if (int rc = launch_gemm(kernel, grid, C::kThreads, C::kSmemBytes, s, mp, mq, p, true)) return rc;
   if (p.ext_reduce) {
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(p.plan.tiles, (p.M + 7) / 8), cfg.blockDim = dim3(128), cfg.stream = s;
@@ -733,19 +780,26 @@ int skinny_common(int kEpi, int M, int N, int K, const uint8_t* a, const uint8_t
   }
 }
 
-template <int kEpi>
-int run_many(const uint8_t* a, const uint8_t* w, GemmParams& p, cudaStream_t s) {
-  // Two CTAs per SM: one thread issues an MMA of this shape only every ~140 cycles while the tensor pipe needs 64
-  // for it, so two issuers keep it busier, and the epilogue of one CTA overlaps the MMAs of the other.
-  constexpr int NB = 128, STAGES = 3, CTAS = 2;
+template <int NB, int STAGES, int CTAS, int kEpi>
+int run_many_cfg(const uint8_t* a, const uint8_t* w, GemmParams& p, cudaStream_t s) {
   using C = Cfg<NB, STAGES, CTAS, false>;
   auto kernel = umma_gemm_kernel<NB, STAGES, CTAS, false, kEpi>;
   if (int rc = ensure_smem<NB, STAGES, CTAS, false, kEpi>()) return rc;
+  p.n_tile = NB, p.items = p.m_tiles * (p.N / NB);
   CUtensorMap mp, mq;
   if (int rc = make_operand_map(&mp, a, p.M, p.K, 128)) return rc;
   if (int rc = make_operand_map(&mq, w, p.N, p.K, NB)) return rc;
   const int slots = CTAS * sm_count();
-  return launch_gemm(kernel, p.items < slots ? p.items : slots, C::kSmemBytes, s, mp, mq, p, true);
+  return launch_gemm(kernel, p.items < slots ? p.items : slots, C::kThreads, C::kSmemBytes, s, mp, mq, p, true);
+}
+
+template <int kEpi>
+int run_many(const uint8_t* a, const uint8_t* w, GemmParams& p, cudaStream_t s) {
+  // 128 x 256 tiles when the weight rows allow: one MMA of that shape keeps the tensor pipe busy for 128 of the
+  // ~140 cycles its issue takes, and every byte an SM pulls from L2 feeds 1.5 x the flops of a 128 x 128 tile.
+  // Otherwise 128 x 128 tiles on two CTAs per SM (two MMA issuers per SM; the epilogue of one overlaps the other).
+  if (p.N % 256 == 0) return run_many_cfg<256, 4, 1, kEpi>(a, w, p, s);
+  return run_many_cfg<128, 3, 2, kEpi>(a, w, p, s);
 }
 
 int many_common(int kEpi, int M, int N, int K, const uint8_t* a, const uint8_t* a_sf, const uint8_t* w,
@@ -759,7 +813,7 @@ int many_common(int kEpi, int M, int N, int K, const uint8_t* a, const uint8_t* 
   p.M = M, p.N = N, p.K = K, p.ksteps = K / 64, p.chunks = (p.ksteps + 3) / 4;
   p.sf_p = a_sf, p.sf_q = w_sf, p.alpha.count = 1, p.alpha.alpha[0] = alpha, p.alpha_up = alpha_up;
   p.c = (c && beta != 0.f) ? c : nullptr, p.beta = beta, p.d = d;
-  p.m_tiles = (M + 127) / 128, p.items = p.m_tiles * (N / 128);
+  p.m_tiles = (M + 127) / 128;
   p.trace = g_trace;
   switch (kEpi) {
     case kEpiF32: return run_many<kEpiF32>(a, w, p, s);

@@ -60,6 +60,18 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
   return ok != 0;
 }
 
+// The same with cluster scope: the arrivals may come from the partner CTA of a pair.
+__device__ __forceinline__ bool mbar_try_wait_cluster(uint32_t bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.acquire.cluster.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok)
+      : "r"(bar), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
 // Budget of a bounded wait in SM clock cycles (about two seconds at 2 GHz) and in polls (each poll may itself
 // block for a hardware-defined slice of time; the cycle budget is what normally ends a wait that cannot succeed).
 constexpr long long kMaxWaitCycles = 4000000000ll;
@@ -68,12 +80,13 @@ constexpr uint32_t kMaxPolls = 1u << 28;
 // Waits for the phase with the given parity; gives up when `abort_flag` (shared memory) is raised by another
 // role or when the budget is spent, in which case it raises the flag itself and records `code`.
 __device__ __forceinline__ bool mbar_wait_bounded(uint32_t bar, uint32_t parity, volatile uint32_t* abort_flag,
-                                                  uint32_t* status, uint32_t code, uint32_t sleep_ns = 0) {
-  if (mbar_try_wait(bar, parity)) return true;
+                                                  uint32_t* status, uint32_t code, uint32_t sleep_ns = 0,
+                                                  bool cluster = false) {
+  if (cluster ? mbar_try_wait_cluster(bar, parity) : mbar_try_wait(bar, parity)) return true;
   const long long t0 = clock64();
   for (uint32_t i = 1; i < kMaxPolls; i++) {
     if (sleep_ns) __nanosleep(sleep_ns);  // long waits back off: polls go through the shared-memory pipe
-    if (mbar_try_wait(bar, parity)) return true;
+    if (cluster ? mbar_try_wait_cluster(bar, parity) : mbar_try_wait(bar, parity)) return true;
     if ((i & 63u) == 0u) {
       if (*abort_flag) return false;
       if (clock64() - t0 > kMaxWaitCycles) break;
@@ -232,5 +245,59 @@ __device__ __forceinline__ void tmem_st16(uint32_t taddr, const uint4 (&v)[4]) {
       : "memory");
 }
 __device__ __forceinline__ void tmem_st_wait() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
+
+
+// ------------------------------------------------------------------------------------------------ CTA pairs
+// (clusters of two CTAs on neighbouring SMs driving one tcgen05.mma.cta_group::2; no multicast loads anywhere)
+
+__device__ __forceinline__ uint32_t cluster_ctarank() {
+  uint32_t r;
+  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+  return r;
+}
+// Every thread of both CTAs arrives and waits: used once at start-up and once before exit, unconditionally.
+__device__ __forceinline__ void cluster_sync_all() {
+  asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+// Arrive on the barrier at the same shared-memory offset in CTA `rank` of the cluster.
+__device__ __forceinline__ void mbar_arrive_remote(uint32_t bar, uint32_t rank) {
+  asm volatile(
+      "{\n\t.reg .b32 ra;\n\t"
+      "mapa.shared::cluster.u32 ra, %0, %1;\n\t"
+      "mbarrier.arrive.shared::cluster.b64 _, [ra];\n\t}"
+      ::"r"(bar), "r"(rank)
+      : "memory");
+}
+__device__ __forceinline__ void tmem_alloc_2sm(uint32_t smem_result, uint32_t ncols) {  // one warp in each CTA
+  asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_result), "r"(ncols)
+               : "memory");
+}
+__device__ __forceinline__ void tmem_relinquish_2sm() {
+  asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc_2sm(uint32_t taddr, uint32_t ncols) {
+  asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(ncols) : "memory");
+}
+// Instruction descriptor for the pair: 256 x n x 64 (each CTA holds 128 of the 256 rows).
+__host__ __device__ constexpr uint32_t umma_idesc_nvfp4_2sm(uint32_t n) {
+  return (1u << 7) | (1u << 10) | ((n >> 3) << 17) | ((256u >> 4) << 24);
+}
+// Issued by the leader CTA only; runs on both SMs. A: each CTA's own 128 rows, B: each CTA holds n / 2 rows.
+__device__ __forceinline__ void umma_nvfp4_2sm(uint32_t d_tmem, uint64_t adesc, uint64_t bdesc, uint32_t idesc,
+                                               uint32_t sfa_tmem, uint32_t sfb_tmem, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::2.kind::mxf4nvf4.block_scale.scale_vec::4X [%0], %1, %2, %3, [%5], [%6], p;\n\t}"
+      ::"r"(d_tmem), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate), "r"(sfa_tmem), "r"(sfb_tmem)
+      : "memory");
+}
+// Arrives on the barrier at this offset in both CTAs once the leader's tcgen05 operations so far have completed.
+__device__ __forceinline__ void umma_commit_2sm(uint32_t bar) {
+  asm volatile(
+      "tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;"
+      ::"r"(bar), "h"(uint16_t(3))
+      : "memory");
+}
 
 }  // namespace q27b

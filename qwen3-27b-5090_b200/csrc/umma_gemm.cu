@@ -25,6 +25,10 @@
 // kernels.cu:319-339) of the reference.
 #include <cuda.h>
 
+#include <algorithm>
+#include <cstdlib>
+#include <cstring>
+
 #include "common.cuh"
 #include "layout.h"
 #include "ptx_sm100.cuh"
@@ -221,6 +225,45 @@ __device__ __forceinline__ void store_swapped(const GemmParams& p, const float (
         if constexpr (kEpi == kEpiF32) static_cast<float*>(p.d)[int64_t(m) * p.N + n] = out;
         else static_cast<uint16_t*>(p.d)[int64_t(m) * p.N + n] = bf16_bits(out);
       }
+    }
+  }
+}
+
+// Many rows: stores 16 finished outputs of one token (tile columns c0 .. c0 + 15 of the tile starting at weight row
+// q_row0; for the SiLU*mul epilogue g / u are 16 gate values and the up values of the same outputs: every 128
+// weight rows are 64 gate rows followed by the up rows of the same 64 outputs).
+template <int kEpi>
+__device__ __forceinline__ void emit_many(const GemmParams& p, int m, bool valid, int q_row0, int c0, const float* g,
+                                          const float* u) {
+  if (!valid) return;
+  if constexpr (kEpi == kEpiGluBf16) {
+    const float ag = p.alpha.alpha[0], au = p.alpha_up;
+    uint32_t pk[8];
+#pragma unroll
+    for (int j = 0; j < 8; j++) {
+      const uint32_t lo = bf16_bits(silu_mul(__fmul_rn(ag, g[2 * j]), __fmul_rn(au, u[2 * j])));
+      const uint32_t hi = bf16_bits(silu_mul(__fmul_rn(ag, g[2 * j + 1]), __fmul_rn(au, u[2 * j + 1])));
+      pk[j] = lo | (hi << 16);
+    }
+    uint4* d = reinterpret_cast<uint4*>(static_cast<uint16_t*>(p.d) + int64_t(m) * (p.N / 2) + (q_row0 + c0) / 2 + (c0 & 63) / 2);
+    d[0] = make_uint4(pk[0], pk[1], pk[2], pk[3]);
+    d[1] = make_uint4(pk[4], pk[5], pk[6], pk[7]);
+  } else {
+    const int n0 = q_row0 + c0;
+    float out[16];
+#pragma unroll
+    for (int j = 0; j < 16; j++) out[j] = finish_f32(p, g[j], m, n0 + j);
+    if constexpr (kEpi == kEpiF32) {
+      float4* d = reinterpret_cast<float4*>(static_cast<float*>(p.d) + int64_t(m) * p.N + n0);
+#pragma unroll
+      for (int j = 0; j < 4; j++) d[j] = make_float4(out[4 * j], out[4 * j + 1], out[4 * j + 2], out[4 * j + 3]);
+    } else {
+      uint32_t pk[8];
+#pragma unroll
+      for (int j = 0; j < 8; j++) pk[j] = uint32_t(bf16_bits(out[2 * j])) | (uint32_t(bf16_bits(out[2 * j + 1])) << 16);
+      uint4* d = reinterpret_cast<uint4*>(static_cast<uint16_t*>(p.d) + int64_t(m) * p.N + n0);
+      d[0] = make_uint4(pk[0], pk[1], pk[2], pk[3]);
+      d[1] = make_uint4(pk[4], pk[5], pk[6], pk[7]);
     }
   }
 }
@@ -509,42 +552,7 @@ __global__ void __launch_bounds__((Cfg<NB, STAGES, CTAS, kSwap>::kThreads), CTAS
         const int m = w.p_row0 + row;
         const bool valid = m < p.M;
         constexpr bool kGlu = kEpi == kEpiGluBf16;
-        // store 16 finished outputs of this thread's token (gate | up pairs for the SiLU*mul epilogue)
-        auto emit = [&](int c0, const float* g, const float* u) {
-          if (!valid) return;
-          if constexpr (kGlu) {
-            const float ag = p.alpha.alpha[0], au = p.alpha_up;
-            uint32_t pk[8];
-#pragma unroll
-            for (int j = 0; j < 8; j++) {
-              const uint32_t lo = bf16_bits(silu_mul(__fmul_rn(ag, g[2 * j]), __fmul_rn(au, u[2 * j])));
-              const uint32_t hi = bf16_bits(silu_mul(__fmul_rn(ag, g[2 * j + 1]), __fmul_rn(au, u[2 * j + 1])));
-              pk[j] = lo | (hi << 16);
-            }
-            // every 128 weight rows: 64 gate rows, then the up rows of the same 64 outputs
-            uint4* d = reinterpret_cast<uint4*>(static_cast<uint16_t*>(p.d) + int64_t(m) * (p.N / 2) + (w.q_row0 + c0) / 2 +
-                                                (c0 & 63) / 2);
-            d[0] = make_uint4(pk[0], pk[1], pk[2], pk[3]);
-            d[1] = make_uint4(pk[4], pk[5], pk[6], pk[7]);
-          } else {
-            const int n0 = w.q_row0 + c0;
-            float out[16];
-#pragma unroll
-            for (int j = 0; j < 16; j++) out[j] = finish_f32(p, g[j], m, n0 + j);
-            if constexpr (kEpi == kEpiF32) {
-              float4* d = reinterpret_cast<float4*>(static_cast<float*>(p.d) + int64_t(m) * p.N + n0);
-#pragma unroll
-              for (int j = 0; j < 4; j++) d[j] = make_float4(out[4 * j], out[4 * j + 1], out[4 * j + 2], out[4 * j + 3]);
-            } else {
-              uint32_t pk[8];
-#pragma unroll
-              for (int j = 0; j < 8; j++) pk[j] = uint32_t(bf16_bits(out[2 * j])) | (uint32_t(bf16_bits(out[2 * j + 1])) << 16);
-              uint4* d = reinterpret_cast<uint4*>(static_cast<uint16_t*>(p.d) + int64_t(m) * p.N + n0);
-              d[0] = make_uint4(pk[0], pk[1], pk[2], pk[3]);
-              d[1] = make_uint4(pk[4], pk[5], pk[6], pk[7]);
-            }
-          }
-        };
+        auto emit = [&](int c0, const float* g, const float* u) { emit_many<kEpi>(p, m, valid, w.q_row0, c0, g, u); };
         // first column of the u-th unit of 16 outputs: plain 16 u; SiLU*mul: 4 gate units per 128-row block
         auto unit_col = [&](int u) { return kGlu ? (u >> 2) * 128 + (u & 3) * 16 : u * 16; };
         constexpr int kUnits = kGlu ? NB / 32 : NB / 16;
@@ -598,6 +606,228 @@ __global__ void __launch_bounds__((Cfg<NB, STAGES, CTAS, kSwap>::kThreads), CTAS
     __syncwarp();
     tc_fence_after_sync();
     tmem_dealloc(tmem_base, C::kTmemCols);
+  }
+}
+
+// ---------------------------------------------------------------------------------------------------------------
+// Many rows on CTA pairs: a cluster of two CTAs on neighbouring SMs computes a 256-token x 256-channel tile with
+// tcgen05.mma.cta_group::2. Each CTA loads its own 128 tokens, HALF of the 256 weight rows (the instruction reads
+// the other half from the partner's shared memory), its own activation scales and the scales of all 256 weight
+// rows: 38 KiB per SM per 256 K-elements for the flops that cost a lone CTA 54 KiB. The kernel with one CTA per
+// tile is bound by what an SM can pull from L2 (~48 bytes per clock measured), so this is the way to more flops.
+// Rank 0 of the pair issues the MMAs and owns the barriers that gather both CTAs; no load is multicast.
+template <int STAGES>
+struct Cfg2 {
+  static constexpr int kPBytes = 128 * 128, kQBytes = 128 * 128, kSfBytes = 4 * 512;
+  static constexpr int kStageBytes = kPBytes + kQBytes + 3 * kSfBytes;  // + scales: own tokens, 2 x 128 weight rows
+  static constexpr int kOffQ = kPBytes, kOffSfP = kPBytes + kQBytes, kOffSfQ = kOffSfP + kSfBytes;
+  static constexpr int kSfCols = 48;
+  static constexpr int kNumBars = 3 * STAGES + 2;
+  static constexpr int kSmemBytes = STAGES * kStageBytes + kNumBars * 8 + 16 + 1024;
+  static constexpr int kTmemCols = 512, kSfCol0 = 256;
+  static constexpr int kEpiWarps = 16, kFeederWarp0 = 2 + kEpiWarps, kThreads = (kFeederWarp0 + 4) * 32;
+  static_assert(kStageBytes % 1024 == 0, "stage tiles must stay 1024-byte aligned");
+  static_assert(kSfCol0 + kSfCols * STAGES <= kTmemCols, "tensor memory budget");
+  static_assert(kSmemBytes + 1024 <= 228 * 1024, "shared memory budget");
+};
+
+template <int STAGES, int kEpi>
+__global__ void __launch_bounds__(Cfg2<STAGES>::kThreads, 1) umma_gemm2_kernel(const __grid_constant__ CUtensorMap tmap_a,
+                                                                              const __grid_constant__ CUtensorMap tmap_w,
+                                                                              const __grid_constant__ GemmParams p) {
+  using C = Cfg2<STAGES>;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + STAGES * C::kStageBytes);
+  const uint32_t full0 = smem_u32(bars), empty0 = full0 + 8 * STAGES, sfr0 = empty0 + 8 * STAGES, afull = sfr0 + 8 * STAGES,
+                 aempty = afull + 8;
+  uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(bars + C::kNumBars);
+  volatile uint32_t* abort_flag = tmem_holder + 1;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const uint32_t rank = cluster_ctarank();  // 0: leader
+  const int pair = blockIdx.x >> 1, npairs = gridDim.x >> 1;
+  const int m_pairs = (p.M + 255) / 256, items = m_pairs * (p.N / 256);
+  const int m_blocks = (p.M + 127) / 128;
+  const uint32_t smem_base = smem_u32(smem);
+
+  if (threadIdx.x == 0) {
+    TRACE(3, 0);
+    prefetch_tensormap(&tmap_a);
+    prefetch_tensormap(&tmap_w);
+    for (int s = 0; s < STAGES; s++) mbar_init(full0 + 8 * s, 1), mbar_init(empty0 + 8 * s, 1), mbar_init(sfr0 + 8 * s, 8);
+    mbar_init(afull, 1), mbar_init(aempty, 2 * C::kEpiWarps);
+    *abort_flag = 0;
+    mbar_init_fence();
+  }
+  if (warp == 1) {
+    tmem_alloc_2sm(smem_u32(tmem_holder), C::kTmemCols);
+    tmem_relinquish_2sm();
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  cluster_sync_all();  // the partner's barriers exist before anything arrives on them
+  tc_fence_after_sync();
+  const uint32_t tmem_base = *tmem_holder;
+
+  if (warp == 0) {
+    // ------------------------------------------------------------------------------------------ TMA producer
+    if (lane == 0) {
+      int stage = 0, tk = 0;
+      uint32_t phase = 0, armed = 0, last_parity = 0;
+      bool ok = true, waited = false;
+      for (int item = pair; ok && item < items; item += npairs) {
+        const int m0 = (item % m_pairs) * 256 + int(rank) * 128, n0 = (item / m_pairs) * 256;
+        const bool sfa_valid = m0 / 128 < m_blocks;  // the partner half of the last token tile may not exist
+        for (int c = 0; c < p.chunks; c++) {
+          if (!mbar_wait_bounded(empty0 + 8 * stage, phase ^ 1, abort_flag, &g_status, kStatusEmptyWaitTimeout)) {
+            ok = false;
+            break;
+          }
+          const int nsteps = min(4, p.ksteps - 4 * c);
+          const uint32_t sbase = smem_base + stage * C::kStageBytes, bar = full0 + 8 * stage;
+          TRACE(0, tk);
+          tk++;
+          mbar_arrive_expect_tx(bar, C::kPBytes + C::kQBytes + (sfa_valid ? 3 : 2) * nsteps * 512);
+          armed |= 1u << stage;
+          last_parity = (last_parity & ~(1u << stage)) | (phase << stage);
+          tma_load_2d(sbase + C::kOffQ, &tmap_w, c * 128, n0 + int(rank) * 128, bar, kEvictNormal);
+          for (int rb = 0; rb < 2; rb++)
+            bulk_load(sbase + C::kOffSfQ + rb * C::kSfBytes, p.sf_q + (int64_t(n0 / 128 + rb) * p.ksteps + 4 * c) * 512,
+                      nsteps * 512, bar, kEvictNormal);
+          if (!waited) pdl_wait(), waited = true;  // the activations come from the preceding kernel
+          tma_load_2d(sbase, &tmap_a, c * 128, m0, bar, kEvictLast);
+          if (sfa_valid)
+            bulk_load(sbase + C::kOffSfP, p.sf_p + (int64_t(m0 / 128) * p.ksteps + 4 * c) * 512, nsteps * 512, bar, kEvictLast);
+          if (++stage == STAGES) stage = 0, phase ^= 1;
+        }
+      }
+      pdl_trigger();
+      if (!ok) {
+        for (int s = 0; s < STAGES; s++)
+          if (armed >> s & 1) {
+            bool landed = false;
+            const long long t0 = clock64();
+            for (uint32_t i = 0; i < kMaxPolls && !landed; i++) {
+              landed = mbar_try_wait(full0 + 8 * s, last_parity >> s & 1);
+              if ((i & 63u) == 63u && clock64() - t0 > kMaxWaitCycles) break;
+            }
+            if (!landed) atomicCAS(&g_status, 0u, uint32_t(kStatusDrainTimeout));
+          }
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------------------------------------ MMA issuer (leader)
+    if (lane == 0 && rank == 0) {
+      constexpr uint32_t idesc = umma_idesc_nvfp4_2sm(256);
+      int stage = 0, ntiles = 0, tk = 0;
+      uint32_t phase = 0;
+      bool ok = true;
+      for (int item = pair; ok && item < items; item += npairs, ntiles++) {
+        // both CTAs' epilogues have read the accumulators of the previous tile
+        if (!mbar_wait_bounded(aempty, (ntiles & 1) ^ 1, abort_flag, &g_status, kStatusAccumFreeTimeout, 0, true)) break;
+        tc_fence_after_sync();
+        uint32_t accumulate = 0;
+        for (int c = 0; c < p.chunks; c++) {
+          // eight arrivals: the scale feeders of both CTAs, each after its CTA's stage has landed
+          if (!mbar_wait_bounded(sfr0 + 8 * stage, phase, abort_flag, &g_status, kStatusFullWaitTimeout, 0, true)) {
+            ok = false;
+            break;
+          }
+          tc_fence_after_sync();
+          TRACE(1, tk);
+          const int nsteps = min(4, p.ksteps - 4 * c);
+          const uint32_t sbase = smem_base + stage * C::kStageBytes;
+          const uint64_t desc_a = umma_desc_k_sw128(sbase), desc_b = umma_desc_k_sw128(sbase + C::kOffQ);
+          const uint32_t sf_col = tmem_base + C::kSfCol0 + C::kSfCols * stage;
+          for (int ks = 0; ks < nsteps; ks++) {
+            umma_nvfp4_2sm(tmem_base, desc_a + 2 * ks, desc_b + 2 * ks, idesc, sf_col + 4 * ks, sf_col + 16 + 8 * ks, accumulate);
+            accumulate = 1;
+          }
+          umma_commit_2sm(empty0 + 8 * stage);  // frees the stage in both CTAs
+          TRACE(2, tk);
+          tk++;
+          if (++stage == STAGES) stage = 0, phase ^= 1;
+        }
+        if (ok) umma_commit_2sm(afull);
+      }
+      if (ok && ntiles > 0) mbar_wait_bounded(aempty, (ntiles - 1) & 1, abort_flag, &g_status, kStatusAccumFreeTimeout, 64, true);
+    }
+  } else if (warp >= C::kFeederWarp0) {
+    // ------------------------------------------------------------------------------------------ scale feeders
+    const uint32_t lane_base = uint32_t((warp & 3) * 32) << 16;
+    int stage = 0;
+    uint32_t phase = 0;
+    bool ok = true;
+    for (int item = pair; ok && item < items; item += npairs) {
+      for (int c = 0; c < p.chunks; c++) {
+        if (!warp_wait(full0 + 8 * stage, phase, abort_flag, &g_status, kStatusFullWaitTimeout, 32)) {
+          ok = false;
+          break;
+        }
+        const uint8_t* sb = smem + stage * C::kStageBytes;
+        const uint4* sfp = reinterpret_cast<const uint4*>(sb + C::kOffSfP) + lane;
+        const uint4* sfq = reinterpret_cast<const uint4*>(sb + C::kOffSfQ) + lane;
+        const uint32_t taddr = tmem_base + lane_base + C::kSfCol0 + C::kSfCols * stage;
+        uint4 a[4];
+#pragma unroll
+        for (int ks = 0; ks < 4; ks++) a[ks] = sfp[32 * ks];
+        tmem_st16(taddr, a);
+#pragma unroll
+        for (int h = 0; h < 2; h++) {
+#pragma unroll
+          for (int ks = 0; ks < 2; ks++) a[2 * ks] = sfq[32 * (2 * h + ks)], a[2 * ks + 1] = sfq[32 * (4 + 2 * h + ks)];
+          tmem_st16(taddr + 16 + 16 * h, a);
+        }
+        tmem_st_wait();
+        tc_fence_before_sync();
+        __syncwarp();
+        if (lane == 0) {
+          if (rank == 0) mbar_arrive(sfr0 + 8 * stage);
+          else mbar_arrive_remote(sfr0 + 8 * stage, 0);
+        }
+        if (++stage == STAGES) stage = 0, phase ^= 1;
+      }
+    }
+  } else {
+    // ------------------------------------------------------------------------------------------ epilogue
+    const int quarter = warp & 3, sub = (warp - 2) >> 2, row = quarter * 32 + lane;
+    const uint32_t taddr = tmem_base + (uint32_t(quarter * 32) << 16);
+    constexpr bool kGlu = kEpi == kEpiGluBf16;
+    constexpr int kUnits = kGlu ? 8 : 16, kMine = kUnits / 4;
+    int ntiles = 0;
+    for (int item = pair; item < items; item += npairs, ntiles++) {
+      const int m = (item % m_pairs) * 256 + int(rank) * 128 + row, n0 = (item / m_pairs) * 256;
+      if (!warp_wait(afull, ntiles & 1, abort_flag, &g_status, kStatusAccumWaitTimeout, 128)) break;
+      tc_fence_after_sync();
+      float g[kMine][16], u[kGlu ? kMine : 1][16];
+#pragma unroll
+      for (int j = 0; j < kMine; j++) {
+        const int un = sub + 4 * j, c0 = kGlu ? (un >> 2) * 128 + (un & 3) * 16 : un * 16;
+        tmem_ld16(taddr + c0, g[j]);
+        if constexpr (kGlu) tmem_ld16(taddr + 64 + c0, u[j]);
+      }
+      tmem_ld_wait();
+      tc_fence_before_sync();
+      __syncwarp();
+      if (lane == 0) {
+        if (rank == 0) mbar_arrive(aempty);
+        else mbar_arrive_remote(aempty, 0);
+      }
+#pragma unroll
+      for (int j = 0; j < kMine; j++) {
+        const int un = sub + 4 * j, c0 = kGlu ? (un >> 2) * 128 + (un & 3) * 16 : un * 16;
+        emit_many<kEpi>(p, m, m < p.M, n0, c0, g[j], u[kGlu ? j : 0]);
+      }
+    }
+  }
+
+  __syncwarp();
+  tc_fence_before_sync();
+  __syncthreads();
+  cluster_sync_all();  // nothing of either CTA goes away while the other may still signal it
+  if (warp == 1) {
+    tc_fence_after_sync();
+    tmem_dealloc_2sm(tmem_base, C::kTmemCols);
   }
 }
 
@@ -794,11 +1024,43 @@ int run_many_cfg(const uint8_t* a, const uint8_t* w, GemmParams& p, cudaStream_t
 }
 
 template <int kEpi>
+int run_many_pairs(const uint8_t* a, const uint8_t* w, GemmParams& p, cudaStream_t s) {
+  constexpr int STAGES = 5;
+  using C = Cfg2<STAGES>;
+  auto kernel = umma_gemm2_kernel<STAGES, kEpi>;
+  static bool done[64] = {};
+  int dev = 0;
+  Q27B_CUDA(cudaGetDevice(&dev));
+  if (!(dev < 64 && done[dev])) {
+    Q27B_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, C::kSmemBytes));
+    if (dev < 64) done[dev] = true;
+  }
+  CUtensorMap ma, mw;
+  if (int rc = make_operand_map(&ma, a, p.M, p.K, 128)) return rc;
+  if (int rc = make_operand_map(&mw, w, p.N, p.K, 128)) return rc;
+  const int items = ((p.M + 255) / 256) * (p.N / 256), pairs = std::min(items, sm_count() / 2);
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(2 * pairs), cfg.blockDim = dim3(C::kThreads), cfg.dynamicSmemBytes = C::kSmemBytes, cfg.stream = s;
+  cudaLaunchAttribute attr[2];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = 2, attr[0].val.clusterDim.y = 1, attr[0].val.clusterDim.z = 1;
+  attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[1].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr, cfg.numAttrs = 2;
+  Q27B_CUDA(cudaLaunchKernelEx(&cfg, kernel, ma, mw, p));
+  return 0;
+}
+
+// Which many-row kernel runs (read at every launch): Q27B_MANY=pairs|wide|narrow forces one, else the best that
+// the shape allows.
+template <int kEpi>
 int run_many(const uint8_t* a, const uint8_t* w, GemmParams& p, cudaStream_t s) {
-  // 128 x 256 tiles when the weight rows allow: one MMA of that shape keeps the tensor pipe busy for 128 of the
-  // ~140 cycles its issue takes, and every byte an SM pulls from L2 feeds 1.5 x the flops of a 128 x 128 tile.
-  // Otherwise 128 x 128 tiles on two CTAs per SM (two MMA issuers per SM; the epilogue of one overlaps the other).
-  if (p.N % 256 == 0) return run_many_cfg<256, 4, 1, kEpi>(a, w, p, s);
+  const char* e = getenv("Q27B_MANY");
+  const bool force_wide = e && !strcmp(e, "wide"), force_narrow = e && !strcmp(e, "narrow");
+  // CTA pairs, 256 x 256 tiles: least L2 traffic per flop. One CTA per 128 x 256 tile where there is less than one
+  // pair tile per SM pair to go round. 128 x 128 tiles on two CTAs per SM when the weight rows do not divide by 256.
+  if (p.N % 256 == 0 && p.M > 128 && !force_wide && !force_narrow) return run_many_pairs<kEpi>(a, w, p, s);
+  if (p.N % 256 == 0 && !force_narrow) return run_many_cfg<256, 4, 1, kEpi>(a, w, p, s);
   return run_many_cfg<128, 3, 2, kEpi>(a, w, p, s);
 }
 

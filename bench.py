@@ -227,6 +227,8 @@ def sweep_main(args, rank, world, local_rank):
         layer = {}
         for name, (codes, sfs, g, n_out, K, glu) in protos.items():
             layer[name] = Fp4Linear(codes.clone(), sfs.clone(), g, 1.0, n_out, K, glu, ws)
+        if args.fuse_qkv:
+            layer["qkv"] = Fp4Linear.fused([layer.pop("q"), layer.pop("k"), layer.pop("v")])
         model.append(layer)
     del protos
     results = {}
@@ -241,14 +243,12 @@ def sweep_main(args, rank, world, local_rank):
         outs = {name: torch.empty(M, model[0][name].out, dtype=torch.bfloat16, device="cuda") for name in model[0]}
         for layer in model:
             for name, lin in layer.items():
-                lin.in_scale, lin.alpha = (s_d if name == "down" else s_o if name == "o" else s_h), 0.0
-                lin.alpha = lin.in_scale * lin.w_scale2
-                lin._alpha[0] = lin.alpha
+                lin.set_in_scale(s_d if name == "down" else s_o if name == "o" else s_h)
 
         def sweep(_i):
             for layer in model:
                 q, sf = act_h.quantize(xh, s_h)
-                for name in ("q", "k", "v"):
+                for name in (("qkv",) if args.fuse_qkv else ("q", "k", "v")):
                     layer[name].gemm(M, q, sf, outs[name])
                 q, sf = act_h.quantize(xo, s_o)
                 layer["o"].gemm(M, q, sf, outs["o"])
@@ -273,12 +273,14 @@ def sweep_main(args, rank, world, local_rank):
         "vs_baseline": None, "dtype": "nvfp4 (e2m1 x e2m1, ue4m3 scale per 16, fp32 accumulate)", "data": "synthetic",
         "config": {"workload": f"cfg3 decode weight sweep, {layers_n} layers x (q,k,v,o,gate_up,down), M={head}",
                    "l2": "every projection of every layer in its own device memory (11.9 GB at 64 layers)",
-                   "step": "per layer: quant, q, k, v, quant, o, quant, gate_up(SiLU*mul), quant, down; 10 launches",
+                   "step": ("per layer: quant, q|k|v (one stacked weight), quant, o, quant, gate_up(SiLU*mul), quant, down; "
+                            "8 launches") if args.fuse_qkv else
+                           "per layer: quant, q, k, v, quant, o, quant, gate_up(SiLU*mul), quant, down; 10 launches",
                    "timing": "CUDA-graph replay" if not args.no_graph else "eager launches",
                    "sharding": f"N-sharded {world} way(s)"},
         "roofline": {"bound": "hbm", "achieved": r["gbs"] / world, "peak": peak, "unit": "GB/s", "frac": r["gbs"] / world / peak,
                      "traffic": None, "peak_source": peak_src, "kernel": "umma_gemm_kernel (weight streaming), whole sweep"},
-        "gpu_launches": args.steps * layers_n * 10,
+        "gpu_launches": args.steps * layers_n * (8 if args.fuse_qkv else 10),
         "sweep": {str(m): v for m, v in results.items()}}))
 
 
@@ -291,6 +293,9 @@ def main():
     ap.add_argument("--config", type=int, default=1, choices=[0, 1, 2, 3, 4])
     ap.add_argument("--m", type=int, default=0, help="configuration 3: the M to sweep at (0: all of 1..128)")
     ap.add_argument("--layers", type=int, default=64, help="configuration 3: layers in the sweep")
+    ap.add_argument("--separate-qkv", dest="fuse_qkv", action="store_false",
+                    help="configuration 3: q, k and v as three launches instead of one stacked weight with three "
+                         "alpha segments (the engine stacks projections that share an input, engine/src/weights.cc:254-267)")
     ap.add_argument("--cpu-steps", type=int, default=20)
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg (profiling runs)")
     ap.add_argument("--no-graph", action="store_true", help="time eager launches instead of a CUDA-graph replay")

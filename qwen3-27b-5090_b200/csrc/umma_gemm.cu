@@ -79,7 +79,12 @@ struct Cfg {
   static constexpr int kPBytes = 128 * 128;  // 128 rows x 256 E2M1
   static constexpr int kQBytes = NB * 128;
   static constexpr int kSfBytes = 4 * 512;   // 4 MMA steps x one 512-byte atom (per 128-row block)
-  static constexpr int kStageBytes = kPBytes + kQBytes + (1 + kQAtoms) * kSfBytes;
+  // N-side scales: whole atoms, except for a 16-row N side, whose rows sit in the first 16 lines (256 bytes) of
+  // each atom: only those are staged, which makes room for one more stage.
+  static constexpr bool kCompactSfQ = SWAP && NB == 16;
+  static constexpr int kSfQLine = kCompactSfQ ? 256 : 512;  // bytes staged per atom
+  static constexpr int kSfQBytes = kCompactSfQ ? 4 * 256 : kQAtoms * kSfBytes;
+  static constexpr int kStageBytes = kPBytes + kQBytes + kSfBytes + kSfQBytes;
   static constexpr int kOffQ = kPBytes, kOffSfP = kPBytes + kQBytes, kOffSfQ = kOffSfP + kSfBytes;
   static constexpr int kSfCols = 16 + 16 * kQAtoms;  // tensor-memory columns of one stage's scales
   static constexpr int kXchgBytes = SWAP ? 8 * 64 * 4 + 2048 : 0;  // SiLU*mul exchange between the gate and the up warps + cut-tile info
@@ -291,7 +296,9 @@ __global__ void __launch_bounds__((Cfg<NB, STAGES, CTAS, kSwap>::kThreads), CTAS
   // Weights are read once (evict first); the activations are re-read by every CTA (keep them in L2).
   const uint64_t hint_w = kEvictFirst, hint_a = kEvictLast;
   const uint64_t hint_p = kSwap ? hint_w : hint_a, hint_q = kSwap ? hint_a : hint_w;
-  auto stage_bytes = [&](int c) { return uint32_t(C::kPBytes + C::kQBytes + (1 + C::kQAtoms) * min(4, p.ksteps - 4 * c) * 512); };
+  auto stage_bytes = [&](int c) {
+    return uint32_t(C::kPBytes + C::kQBytes + min(4, p.ksteps - 4 * c) * (512 + C::kQAtoms * C::kSfQLine));
+  };
   auto load_p = [&](const Chunks& k, int stage) {
     const uint32_t sbase = smem_base + stage * C::kStageBytes, bar = full0 + 8 * stage;
     tma_load_2d(sbase, &tmap_p, k.c * 128, k.w.p_row0, bar, hint_p);
@@ -301,6 +308,13 @@ __global__ void __launch_bounds__((Cfg<NB, STAGES, CTAS, kSwap>::kThreads), CTAS
   auto load_q = [&](const Chunks& k, int stage) {
     const uint32_t sbase = smem_base + stage * C::kStageBytes, bar = full0 + 8 * stage;
     tma_load_2d(sbase + C::kOffQ, &tmap_q, k.c * 128, k.w.q_row0, bar, hint_q);
+    if constexpr (C::kCompactSfQ) {
+      const int nsteps = min(4, p.ksteps - 4 * k.c);
+      for (int ks = 0; ks < nsteps; ks++)  // the first 16 lines of each atom
+        bulk_load(sbase + C::kOffSfQ + ks * 256, p.sf_q + (int64_t(k.w.q_row0 / 128) * p.ksteps + 4 * k.c + ks) * 512, 256, bar,
+                  hint_q);
+      return;
+    }
 #pragma unroll
     for (int rb = 0; rb < C::kQAtoms; rb++)  // one run of atoms per 128-row block
       bulk_load(sbase + C::kOffSfQ + rb * C::kSfBytes, p.sf_q + (int64_t(k.w.q_row0 / 128 + rb) * p.ksteps + 4 * k.c) * 512,
@@ -440,7 +454,8 @@ __global__ void __launch_bounds__((Cfg<NB, STAGES, CTAS, kSwap>::kThreads), CTAS
       if (!warp_wait(full0 + 8 * stage, phase, abort_flag, &g_status, kStatusFullWaitTimeout, 32)) break;
       const uint8_t* sb = smem + stage * C::kStageBytes;
       const uint4* sfp = reinterpret_cast<const uint4*>(sb + C::kOffSfP) + lane;
-      const uint4* sfq = reinterpret_cast<const uint4*>(sb + C::kOffSfQ) + lane;
+      const uint4* sfq = reinterpret_cast<const uint4*>(sb + C::kOffSfQ) + (C::kCompactSfQ ? (lane & 15) : lane);
+      constexpr int kSfQStep = C::kSfQLine / 16;  // uint4 per staged atom
       const uint32_t taddr = tmem_base + lane_base + C::kSfCol0 + C::kSfCols * stage;
       uint4 a[4];
 #pragma unroll
@@ -448,7 +463,7 @@ __global__ void __launch_bounds__((Cfg<NB, STAGES, CTAS, kSwap>::kThreads), CTAS
       tmem_st16(taddr, a);
       if constexpr (C::kQAtoms == 1) {
 #pragma unroll
-        for (int ks = 0; ks < 4; ks++) a[ks] = sfq[32 * ks];
+        for (int ks = 0; ks < 4; ks++) a[ks] = sfq[kSfQStep * ks];  // (lanes past the N side: unused scale rows)
         tmem_st16(taddr + 16, a);
       } else {
         // 256-row N side: per MMA step the columns of rows 0..127, then those of rows 128..255
@@ -963,7 +978,7 @@ int run_skinny(const uint8_t* a, const uint8_t* w, GemmParams& p, cudaStream_t s
 
 template <int kEpi>
 int skinny_dispatch(const uint8_t* a, const uint8_t* w, GemmParams& p, cudaStream_t s) {
-  if (p.M <= 16) return run_skinny<16, 4, 2, kEpi>(a, w, p, s);
+  if (p.M <= 16) return run_skinny<16, 5, 2, kEpi>(a, w, p, s);
   if (p.M <= 32) return run_skinny<32, 4, 2, kEpi>(a, w, p, s);
   if (p.M <= 64) return run_skinny<64, 3, 2, kEpi>(a, w, p, s);
   return run_skinny<128, 6, 1, kEpi>(a, w, p, s);

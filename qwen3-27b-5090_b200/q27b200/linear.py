@@ -53,8 +53,38 @@ class Fp4Linear:
         # zeroed once: the head of the workspace holds arrival counters that the kernels leave at zero
         self.ws = workspace if workspace is not None else torch.zeros(WORKSPACE_BYTES, dtype=torch.uint8, device=dev)
         self._act: ActQuant | None = None
-        self._zero = (ctypes.c_int * 1)(0)
-        self._alpha = (ctypes.c_float * 1)(self.alpha)
+        self._set_segments([0], [self.alpha])
+
+    def _set_segments(self, begins, alphas):
+        # output-channel segments with their own alpha (AlphaSegments, engine/src/kernels.h:228-239): at most four
+        assert 1 <= len(begins) == len(alphas) <= 4 and begins[0] == 0
+        self._nseg = len(begins)
+        self._zero = (ctypes.c_int * self._nseg)(*begins)
+        self._alpha = (ctypes.c_float * self._nseg)(*alphas)
+
+    def set_in_scale(self, in_scale: float):
+        """A new activation tensor scale: alpha = in_scale * w_scale2 per segment."""
+        self.in_scale = float(in_scale)
+        self.alpha = self.in_scale * self.w_scale2
+        for i, g in enumerate(getattr(self, "_w_scales", [self.w_scale2])):
+            self._alpha[i] = self.in_scale * g
+
+    @classmethod
+    def fused(cls, parts: "list[Fp4Linear]"):
+        """Projections that read the same activation, stacked along the output dimension into one weight with one
+        alpha per part (the engine's fuse4, engine/src/weights.cc:254-267): one launch instead of len(parts). Each
+        part's rows are a multiple of 128, so the swizzled scale buffers concatenate as they are."""
+        assert 2 <= len(parts) <= 4 and all(not p.glu and p.inp == parts[0].inp and p.rows() % 128 == 0 for p in parts)
+        codes = torch.cat([p.w for p in parts]).contiguous()
+        sfs = torch.cat([p.sf for p in parts]).contiguous()
+        f = cls(codes, sfs, parts[0].w_scale2, parts[0].in_scale, codes.shape[0], parts[0].inp, False, parts[0].ws)
+        begins, row = [], 0
+        for p in parts:
+            begins.append(row)
+            row += p.rows()
+        f._w_scales = [p.w_scale2 for p in parts]
+        f._set_segments(begins, [f.in_scale * g for g in f._w_scales])
+        return f
 
     @classmethod
     def from_float(cls, w: torch.Tensor, in_scale: float, glu: bool = False, device="cuda", workspace=None):
@@ -104,14 +134,16 @@ class Fp4Linear:
         elif out.dtype == torch.bfloat16:
             assert residual is None
             if skinny:
-                call("q27b_skinny_fp4_bf16", M, N, K, q, sf, self.w, self.sf, 1, self._zero, self._alpha, out, self.ws,
+                call("q27b_skinny_fp4_bf16", M, N, K, q, sf, self.w, self.sf, self._nseg, self._zero, self._alpha, out, self.ws,
                      self.ws.numel(), s)
             else:
+                assert self._nseg == 1, "the many-row GEMM takes one alpha"
                 call("q27b_gemm_fp4_bf16", M, N, K, q, sf, self.w, self.sf, self.alpha, out, s)
         else:
             beta = 1.0 if residual is not None else 0.0
             if skinny:
-                call("q27b_skinny_fp4", M, N, K, q, sf, self.w, self.sf, 1, self._zero, self._alpha, residual, beta, out,
+                call("q27b_skinny_fp4", M, N, K, q, sf, self.w, self.sf, self._nseg, self._zero, self._alpha, residual, beta, out,
                      self.ws, self.ws.numel(), s)
             else:
+                assert self._nseg == 1, "the many-row GEMM takes one alpha"
                 call("q27b_gemm_fp4", M, N, K, q, sf, self.w, self.sf, self.alpha, residual, beta, out, s)

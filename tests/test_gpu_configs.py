@@ -178,3 +178,31 @@ def test_cfg4_prefill_gate_up(gate_up):
         assert (small != big).float().mean().item() < 1e-2
         assert rel_err(bf16_to_f32(small), bf16_to_f32(big)) < 1e-3
     assert torch.isfinite(y.float()).all()
+
+
+@pytest.mark.parametrize("M", [1, 16, 64])
+def test_fused_qkv_equals_separate_projections(M):
+    """q, k and v stacked into one weight with one alpha per part (the engine's fuse4): every part of the fused
+    output meets the acceptance rule against the oracle of its own projection, and the fp32 results agree with
+    the separate launches to fp32 summation-order level."""
+    x = configs.make_x(configs.GemmConfig(3, "qkv", M, configs.HIDDEN, configs.HIDDEN, False), seed=17)
+    s = configs.input_scale_of(x)
+    parts, refs = [], []
+    for pi, (name, N, K, glu) in enumerate(configs.LAYER_PROJECTIONS[:3]):
+        cfg = configs.GemmConfig(3, name, M, N, K, glu)
+        codes, sfb, g = build(cfg, 2000 + pi)
+        parts.append(layer_from(codes, sfb, g, s, False, cfg))
+        refs.append(oracle_rows(x, codes, sfb, g, s))
+    fused = Fp4Linear.fused(parts)
+    assert fused.rows() == 5120 + 1024 + 1024
+    y = fused(x.to(DEV))
+    y32 = fused(x.to(DEV), out_dtype=torch.float32)
+    assert torch.equal(y, y32.bfloat16())
+    row = 0
+    for lin, ref in zip(parts, refs):
+        n = lin.rows()
+        assert_within(bf16_to_f32(y[:, row:row + n]), ref)
+        assert_within(y32[:, row:row + n].cpu().numpy(), ref, stored_bf16=False)
+        sep = lin(x.to(DEV), out_dtype=torch.float32).cpu().numpy()
+        assert rel_err(y32[:, row:row + n].cpu().numpy(), sep) < 1e-5
+        row += n

@@ -6,13 +6,20 @@ projection (x bf16 [16, 5120], W NVFP4 [34816, 5120], SiLU*mul -> bf16 [16, 1740
 rows are sharded N ways (every rank computes its block of output columns, no reduction) and one NCCL all-gather
 of the bf16 output is timed separately.
 
-    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--config 0|1|2|4]
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--config 0|1|2|3|4]
+                    [--m M] [--layers L] [--separate-qkv] [--no-graph] [--no-cpu]
 
 Prints one JSON line (rank 0). `value` = algorithmic bytes of the step / device time with everything resident in
-HBM and the weights rotating through more than L2-size of distinct copies; `e2e` = the same step through the host
-API with the activation coming from pinned host memory and the result copied back, copies inside the timed
-region. `--impl reference` times the CPU restatement of the reference's own path (fake-quantise, fp32 matmul
-against the dequantised weight, SiLU*mul) on the host cores instead.
+HBM and the weights rotating through more than L2-size of distinct copies (the steps are replayed from a CUDA
+graph unless --no-graph); `e2e` = the same step through the host API with the activation coming from pinned host
+memory and the result copied back to pinned host memory every step, copies inside the timed region. `--impl
+reference` times the CPU restatement of the reference's own path (fake-quantise, fp32 matmul against the
+dequantised weight, SiLU*mul) on the host cores instead.
+
+--config 0 / 2 / 4 run the other single-GEMM configurations (decode GEMV, batched verify down-projection, prefill
+chunk: reported in TFLOP/s against the tensor roof). --config 3 is the whole-model decode weight sweep: 64 layers
+(--layers) x {q|k|v stacked, o, gate_up, down} at M = 1 ... 128 (--m for one M), every projection in its own
+device memory; its line carries the GB/s of every M under "sweep".
 """
 
 from __future__ import annotations
@@ -128,7 +135,7 @@ def max_over_ranks(ms, world):
     return float(t.item())
 
 
-def timed(fn, steps, warmup, world, graph=False):
+def timed(fn, steps, warmup, world, graph=False, after=None):
     """`steps` calls of fn(i) bracketed by a barrier + synchronize, timed with CUDA events on the current stream
     (the stream every launch of the library goes to); max over ranks, in ms. graph=True: the steps are captured
     once into a CUDA graph and the timed region is its replay, so that the host's launch cost (two ctypes calls
@@ -157,6 +164,8 @@ def timed(fn, steps, warmup, world, graph=False):
     else:
         for i in range(steps):
             fn(warmup + i)
+    if after:
+        after()  # e.g. make the timed stream wait for work the steps put on another stream
     e1.record()
     sync_all(world)
     return max_over_ranks(e0.elapsed_time(e1), world)
@@ -359,14 +368,31 @@ def main():
 
     # host-facing step: pinned host activation in, result back to pinned host memory
     xh = x.pin_memory()
-    yh = torch.empty(M, n_local, dtype=torch.bfloat16).pin_memory()
-    xdev = torch.empty_like(xd)
+    yh = [torch.empty(M, n_local, dtype=torch.bfloat16).pin_memory() for _ in range(2)]
+    xdev = [torch.empty_like(xd) for _ in range(2)]
+    copy_stream = torch.cuda.Stream()
+    computed = [torch.cuda.Event() for _ in range(2)]
+    copied = [torch.cuda.Event() for _ in range(2)]
+
+    def step_e2e_sync(i):  # latency form: the caller waits for every result before the next step
+        xdev[0].copy_(xh, non_blocking=True)
+        layers[i % nbuf](xdev[0], out=outs[0])
+        yh[0].copy_(outs[0], non_blocking=True)
+        torch.cuda.current_stream().synchronize()
 
     def step_e2e(i):
-        xdev.copy_(xh, non_blocking=True)
-        layers[i % nbuf](xdev, out=outs[i & 1])
-        yh.copy_(outs[i & 1], non_blocking=True)
-        torch.cuda.current_stream().synchronize()  # the caller reads the result
+        # throughput form: every step copies its input in, computes, and copies its result out; the copy back runs
+        # on a second stream so that it overlaps the next step (two buffers of everything), nothing waits on the host
+        b = i & 1
+        main = torch.cuda.current_stream()
+        main.wait_event(copied[b])  # the result buffer of step i - 2 has been read out
+        xdev[b].copy_(xh, non_blocking=True)
+        layers[i % nbuf](xdev[b], out=outs[b])
+        computed[b].record(main)
+        copy_stream.wait_event(computed[b])
+        with torch.cuda.stream(copy_stream):
+            yh[b].copy_(outs[b], non_blocking=True)
+            copied[b].record(copy_stream)
 
     gathered = torch.empty(world, M, n_local, dtype=torch.bfloat16, device="cuda") if world > 1 else None
 
@@ -382,7 +408,13 @@ def main():
                 timed(step, args.steps, 0, world, False)
     ms_gemm = timed(gemm_only, args.steps, args.warmup, world, graph)
     ms_eager = timed(step, args.steps, args.warmup, world, False)
-    ms_e2e = timed(step_e2e, args.steps, args.warmup, world)
+
+    def e2e_join():  # the timed region ends when the last results have reached the host buffers
+        for ev in copied:
+            torch.cuda.current_stream().wait_event(ev)
+
+    ms_e2e = timed(step_e2e, args.steps, args.warmup, world, after=e2e_join)
+    ms_e2e_sync = timed(step_e2e_sync, args.steps, args.warmup, world)
     ms_gather = timed(step_gather, args.steps, args.warmup, world) if world > 1 else None
     assert device_status() == 0, "a bounded wait inside a kernel ran out"
     clocks = clk.summary()
@@ -430,7 +462,9 @@ def main():
                    "step": "quant_fp4_bf16 + skinny_fp4_glu_bf16" if M <= 128 else "quant_fp4_bf16 + gemm_fp4_glu_bf16",
                    "timing": "CUDA-graph replay of the timed steps" if graph else "eager launches", "eager_ms_per_step": ms_eager / args.steps},
         "e2e": {"value": val(e2e_s), "unit": unit, "h2d_bytes_per_step": x.numel() * 2, "d2h_bytes_per_step": M * n_local * 2,
-                "ms_per_step": ms_e2e / args.steps},
+                "ms_per_step": ms_e2e / args.steps, "ms_per_step_host_waits_each_result": ms_e2e_sync / args.steps,
+                "how": "per step: pinned host activation -> device, quantise + GEMM, result -> pinned host (second stream, "
+                       "overlapping the next step); eager launches through Fp4Linear"},
         "gpu_launches": args.steps * 2,  # quantiser + GEMM
         "roofline": roof,
         "clocks": clocks,

@@ -118,6 +118,14 @@ int q27b_gemm_fp4_bf16(int M, int N, int K, const uint8_t* a, const uint8_t* a_s
  * benchmark configurations ask for instead of re-quantised NVFP4. */
 int q27b_gemm_fp4_glu_bf16(int M, int I, int K, const uint8_t* a, const uint8_t* a_sf, const uint8_t* gate_up,
                            const uint8_t* gate_up_sf, float alpha_gate, float alpha_up, void* d, void* stream);
+/* gate | up GEMM on interleaved weights with silu(alpha_gate * gate) * (alpha_up * up) quantised to NVFP4 in the
+ * epilogue: q [M][I / 2] codes and q_sf swizzled scales ([M rows][I / 16 blocks]) are the activation of the down
+ * GEMM, quantised with the tensor scale out_scale; gate and up are never rounded to bf16. Replaces gemm_fp4_glu
+ * (engine/src/kernels.h:216-221, engine/src/gemm_mma.cu:350-399,646-652). Scale bytes of rows past M inside the
+ * last 128-row atom are left untouched. */
+int q27b_gemm_fp4_glu(int M, int I, int K, const uint8_t* a, const uint8_t* a_sf, const uint8_t* gate_up,
+                      const uint8_t* gate_up_sf, float alpha_gate, float alpha_up, float out_scale, uint8_t* q,
+                      uint8_t* q_sf, void* stream);
 
 /* ---- diagnostics -------------------------------------------------------------------------------------------------- */
 
@@ -158,6 +166,9 @@ int q27t_gemm_fp4_bf16(int M, int N, int K, const uint8_t* a, const uint8_t* a_s
                        const uint8_t* b_sf, float alpha, void* d);                      /* capi.cc:539-542 */
 int q27t_gemm_fp4_glu_bf16(int M, int I, int K, const uint8_t* a, const uint8_t* a_sf, const uint8_t* gate_up,
                            const uint8_t* gate_up_sf, float alpha_gate, float alpha_up, void* d);
+int q27t_gemm_fp4_glu(int M, int I, int K, const uint8_t* a, const uint8_t* a_sf, const uint8_t* gate_up,
+                      const uint8_t* gate_up_sf, float alpha_gate, float alpha_up, float out_scale, uint8_t* q,
+                      uint8_t* q_sf);                                                  /* capi.cc:570-574 */
 int q27t_skinny_fp4(int M, int N, int K, const uint8_t* a, const uint8_t* a_sf, const uint8_t* w, const uint8_t* w_sf,
                     float alpha, const float* c, float beta, float* d, void* ws, size_t ws_bytes); /* capi.cc:599-602 */
 int q27t_skinny_fp4_segments(int M, int N, int K, const uint8_t* a, const uint8_t* a_sf, const uint8_t* w,

@@ -47,6 +47,11 @@ void gemm_fp4_bf16(int M, int N, int K, const uint8_t* a, const uint8_t* a_sf, c
 // form of gemm_fp4_glu, engine/src/kernels.h:216-221).
 void gemm_fp4_glu_bf16(int M, int I, int K, const uint8_t* a, const uint8_t* a_sf, const uint8_t* gate_up,
                        const uint8_t* gate_up_sf, float alpha_gate, float alpha_up, bf16* d, cudaStream_t s);
+// engine/src/kernels.h:216-221: the same GEMM with silu(gate) * up quantised to NVFP4 (q, q_sf: the down GEMM's
+// activation, tensor scale out_scale).
+void gemm_fp4_glu(int M, int I, int K, const uint8_t* a, const uint8_t* a_sf, const uint8_t* gate_up,
+                  const uint8_t* gate_up_sf, float alpha_gate, float alpha_up, float out_scale, uint8_t* q,
+                  uint8_t* q_sf, cudaStream_t s);
 
 // engine/src/kernels.h:228-245
 struct AlphaSegments {

@@ -50,6 +50,11 @@ void gemm_fp4_glu_bf16(int M, int I, int K, const uint8_t* a, const uint8_t* a_s
                        const uint8_t* gate_up_sf, float alpha_gate, float alpha_up, bf16* d, cudaStream_t s) {
   check(q27b_gemm_fp4_glu_bf16(M, I, K, a, a_sf, gate_up, gate_up_sf, alpha_gate, alpha_up, d, s));
 }
+void gemm_fp4_glu(int M, int I, int K, const uint8_t* a, const uint8_t* a_sf, const uint8_t* gate_up,
+                  const uint8_t* gate_up_sf, float alpha_gate, float alpha_up, float out_scale, uint8_t* q,
+                  uint8_t* q_sf, cudaStream_t s) {
+  check(q27b_gemm_fp4_glu(M, I, K, a, a_sf, gate_up, gate_up_sf, alpha_gate, alpha_up, out_scale, q, q_sf, s));
+}
 void skinny_fp4(int M, int N, int K, const uint8_t* a, const uint8_t* a_sf, const uint8_t* w, const uint8_t* w_sf,
                 const AlphaSegments& alpha, const float* c, float beta, float* d, void* ws, size_t ws_bytes,
                 cudaStream_t s) {

@@ -6,29 +6,15 @@
 //   code = rne_e2m1(x * inv)   (ties to the even code, saturating at +-6)
 // with every operation a separate IEEE fp32 operation (no contraction, no fast-math). Codes are packed two per
 // byte, even column in the low nibble; scales go to the swizzled 128 x 4 atom layout (layout.h).
-#include <cuda_fp8.h>
-
 #include "common.cuh"
 #include "layout.h"
 #include "ptx_sm100.cuh"
+#include "quant_block.cuh"
 
 namespace q27b {
 namespace {
 
 constexpr int kThreads = 256;
-
-// Two values -> one byte of E2M1 codes, `even` in the low nibble.
-__device__ __forceinline__ uint32_t e2m1x2(float even, float odd) {
-  uint16_t r;
-  asm("{\n\t.reg .b8 t;\n\tcvt.rn.satfinite.e2m1x2.f32 t, %1, %2;\n\tcvt.u16.u8 %0, t;\n\t}"
-      : "=h"(r)
-      : "f"(odd), "f"(even));
-  return r;
-}
-
-__device__ __forceinline__ float e4m3_to_float(__nv_fp8_storage_t c) {
-  return __half2float(__half(__nv_cvt_fp8_to_halfraw(c, __NV_E4M3)));
-}
 
 __device__ __forceinline__ void load16(const float* p, float* v) {
   const float4* s = reinterpret_cast<const float4*>(p);
@@ -51,26 +37,6 @@ __device__ __forceinline__ void load16(const __nv_bfloat16* p, float* v) {
       v[8 * j + 2 * k + 1] = __uint_as_float(w[k] & 0xFFFF0000u);
     }
   }
-}
-
-// One 16-element block (row m, k-block kb) of an [M][K] activation.
-__device__ __forceinline__ void quant_block16(const float* v, float input_scale, int m, int kb, int K, uint8_t* q,
-                                              uint8_t* sf) {
-  float amax = 0.f;
-#pragma unroll
-  for (int j = 0; j < 16; j++) amax = fmaxf(amax, fabsf(v[j]));
-  const float gs = __fdiv_rn(1.f, input_scale);
-  const __nv_fp8_storage_t sfq = __nv_cvt_float_to_fp8(__fdiv_rn(__fmul_rn(gs, amax), 6.f), __NV_SATFINITE, __NV_E4M3);
-  const float sff = e4m3_to_float(sfq);
-  const float inv = sff != 0.f ? __fdiv_rn(gs, sff) : 0.f;
-  uint32_t lo = 0, hi = 0;
-#pragma unroll
-  for (int j = 0; j < 4; j++) {
-    lo |= e2m1x2(__fmul_rn(v[2 * j], inv), __fmul_rn(v[2 * j + 1], inv)) << (8 * j);
-    hi |= e2m1x2(__fmul_rn(v[8 + 2 * j], inv), __fmul_rn(v[9 + 2 * j], inv)) << (8 * j);
-  }
-  *reinterpret_cast<uint2*>(q + int64_t(m) * (K / 2) + kb * 8) = make_uint2(lo, hi);
-  sf[sf_offset(m, kb, K / 16)] = sfq;
 }
 
 template <typename E>

@@ -32,6 +32,7 @@
 #include "common.cuh"
 #include "layout.h"
 #include "ptx_sm100.cuh"
+#include "quant_block.cuh"
 
 namespace q27b {
 
@@ -41,7 +42,8 @@ unsigned long long* g_trace = nullptr;  // optional device buffer for in-kernel 
 
 namespace {
 
-enum Epi : int { kEpiF32 = 0, kEpiBf16 = 1, kEpiGluBf16 = 2 };
+enum Epi : int { kEpiF32 = 0, kEpiBf16 = 1, kEpiGluBf16 = 2, kEpiGluFp4 = 3 };
+constexpr bool epi_is_glu(int e) { return e == kEpiGluBf16 || e == kEpiGluFp4; }
 
 // warp 0: TMA producer, 1: MMA issuer, then the epilogue warps (4, or 16 where a big tile is drained by one CTA
 // alone), then 4 scale feeders
@@ -58,7 +60,9 @@ struct GemmParams {
   float alpha_up;
   const float* c;       // residual (may alias d) or null
   float beta;
-  void* d;              // fp32 or bf16 output
+  void* d;              // fp32 or bf16 output; NVFP4 epilogue: E2M1 codes [M][N / 4]
+  uint8_t* d_sf;        // NVFP4 epilogue: swizzled scales of the output, [M rows][N / 32 blocks]
+  float out_gs;         // NVFP4 epilogue: 1 / (tensor scale of the output)
   int* counters;        // weight streaming: arrivals per cut tile (zero between calls)
   float* partials;      // weight streaming: per-CTA partial tiles [2 * grid][M][128]
   SkinnyPlan plan;      // weight streaming
@@ -79,12 +83,7 @@ struct Cfg {
   static constexpr int kPBytes = 128 * 128;  // 128 rows x 256 E2M1
   static constexpr int kQBytes = NB * 128;
   static constexpr int kSfBytes = 4 * 512;   // 4 MMA steps x one 512-byte atom (per 128-row block)
-  // N-side scales: whole atoms, except for a 16-row N side, whose rows sit in the first 16 lines (256 bytes) of
-  // each atom: only those are staged, which makes room for one more stage.
-  static constexpr bool kCompactSfQ = SWAP && NB == 16;
-  static constexpr int kSfQLine = kCompactSfQ ? 256 : 512;  // bytes staged per atom
-  static constexpr int kSfQBytes = kCompactSfQ ? 4 * 256 : kQAtoms * kSfBytes;
-  static constexpr int kStageBytes = kPBytes + kQBytes + kSfBytes + kSfQBytes;
+  static constexpr int kStageBytes = kPBytes + kQBytes + (1 + kQAtoms) * kSfBytes;
   static constexpr int kOffQ = kPBytes, kOffSfP = kPBytes + kQBytes, kOffSfQ = kOffSfP + kSfBytes;
   static constexpr int kSfCols = 16 + 16 * kQAtoms;  // tensor-memory columns of one stage's scales
   static constexpr int kXchgBytes = SWAP ? 8 * 64 * 4 + 2048 : 0;  // SiLU*mul exchange between the gate and the up warps + cut-tile info
@@ -241,7 +240,20 @@ template <int kEpi>
 __device__ __forceinline__ void emit_many(const GemmParams& p, int m, bool valid, int q_row0, int c0, const float* g,
                                           const float* u) {
   if (!valid) return;
-  if constexpr (kEpi == kEpiGluBf16) {
+  if constexpr (kEpi == kEpiGluFp4) {
+    // silu(gate) * up in fp32 (never rounded to bf16), then the activation quantiser's block arithmetic: the 16
+    // outputs are one NVFP4 block of the next GEMM's activation (engine/src/gemm_mma.cu:350-399).
+    const float ag = p.alpha.alpha[0], au = p.alpha_up;
+    float v[16];
+#pragma unroll
+    for (int j = 0; j < 16; j++) v[j] = silu_mul(__fmul_rn(ag, g[j]), __fmul_rn(au, u[j]));
+    uint32_t lo, hi;
+    uint8_t sfq;
+    quant_block16_codes(v, p.out_gs, lo, hi, sfq);
+    const int I = p.N / 2, o0 = (q_row0 + c0) / 2 + (c0 & 63) / 2;  // first of the 16 output channels
+    *reinterpret_cast<uint2*>(static_cast<uint8_t*>(p.d) + int64_t(m) * (I / 2) + o0 / 2) = make_uint2(lo, hi);
+    p.d_sf[sf_offset(m, o0 / 16, I / 16)] = sfq;
+  } else if constexpr (kEpi == kEpiGluBf16) {
     const float ag = p.alpha.alpha[0], au = p.alpha_up;
     uint32_t pk[8];
 #pragma unroll
@@ -296,9 +308,7 @@ __global__ void __launch_bounds__((Cfg<NB, STAGES, CTAS, kSwap>::kThreads), CTAS
   // Weights are read once (evict first); the activations are re-read by every CTA (keep them in L2).
   const uint64_t hint_w = kEvictFirst, hint_a = kEvictLast;
   const uint64_t hint_p = kSwap ? hint_w : hint_a, hint_q = kSwap ? hint_a : hint_w;
-  auto stage_bytes = [&](int c) {
-    return uint32_t(C::kPBytes + C::kQBytes + min(4, p.ksteps - 4 * c) * (512 + C::kQAtoms * C::kSfQLine));
-  };
+  auto stage_bytes = [&](int c) { return uint32_t(C::kPBytes + C::kQBytes + (1 + C::kQAtoms) * min(4, p.ksteps - 4 * c) * 512); };
   auto load_p = [&](const Chunks& k, int stage) {
     const uint32_t sbase = smem_base + stage * C::kStageBytes, bar = full0 + 8 * stage;
     tma_load_2d(sbase, &tmap_p, k.c * 128, k.w.p_row0, bar, hint_p);
@@ -308,13 +318,6 @@ __global__ void __launch_bounds__((Cfg<NB, STAGES, CTAS, kSwap>::kThreads), CTAS
   auto load_q = [&](const Chunks& k, int stage) {
     const uint32_t sbase = smem_base + stage * C::kStageBytes, bar = full0 + 8 * stage;
     tma_load_2d(sbase + C::kOffQ, &tmap_q, k.c * 128, k.w.q_row0, bar, hint_q);
-    if constexpr (C::kCompactSfQ) {
-      const int nsteps = min(4, p.ksteps - 4 * k.c);
-      for (int ks = 0; ks < nsteps; ks++)  // the first 16 lines of each atom
-        bulk_load(sbase + C::kOffSfQ + ks * 256, p.sf_q + (int64_t(k.w.q_row0 / 128) * p.ksteps + 4 * k.c + ks) * 512, 256, bar,
-                  hint_q);
-      return;
-    }
 #pragma unroll
     for (int rb = 0; rb < C::kQAtoms; rb++)  // one run of atoms per 128-row block
       bulk_load(sbase + C::kOffSfQ + rb * C::kSfBytes, p.sf_q + (int64_t(k.w.q_row0 / 128 + rb) * p.ksteps + 4 * k.c) * 512,
@@ -454,8 +457,7 @@ __global__ void __launch_bounds__((Cfg<NB, STAGES, CTAS, kSwap>::kThreads), CTAS
       if (!warp_wait(full0 + 8 * stage, phase, abort_flag, &g_status, kStatusFullWaitTimeout, 32)) break;
       const uint8_t* sb = smem + stage * C::kStageBytes;
       const uint4* sfp = reinterpret_cast<const uint4*>(sb + C::kOffSfP) + lane;
-      const uint4* sfq = reinterpret_cast<const uint4*>(sb + C::kOffSfQ) + (C::kCompactSfQ ? (lane & 15) : lane);
-      constexpr int kSfQStep = C::kSfQLine / 16;  // uint4 per staged atom
+      const uint4* sfq = reinterpret_cast<const uint4*>(sb + C::kOffSfQ) + lane;
       const uint32_t taddr = tmem_base + lane_base + C::kSfCol0 + C::kSfCols * stage;
       uint4 a[4];
 #pragma unroll
@@ -463,7 +465,7 @@ __global__ void __launch_bounds__((Cfg<NB, STAGES, CTAS, kSwap>::kThreads), CTAS
       tmem_st16(taddr, a);
       if constexpr (C::kQAtoms == 1) {
 #pragma unroll
-        for (int ks = 0; ks < 4; ks++) a[ks] = sfq[kSfQStep * ks];  // (lanes past the N side: unused scale rows)
+        for (int ks = 0; ks < 4; ks++) a[ks] = sfq[32 * ks];
         tmem_st16(taddr + 16, a);
       } else {
         // 256-row N side: per MMA step the columns of rows 0..127, then those of rows 128..255
@@ -566,7 +568,7 @@ __global__ void __launch_bounds__((Cfg<NB, STAGES, CTAS, kSwap>::kThreads), CTAS
         // lane = token, column = output channel
         const int m = w.p_row0 + row;
         const bool valid = m < p.M;
-        constexpr bool kGlu = kEpi == kEpiGluBf16;
+        constexpr bool kGlu = epi_is_glu(kEpi);
         auto emit = [&](int c0, const float* g, const float* u) { emit_many<kEpi>(p, m, valid, w.q_row0, c0, g, u); };
         // first column of the u-th unit of 16 outputs: plain 16 u; SiLU*mul: 4 gate units per 128-row block
         auto unit_col = [&](int u) { return kGlu ? (u >> 2) * 128 + (u & 3) * 16 : u * 16; };
@@ -807,7 +809,7 @@ __global__ void __launch_bounds__(Cfg2<STAGES>::kThreads, 1) umma_gemm2_kernel(c
     // ------------------------------------------------------------------------------------------ epilogue
     const int quarter = warp & 3, sub = (warp - 2) >> 2, row = quarter * 32 + lane;
     const uint32_t taddr = tmem_base + (uint32_t(quarter * 32) << 16);
-    constexpr bool kGlu = kEpi == kEpiGluBf16;
+    constexpr bool kGlu = epi_is_glu(kEpi);
     constexpr int kUnits = kGlu ? 8 : 16, kMine = kUnits / 4;
     int ntiles = 0;
     for (int item = pair; item < items; item += npairs, ntiles++) {
@@ -978,7 +980,7 @@ int run_skinny(const uint8_t* a, const uint8_t* w, GemmParams& p, cudaStream_t s
 
 template <int kEpi>
 int skinny_dispatch(const uint8_t* a, const uint8_t* w, GemmParams& p, cudaStream_t s) {
-  if (p.M <= 16) return run_skinny<16, 5, 2, kEpi>(a, w, p, s);
+  if (p.M <= 16) return run_skinny<16, 4, 2, kEpi>(a, w, p, s);
   if (p.M <= 32) return run_skinny<32, 4, 2, kEpi>(a, w, p, s);
   if (p.M <= 64) return run_skinny<64, 3, 2, kEpi>(a, w, p, s);
   return run_skinny<128, 6, 1, kEpi>(a, w, p, s);
@@ -1080,7 +1082,8 @@ int run_many(const uint8_t* a, const uint8_t* w, GemmParams& p, cudaStream_t s) 
 }
 
 int many_common(int kEpi, int M, int N, int K, const uint8_t* a, const uint8_t* a_sf, const uint8_t* w,
-                const uint8_t* w_sf, float alpha, float alpha_up, const float* c, float beta, void* d, cudaStream_t s) {
+                const uint8_t* w_sf, float alpha, float alpha_up, const float* c, float beta, void* d, cudaStream_t s,
+                uint8_t* d_sf = nullptr, float out_scale = 1.f) {
   Q27B_REQUIRE(M >= 0, "gemm_fp4: M must not be negative");
   if (M == 0) return 0;
   if (int rc = check_operands("gemm_fp4", M, N, K, a, a_sf, w, w_sf, d)) return rc;
@@ -1091,10 +1094,12 @@ int many_common(int kEpi, int M, int N, int K, const uint8_t* a, const uint8_t* 
   p.sf_p = a_sf, p.sf_q = w_sf, p.alpha.count = 1, p.alpha.alpha[0] = alpha, p.alpha_up = alpha_up;
   p.c = (c && beta != 0.f) ? c : nullptr, p.beta = beta, p.d = d;
   p.m_tiles = (M + 127) / 128;
+  p.d_sf = d_sf, p.out_gs = 1.f / out_scale;  // (IEEE division, as the quantiser kernels compute it)
   p.trace = g_trace;
   switch (kEpi) {
     case kEpiF32: return run_many<kEpiF32>(a, w, p, s);
     case kEpiBf16: return run_many<kEpiBf16>(a, w, p, s);
+    case kEpiGluFp4: return run_many<kEpiGluFp4>(a, w, p, s);
     default: return run_many<kEpiGluBf16>(a, w, p, s);
   }
 }
@@ -1168,6 +1173,15 @@ int q27b_gemm_fp4_glu_bf16(int M, int I, int K, const uint8_t* a, const uint8_t*
   Q27B_REQUIRE(I > 0 && I % 64 == 0, "gemm_fp4_glu_bf16: I must be a positive multiple of 64 (I = %d)", I);
   return many_common(kEpiGluBf16, M, 2 * I, K, a, a_sf, gate_up, gate_up_sf, alpha_gate, alpha_up, nullptr, 0.f, d,
                      static_cast<cudaStream_t>(stream));
+}
+int q27b_gemm_fp4_glu(int M, int I, int K, const uint8_t* a, const uint8_t* a_sf, const uint8_t* gate_up,
+                      const uint8_t* gate_up_sf, float alpha_gate, float alpha_up, float out_scale, uint8_t* q,
+                      uint8_t* q_sf, void* stream) {
+  Q27B_REQUIRE(I > 0 && I % 64 == 0, "gemm_fp4_glu: I must be a positive multiple of 64 (I = %d)", I);
+  Q27B_REQUIRE(q_sf && aligned16(q_sf), "gemm_fp4_glu: the output scales must be a 16-byte aligned device buffer");
+  Q27B_REQUIRE(out_scale > 0.f, "gemm_fp4_glu: out_scale must be positive");
+  return many_common(kEpiGluFp4, M, 2 * I, K, a, a_sf, gate_up, gate_up_sf, alpha_gate, alpha_up, nullptr, 0.f, q,
+                     static_cast<cudaStream_t>(stream), q_sf, out_scale);
 }
 
 int q27b_trace_set(void* buf) { g_trace = static_cast<unsigned long long*>(buf); return 0; }

@@ -35,6 +35,7 @@ SIGNATURES = {
     "q27b_gemm_fp4": ([I, I, I, P, P, P, P, F, P, F, P, P], I),
     "q27b_gemm_fp4_bf16": ([I, I, I, P, P, P, P, F, P, P], I),
     "q27b_gemm_fp4_glu_bf16": ([I, I, I, P, P, P, P, F, F, P, P], I),
+    "q27b_gemm_fp4_glu": ([I, I, I, P, P, P, P, F, F, F, P, P, P], I),
     "q27b_device_status": ([U32P], I),
     "q27b_ref_gemm_fp4": ([I, I, I, P, P, P, P, F, P, P], I),
     "q27b_skinny_plan": ([I, I, I, I, P, I, P, P, P], I),
@@ -52,6 +53,7 @@ SIGNATURES = {
     "q27t_gemm_fp4": ([I, I, I, P, P, P, P, F, P, F, P], I),
     "q27t_gemm_fp4_bf16": ([I, I, I, P, P, P, P, F, P], I),
     "q27t_gemm_fp4_glu_bf16": ([I, I, I, P, P, P, P, F, F, P], I),
+    "q27t_gemm_fp4_glu": ([I, I, I, P, P, P, P, F, F, F, P, P], I),
     "q27t_skinny_fp4": ([I, I, I, P, P, P, P, F, P, F, P, P, SZ], I),
     "q27t_skinny_fp4_segments": ([I, I, I, P, P, P, P, I, P, P, P, F, P, P, SZ], I),
     "q27t_skinny_fp4_bf16": ([I, I, I, P, P, P, P, F, P, P, SZ], I),

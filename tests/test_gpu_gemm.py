@@ -9,7 +9,7 @@ import torch
 from helpers import DEV, bf16_to_f32, dev, fp4_operand, rel_err, swizzled_dev, workspace
 from oracle import nvfp4_oracle as O
 from q27b200 import layouts
-from q27b200.q27lib import call
+from q27b200.q27lib import call, lib
 
 pytestmark = pytest.mark.gpu
 
@@ -74,3 +74,56 @@ def test_gemm_fp4_glu_bf16(M, I, K):
         ds = torch.zeros_like(d)
         call("q27t_skinny_fp4_glu_bf16", M, I, K, ad, asw, wid, wsw, ag, au, ds, ws, ws.numel())
         assert (ds != d).float().mean().item() < 1e-2 and rel_err(bf16_to_f32(ds), out) < 1e-3
+
+
+def _nibbles(q):
+    return torch.stack([q & 15, q >> 4], -1)
+
+
+def _code_mismatch(q, q_ref):
+    """Share of E2M1 codes that differ, the two zero codes taken as equal (its sign is unpinned in the reference)."""
+    a, b = _nibbles(q), _nibbles(q_ref)
+    a, b = torch.where(a == 8, torch.zeros_like(a), a), torch.where(b == 8, torch.zeros_like(b), b)
+    return (a != b).float().mean().item()
+
+
+@pytest.mark.parametrize("M", [1, 77, 300, 2048])
+@pytest.mark.parametrize("I,K", [(384, 5120), (17408, 5120)])
+def test_gemm_fp4_glu_nvfp4_out(M, I, K):
+    """gate | up GEMM (interleaved weights) with silu(gate) * up quantised to NVFP4 in the epilogue, against the
+    separate path (fp32 GEMM, then silu_mul_quant_fp4_glu) and against the CPU oracle. The fused epilogue uses the
+    fast exponential and reciprocal and its own accumulation order, so a value on a rounding boundary may land in
+    the next code: the reference's bounds apply (engine/tests/test_gemm.py:59-96: < 1e-3 of the scales, < 2e-3 of
+    the codes)."""
+    rng = np.random.RandomState(M + I + 1)
+    a, asf, adq = fp4_operand(M, K, rng)
+    w, wsf, wdq = fp4_operand(2 * I, K, rng)  # gate rows, then up rows
+    wi, wsfi = layouts.interleave_glu(w), layouts.interleave_glu(wsf)
+    ad, asw, wid, wsw = dev(a), swizzled_dev(asf), dev(wi), swizzled_dev(wsfi)
+    ag, au, out_scale = 0.013, 0.021, 0.05
+    sfb = lib().q27t_sf_bytes(M, I // 16)
+
+    def out():
+        return torch.zeros(M, I // 2, dtype=torch.uint8, device=DEV), torch.zeros(sfb, dtype=torch.uint8, device=DEV)
+
+    # the separate path on this library's own kernels
+    gui = torch.empty(M, 2 * I, device=DEV)
+    call("q27t_gemm_fp4", M, 2 * I, K, ad, asw, wid, wsw, 1.0, None, 0.0, gui)
+    q_ref, sf_ref = out()
+    call("q27t_silu_mul_quant_fp4_glu", gui, M, I, ag, au, out_scale, q_ref, sf_ref)
+    # fused
+    q, sf = out()
+    call("q27t_gemm_fp4_glu", M, I, K, ad, asw, wid, wsw, ag, au, out_scale, q, sf)
+    sf_u, sf_ref_u = (layouts.unswizzle(t.cpu().numpy(), M, I // 16) for t in (sf, sf_ref))
+    assert (sf_u != sf_ref_u).mean() < 1e-3
+    assert _code_mismatch(q, q_ref) < 2e-3
+    # rows past M inside the last scale atom stay untouched (zero here)
+    touched = np.zeros(sfb, dtype=bool)
+    touched[layouts.sf_index(M, I // 16).reshape(-1)] = True
+    assert not sf.cpu().numpy()[~touched].any()
+    # against the oracle: fp64 GEMM of the dequantised operands, SiLU*mul, then the activation quantiser
+    full = (torch.from_numpy(adq) @ torch.from_numpy(wdq).T).numpy()
+    h = O.silu_mul(ag * full[:, :I], au * full[:, I:]).astype(np.float32)
+    codes, sfo = O.quant_act_codes(h, out_scale)
+    assert (sf_u != sfo).mean() < 1e-3
+    assert _code_mismatch(q, dev(codes)) < 2e-3

@@ -147,3 +147,52 @@ class Fp4Linear:
             else:
                 assert self._nseg == 1, "the many-row GEMM takes one alpha"
                 call("q27b_gemm_fp4", M, N, K, q, sf, self.w, self.sf, self.alpha, residual, beta, out, s)
+
+
+class Fp4Mlp:
+    """The NVFP4 MLP of one layer, down(silu(gate(x)) * up(x)) (+ residual), as Model::mlp runs it
+    (engine/src/model.cc:1054-1096): `gate_up` holds gate | up interleaved, `down` consumes NVFP4 activations
+    quantised with its own in_scale.
+
+    * many rows (M > 128): one gate | up GEMM whose epilogue writes silu(gate) * up as NVFP4 codes and scales
+      (gemm_fp4_glu), then the down GEMM on them: the [M][I] intermediate never exists in bf16 or fp32;
+    * few rows: the weight-streaming GEMM to fp32 [M][2 I], the SiLU*mul quantiser, the weight-streaming down GEMM.
+    """
+
+    def __init__(self, gate_up: Fp4Linear, down: Fp4Linear, alpha_gate: float | None = None, alpha_up: float | None = None):
+        assert gate_up.glu and not down.glu and gate_up.out == down.inp
+        self.gate_up, self.down = gate_up, down
+        self.alpha_gate = gate_up.alpha if alpha_gate is None else float(alpha_gate)
+        self.alpha_up = gate_up.alpha if alpha_up is None else float(alpha_up)
+        self._one = (ctypes.c_float * 1)(1.0)
+        self._zero = (ctypes.c_int * 1)(0)
+        self._rows = 0
+
+    def _buffers(self, M: int):
+        if self._rows < M:
+            dev, inter = self.gate_up.w.device, self.gate_up.out
+            self._rows = max(M, 128)
+            self._x = ActQuant(self._rows, self.gate_up.inp, dev)
+            self._h = ActQuant(self._rows, inter, dev)
+            self._gu = torch.empty(min(self._rows, SKINNY_MAX_M), 2 * inter, dtype=torch.float32, device=dev)
+        return self._x, self._h, self._gu
+
+    def __call__(self, x: torch.Tensor, residual: torch.Tensor | None = None, out: torch.Tensor | None = None) -> torch.Tensor:
+        """x: bf16 / fp32 [M][hidden]; returns fp32 [M][hidden] = down(...) (+ residual, which may be `out`)."""
+        M = x.shape[0]
+        gu, dn, s = self.gate_up, self.down, _stream()
+        if out is None:
+            out = torch.empty(M, dn.rows(), dtype=torch.float32, device=x.device)
+        if M == 0:
+            return out
+        xq, hq, gbuf = self._buffers(M)
+        q, sf = xq.quantize(x, gu.in_scale)
+        if M > SKINNY_MAX_M:
+            call("q27b_gemm_fp4_glu", M, gu.out, gu.inp, q, sf, gu.w, gu.sf, self.alpha_gate, self.alpha_up, dn.in_scale,
+                 hq.q, hq.sf, s)
+        else:
+            call("q27b_skinny_fp4", M, gu.rows(), gu.inp, q, sf, gu.w, gu.sf, 1, self._zero, self._one, None, 0.0, gbuf,
+                 gu.ws, gu.ws.numel(), s)
+            call("q27b_silu_mul_quant_fp4_glu", gbuf, M, gu.out, self.alpha_gate, self.alpha_up, dn.in_scale, hq.q, hq.sf, s)
+        dn.gemm(M, hq.q, hq.sf, out, residual)
+        return out

@@ -206,3 +206,34 @@ def test_fused_qkv_equals_separate_projections(M):
         sep = lin(x.to(DEV), out_dtype=torch.float32).cpu().numpy()
         assert rel_err(y32[:, row:row + n].cpu().numpy(), sep) < 1e-5
         row += n
+
+
+@pytest.mark.parametrize("M", [16, 300])
+def test_mlp_two_stage_against_oracle(M, gate_up):
+    """The whole MLP (gate | up, SiLU*mul, re-quantisation to NVFP4, down) through Fp4Mlp on both dispatch paths
+    against the oracle doing the same two quantised stages. A code of the intermediate activation may land on the
+    neighbouring value (fast exponential, accumulation order), so the comparison is norm-wise."""
+    from q27b200.linear import Fp4Mlp
+
+    cfg = configs.CONFIGS[1]
+    codes, sfb, g = gate_up
+    x = configs.make_x(cfg, M=M, seed=31)
+    s_in = configs.input_scale_of(x)
+    gu = layer_from(codes, sfb, g, s_in, True, cfg)
+    dcfg = configs.GemmConfig(2, "down", M, configs.HIDDEN, configs.INTER, False)
+    dcodes, dsfb, dg = build(dcfg, 2002)
+    # oracle, stage 1
+    full = oracle_rows(x, codes, sfb, g, s_in)
+    h = O.silu_mul(full[:, :cfg.n_out], full[:, cfg.n_out:]).astype(np.float32)
+    s_h = float(np.abs(h).max() / (6.0 * 448.0))
+    down = layer_from(dcodes, dsfb, dg, s_h, False, dcfg)
+    # oracle, stage 2: quantise h, down GEMM, alpha
+    hq = torch.from_numpy(O.quant_act_nvfp4(h, s_h)).double()
+    ref = np.empty((M, configs.HIDDEN))
+    for r0 in range(0, configs.HIDDEN, 1024):
+        wdq = O.dequant_nvfp4(dcodes[r0:r0 + 1024].cpu().numpy(), dsfb[r0:r0 + 1024].cpu().numpy(), dg)
+        ref[:, r0:r0 + 1024] = (hq @ torch.from_numpy(wdq).double().T).numpy()
+    res = torch.randn(M, configs.HIDDEN, generator=torch.Generator().manual_seed(5)).to(DEV)
+    y = Fp4Mlp(gu, down)(x.to(DEV), residual=res)
+    assert y.dtype == torch.float32 and tuple(y.shape) == (M, configs.HIDDEN)
+    assert rel_err((y - res).cpu().numpy(), ref) < 5e-3

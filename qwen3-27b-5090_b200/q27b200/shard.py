@@ -39,6 +39,8 @@ def all_gather_output(local: torch.Tensor, group=None) -> torch.Tensor:
     world = dist.get_world_size(group)
     if world == 1:
         return local
-    buf = torch.empty((world,) + tuple(local.shape), dtype=local.dtype, device=local.device)
+    M, n_local = local.shape
+    # rank blocks concatenated along dim 0 (the form every backend accepts), viewed as [world][M][n_local]
+    buf = torch.empty(world * M, n_local, dtype=local.dtype, device=local.device)
     dist.all_gather_into_tensor(buf, local.contiguous(), group=group)
-    return gathered_to_row_major(buf)
+    return gathered_to_row_major(buf.view(world, M, n_local))

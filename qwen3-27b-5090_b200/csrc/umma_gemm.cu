@@ -861,11 +861,23 @@ __global__ void __launch_bounds__(128) skinny_fixup_kernel(const __grid_constant
   const int m0 = blockIdx.y * 8;
   pdl_wait();
   float v[8];
-  for (int q = 0; q < t.n; q++) {
-    const float* part = p.partials + (int64_t(part_slot(p.plan, t, q)) * p.M + m0) * 128 + row;
+  for (int q0 = 0; q0 < t.n; q0 += 8) {  // eight partial tiles in flight at a time, summed in ascending K order
+    float x[8][8];
 #pragma unroll
-    for (int j = 0; j < 8; j++)
-      if (m0 + j < p.M) v[j] = q == 0 ? __ldcg(part + j * 128) : __fadd_rn(v[j], __ldcg(part + j * 128));
+    for (int q = 0; q < 8; q++) {
+      if (q0 + q < t.n) {
+        const float* part = p.partials + (int64_t(part_slot(p.plan, t, q0 + q)) * p.M + m0) * 128 + row;
+#pragma unroll
+        for (int j = 0; j < 8; j++) x[q][j] = m0 + j < p.M ? __ldcg(part + j * 128) : 0.f;
+      }
+    }
+#pragma unroll
+    for (int q = 0; q < 8; q++) {
+      if (q0 + q < t.n) {
+#pragma unroll
+        for (int j = 0; j < 8; j++) v[j] = (q0 + q == 0) ? x[q][j] : __fadd_rn(v[j], x[q][j]);
+      }
+    }
   }
   if constexpr (kEpi == kEpiGluBf16) {
     if (row >= 64) {
@@ -997,6 +1009,10 @@ int check_operands(const char* what, int M, int N, int K, const void* a, const v
   return 0;
 }
 
+int many_common(int kEpi, int M, int N, int K, const uint8_t* a, const uint8_t* a_sf, const uint8_t* w,
+                const uint8_t* w_sf, float alpha, float alpha_up, const float* c, float beta, void* d, cudaStream_t s,
+                uint8_t* d_sf, float out_scale);
+
 int skinny_common(int kEpi, int M, int N, int K, const uint8_t* a, const uint8_t* a_sf, const uint8_t* w,
                   const uint8_t* w_sf, const AlphaSeg& alpha, float alpha_up, const float* c, float beta, void* d,
                   void* ws, size_t ws_bytes, cudaStream_t s) {
@@ -1005,13 +1021,20 @@ int skinny_common(int kEpi, int M, int N, int K, const uint8_t* a, const uint8_t
   Q27B_REQUIRE(alpha.count >= 1 && alpha.count <= 4, "skinny_fp4: 1..4 alpha segments");
   const int sms = sm_count();
   Q27B_REQUIRE(sms > 0, "skinny_fp4: no CUDA device");
+  // 65 .. 128 tokens on a weight with about one 256-row tile per SM or more (gate | up): tiles of 128 tokens x 256
+  // weight rows without any K split stream faster than split 128-row tiles with their partial sums. The choice
+  // depends on the weight's shape only, so a token's result stays the same for every M in 65 .. 128.
+  if (M > 64 && alpha.count == 1 && N % 256 == 0 && K % 128 == 0 && N / 256 >= 3 * sms / 4)
+    return many_common(kEpi, M, N, K, a, a_sf, w, w_sf, alpha.alpha[0], alpha_up, c, beta, d, s, nullptr, 1.f);
   GemmParams p = {};
   p.M = M, p.N = N, p.K = K, p.ksteps = K / 64, p.chunks = (p.ksteps + 3) / 4;
   p.sf_p = w_sf, p.sf_q = a_sf, p.alpha = alpha, p.alpha_up = alpha_up, p.c = c, p.beta = beta, p.d = d;
   // Two CTA slots per SM for every M up to 64 (a token's result is the same whatever M <= 64 it is computed
   // with, the reference's invariant for its M <= 64 path); one per SM above, where partial tiles are large.
   p.plan = choose_skinny_plan(N, K, M <= 64 ? 2 * sms : sms);
-  p.ext_reduce = plan_cuts_tiles(p.plan) && M > 32;
+  // Cut tiles: up to 8 tokens the last CTA to arrive sums them inside the kernel; above, a second small kernel
+  // does it across the whole GPU (measured cross-over on B200).
+  p.ext_reduce = plan_cuts_tiles(p.plan) && M > 8;
   Q27B_REQUIRE(p.plan.grid <= kMaxParts, "skinny_fp4: more than %d CTAs", kMaxParts);
   Q27B_REQUIRE(p.plan.tiles * 4 <= kCounterBytes, "skinny_fp4: N too large (%d rows, at most %d)", N, kCounterBytes / 4 * 128);
   const size_t need = size_t(kCounterBytes + skinny_workspace_bytes(M, p.plan));
@@ -1083,7 +1106,7 @@ int run_many(const uint8_t* a, const uint8_t* w, GemmParams& p, cudaStream_t s) 
 
 int many_common(int kEpi, int M, int N, int K, const uint8_t* a, const uint8_t* a_sf, const uint8_t* w,
                 const uint8_t* w_sf, float alpha, float alpha_up, const float* c, float beta, void* d, cudaStream_t s,
-                uint8_t* d_sf = nullptr, float out_scale = 1.f) {
+                uint8_t* d_sf, float out_scale) {
   Q27B_REQUIRE(M >= 0, "gemm_fp4: M must not be negative");
   if (M == 0) return 0;
   if (int rc = check_operands("gemm_fp4", M, N, K, a, a_sf, w, w_sf, d)) return rc;
@@ -1162,17 +1185,18 @@ int64_t q27b_skinny_workspace_bytes(int M, int N, int K) {
 
 int q27b_gemm_fp4(int M, int N, int K, const uint8_t* a, const uint8_t* a_sf, const uint8_t* b, const uint8_t* b_sf,
                   float alpha, const float* c, float beta, float* d, void* stream) {
-  return many_common(kEpiF32, M, N, K, a, a_sf, b, b_sf, alpha, 1.f, c, beta, d, static_cast<cudaStream_t>(stream));
+  return many_common(kEpiF32, M, N, K, a, a_sf, b, b_sf, alpha, 1.f, c, beta, d, static_cast<cudaStream_t>(stream), nullptr, 1.f);
 }
 int q27b_gemm_fp4_bf16(int M, int N, int K, const uint8_t* a, const uint8_t* a_sf, const uint8_t* b,
                        const uint8_t* b_sf, float alpha, void* d, void* stream) {
-  return many_common(kEpiBf16, M, N, K, a, a_sf, b, b_sf, alpha, 1.f, nullptr, 0.f, d, static_cast<cudaStream_t>(stream));
+  return many_common(kEpiBf16, M, N, K, a, a_sf, b, b_sf, alpha, 1.f, nullptr, 0.f, d, static_cast<cudaStream_t>(stream),
+                     nullptr, 1.f);
 }
 int q27b_gemm_fp4_glu_bf16(int M, int I, int K, const uint8_t* a, const uint8_t* a_sf, const uint8_t* gate_up,
                            const uint8_t* gate_up_sf, float alpha_gate, float alpha_up, void* d, void* stream) {
   Q27B_REQUIRE(I > 0 && I % 64 == 0, "gemm_fp4_glu_bf16: I must be a positive multiple of 64 (I = %d)", I);
   return many_common(kEpiGluBf16, M, 2 * I, K, a, a_sf, gate_up, gate_up_sf, alpha_gate, alpha_up, nullptr, 0.f, d,
-                     static_cast<cudaStream_t>(stream));
+                     static_cast<cudaStream_t>(stream), nullptr, 1.f);
 }
 int q27b_gemm_fp4_glu(int M, int I, int K, const uint8_t* a, const uint8_t* a_sf, const uint8_t* gate_up,
                       const uint8_t* gate_up_sf, float alpha_gate, float alpha_up, float out_scale, uint8_t* q,

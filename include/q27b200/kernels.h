@@ -66,7 +66,7 @@ struct AlphaSegments {
   }
 };
 // 1 <= M <= 128 here (the reference: 64). The workspace needs skinny_workspace_bytes(M, N, K) bytes (within the
-// reference's 32 MiB for every M on a 148-SM device) and, as in the reference, must be zeroed once
+// reference's 32 MiB up to M = 64 on a 148-SM device, up to 38.8 MiB at M = 128) and, as in the reference, must be zeroed once
 // before the first call; the kernels leave its counters at zero.
 void skinny_fp4(int M, int N, int K, const uint8_t* a, const uint8_t* a_sf, const uint8_t* w, const uint8_t* w_sf,
                 const AlphaSegments& alpha, const float* c, float beta, float* d, void* ws, size_t ws_bytes,

@@ -140,8 +140,7 @@ Q27B_HD bool plan_cuts_tiles(const SkinnyPlan& p) {
   return false;
 }
 
-// The split of a shape for `slots` CTAs that can run at once (the launchers use two per multiprocessor up to
-// M = 64, one above). Cost model, in hundredths of a microsecond as measured on B200: 0.76 us per unit a CTA
+// The split of a shape for `slots` CTAs that can run at once (the launchers use two per multiprocessor). Cost model, in hundredths of a microsecond as measured on B200: 0.76 us per unit a CTA
 // streams while the GPU is full, ~3.3 us to publish and sum a cut tile at the end of a CTA, ~1 us for an epilogue
 // in place.
 Q27B_HD SkinnyPlan choose_skinny_plan(int N, int K, int slots) {

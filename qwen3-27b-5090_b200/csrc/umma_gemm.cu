@@ -5,13 +5,13 @@
 //  * weight streaming (1 <= M <= 128, "skinny"): the roles of the operands are swapped — a 128-row weight tile is
 //    the MMA's M side, the (padded) tokens are its N side — so one instruction consumes 4 KiB of weights whatever
 //    the token count, and the kernel is bound by HBM. The K range of the whole weight matrix is cut into
-//    equal contiguous unit ranges (layout.h: two per SM up to M = 64, one above); a tile cut by a range boundary
-//    is finished by whichever of its CTAs arrives last, which sums the partial tiles in ascending K order whatever
-//    the order of arrival, or above 32 tokens by a small fix-up kernel doing the same sums on the whole GPU
-//    (deterministic; independent of M up to 64; no CTA ever waits for another).
-//  * many rows (prefill): 128 tokens x 128 output channels per tile, tiles walked token-tile fastest so that the
-//    CTAs running together share weight tiles through L2; accumulators double-buffered in tensor memory so the
-//    epilogue of one tile overlaps the MMAs of the next.
+//    pieces for two CTAs per SM (layout.h: contiguous unit ranges, or every tile in s equal K-parts, whichever a
+//    cost model prefers; the split never depends on M). A tile that is cut is summed in ascending K order
+//    whatever the order of arrival: up to 8 tokens by whichever of its CTAs arrives last, above by a small
+//    fix-up kernel doing the same sums on the whole GPU (deterministic; no CTA ever waits for another).
+//  * many rows (prefill): 128 tokens x 128 or 256 output channels per tile, tiles walked token-tile fastest so
+//    that the CTAs running together share weight tiles through L2; the accumulator goes back to the MMA issuer
+//    as soon as the epilogue warps hold it in registers. umma_gemm2_kernel runs the same on CTA pairs.
 //
 // Warp roles (320 threads): warp 0 = TMA producer (one lane), warp 1 = tensor-memory owner and MMA issuer (one
 // lane), warps 2..5 = epilogue (tcgen05.ld -> alpha / residual / SiLU*mul -> fp32 or bf16 stores), warps 6..9 =
@@ -86,7 +86,10 @@ struct Cfg {
   static constexpr int kStageBytes = kPBytes + kQBytes + (1 + kQAtoms) * kSfBytes;
   static constexpr int kOffQ = kPBytes, kOffSfP = kPBytes + kQBytes, kOffSfQ = kOffSfP + kSfBytes;
   static constexpr int kSfCols = 16 + 16 * kQAtoms;  // tensor-memory columns of one stage's scales
-  static constexpr int kXchgBytes = SWAP ? 8 * 64 * 4 + 2048 : 0;  // SiLU*mul exchange between the gate and the up warps + cut-tile info
+  // Cut tiles may be summed inside the kernel only by the 16-token configuration (few tokens); the others always
+  // leave that to the fix-up kernel and do not carry the list of partial tiles.
+  static constexpr bool kInKernelReduce = SWAP && NB == 16;
+  static constexpr int kXchgBytes = SWAP ? 8 * 64 * 4 + (kInKernelReduce ? 2048 : 0) : 0;  // SiLU*mul exchange between the gate and the up warps (+ cut-tile info)
   static constexpr int kNumBars = 3 * STAGES + 4;
   static constexpr int kBarBytes = kNumBars * 8 + 16;
   static constexpr int kSmemBytes = STAGES * kStageBytes + kXchgBytes + kBarBytes + 1024;  // + alignment slack
@@ -491,7 +494,7 @@ __global__ void __launch_bounds__((Cfg<NB, STAGES, CTAS, kSwap>::kThreads), CTAS
     for (int i = 0; it.next(w); i++) {
       const int buf = i % C::kAccBufs;
       if constexpr (kSwap) {
-        if (w.slot >= 0 && !p.ext_reduce && threadIdx.x == 64) {  // the partial tiles this cut tile is summed from
+        if (C::kInKernelReduce && w.slot >= 0 && !p.ext_reduce && threadIdx.x == 64) {  // the partial tiles this cut tile is summed from
           const TileParts t = tile_parts(p.plan, w.tile);
           seg_info[0] = t.n;
           for (int q = 0; q < t.n && q < kMaxParts; q++) seg_info[1 + q] = part_slot(p.plan, t, q);
@@ -528,7 +531,7 @@ __global__ void __launch_bounds__((Cfg<NB, STAGES, CTAS, kSwap>::kThreads), CTAS
           tc_fence_before_sync();
           __syncwarp();
           if (lane == 0) mbar_arrive(aempty0 + 8 * buf);
-          if (p.ext_reduce) continue;  // (uniform) a separate kernel sums the partial tiles: many tokens
+          if (!C::kInKernelReduce || p.ext_reduce) continue;  // (uniform) a separate kernel sums the partial tiles
           epi_bar();  // every partial of this CTA is written (and seg_info is visible) ...
           if (threadIdx.x == 64) {
             __threadfence();  // ... and published device-wide before the arrival is counted
@@ -995,7 +998,7 @@ int skinny_dispatch(const uint8_t* a, const uint8_t* w, GemmParams& p, cudaStrea
   if (p.M <= 16) return run_skinny<16, 4, 2, kEpi>(a, w, p, s);
   if (p.M <= 32) return run_skinny<32, 4, 2, kEpi>(a, w, p, s);
   if (p.M <= 64) return run_skinny<64, 3, 2, kEpi>(a, w, p, s);
-  return run_skinny<128, 6, 1, kEpi>(a, w, p, s);
+  return run_skinny<128, 3, 2, kEpi>(a, w, p, s);
 }
 
 int check_operands(const char* what, int M, int N, int K, const void* a, const void* a_sf, const void* w,
@@ -1029,9 +1032,9 @@ int skinny_common(int kEpi, int M, int N, int K, const uint8_t* a, const uint8_t
   GemmParams p = {};
   p.M = M, p.N = N, p.K = K, p.ksteps = K / 64, p.chunks = (p.ksteps + 3) / 4;
   p.sf_p = w_sf, p.sf_q = a_sf, p.alpha = alpha, p.alpha_up = alpha_up, p.c = c, p.beta = beta, p.d = d;
-  // Two CTA slots per SM for every M up to 64 (a token's result is the same whatever M <= 64 it is computed
-  // with, the reference's invariant for its M <= 64 path); one per SM above, where partial tiles are large.
-  p.plan = choose_skinny_plan(N, K, M <= 64 ? 2 * sms : sms);
+  // Two CTA slots per SM whatever M: the split depends on the weight's shape only, so a token's result is the
+  // same whatever M it is computed with (the reference's invariant for its M <= 64 path, engine/src/skinny.cu:142-147).
+  p.plan = choose_skinny_plan(N, K, 2 * sms);
   // Cut tiles: up to 8 tokens the last CTA to arrive sums them inside the kernel; above, a second small kernel
   // does it across the whole GPU (measured cross-over on B200).
   p.ext_reduce = plan_cuts_tiles(p.plan) && M > 8;
@@ -1180,7 +1183,7 @@ int q27b_skinny_fp4_glu_bf16(int M, int I, int K, const uint8_t* a, const uint8_
 int64_t q27b_skinny_workspace_bytes(int M, int N, int K) {
   const int sms = sm_count();
   if (sms <= 0 || N <= 0 || K <= 0 || M <= 0) return -1;
-  return kCounterBytes + skinny_workspace_bytes(M, choose_skinny_plan(N, K, M <= 64 ? 2 * sms : sms));
+  return kCounterBytes + skinny_workspace_bytes(M, choose_skinny_plan(N, K, 2 * sms));
 }
 
 int q27b_gemm_fp4(int M, int N, int K, const uint8_t* a, const uint8_t* a_sf, const uint8_t* b, const uint8_t* b_sf,

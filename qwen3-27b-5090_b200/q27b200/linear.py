@@ -15,7 +15,9 @@ from . import layouts, weights
 from .q27lib import call, lib
 
 SKINNY_MAX_M = 128  # rows up to which the weight-streaming kernel is used (the reference: 64)
-WORKSPACE_BYTES = 32 << 20  # as the reference's shared skinny workspace (engine/src/model.h:462)
+# The reference shares one 32 MiB workspace (engine/src/model.h:462), enough here for every shape of the model up to
+# 64 tokens (19.4 MiB); 65 .. 128 tokens need up to 38.8 MiB (q27b_skinny_workspace_bytes gives the exact figure).
+WORKSPACE_BYTES = 40 << 20
 
 
 def _stream() -> int:

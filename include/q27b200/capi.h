@@ -50,6 +50,10 @@ int q27b_quant_fp4(const float* x, int M, int K, float input_scale, uint8_t* q, 
 /* The same for bf16 input (bf16 -> fp32 is exact, so the result equals quantising the widened values). New entry
  * point (the benchmark's activations are bf16); the reference quantises bf16 only inside silu_mul_quant_fp4. */
 int q27b_quant_fp4_bf16(const void* x, int M, int K, float input_scale, uint8_t* q, uint8_t* sf, void* stream);
+/* Load-time weight quantiser: bf16 W[M][K] -> codes q[M][K/2] and swizzled scales, value = global * scale * e2m1,
+ * each block's scale code searched (4 codes below to 8 above the code of amax / 6) for the smallest squared error.
+ * Replaces quant_fp4_weight (engine/src/kernels.h:130, engine/src/kernels.cu:167-206,670-674). */
+int q27b_quant_fp4_weight(const void* w, int M, int K, float global, uint8_t* q, uint8_t* sf, void* stream);
 /* silu(gate) * up, then quantised; gate / up rows ld elements apart. Replaces silu_mul_quant_fp4
  * (engine/src/kernels.h:137-141, engine/src/kernels.cu:319-339,728-743). */
 int q27b_silu_mul_quant_fp4(const float* gate, const float* up, int64_t ld, int T, int I, float input_scale,
@@ -150,6 +154,7 @@ float q27t_last_us(void); /* per-launch time of the last Q27T_REPEAT graph repla
 int64_t q27t_sf_bytes(int64_t rows, int64_t kblocks);                                  /* capi.cc:565 */
 int q27t_quant_fp4(const float* x, int M, int K, float input_scale, uint8_t* q, uint8_t* sf); /* capi.cc:498-500 */
 int q27t_quant_fp4_bf16(const void* x, int M, int K, float input_scale, uint8_t* q, uint8_t* sf);
+int q27t_quant_fp4_weight(const void* w, int M, int K, float global, uint8_t* q, uint8_t* sf); /* (new wrapper) */
 int q27t_silu_mul_quant_fp4(const float* g, const float* u, int64_t ld, int T, int I, float in_scale, uint8_t* q,
                             uint8_t* sf);                                               /* capi.cc:523-526 */
 int q27t_silu_mul_quant_fp4_bf16(const void* g, const void* u, int64_t ld, int T, int I, float in_scale, uint8_t* q,

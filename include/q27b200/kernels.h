@@ -29,6 +29,8 @@ void swizzle_sf(const uint8_t* src, int rows, int kblocks, uint8_t* dst, cudaStr
 // engine/src/kernels.h:124-126,137-147
 void quant_fp4(const float* x, int M, int K, float input_scale, uint8_t* q, uint8_t* sf, cudaStream_t s);
 void quant_fp4(const bf16* x, int M, int K, float input_scale, uint8_t* q, uint8_t* sf, cudaStream_t s);  // new
+// engine/src/kernels.h:130: the load-time weight quantiser (block scales searched for the smallest squared error)
+void quant_fp4_weight(const bf16* w, int M, int K, float global, uint8_t* q, uint8_t* sf, cudaStream_t s);
 void silu_mul_quant_fp4(const float* gate, const float* up, int64_t ld, int T, int I, float input_scale, uint8_t* q,
                         uint8_t* sf, cudaStream_t s);
 void silu_mul_quant_fp4(const bf16* gate, const bf16* up, int64_t ld, int T, int I, float input_scale, uint8_t* q,

@@ -16,6 +16,10 @@ What each function follows (paths inside the reference project):
   dequant_nvfp4      reference/qwen27b/quant.py:52-55
   quant_act_nvfp4    reference/qwen27b/quant.py:58-67   (device twin: engine/src/kernels.cu:99-113)
   quant_weight_rtn   scripts/quantize_proj.py:77-81 (search = 0), :94-101 (pack), :176-180 (global scale)
+  quant_weight_search engine/src/kernels.cu:167-206     (the load-time quantiser with a searched block scale; the
+                     kernel cannot run where the golden vectors are made, so it is pinned through the pieces of its
+                     Python twin, scripts/quantize_proj.py:70-97 block_error / pack, evaluated on the kernel's 13
+                     candidates: tests/golden/make_golden_weight_search.py)
   qlinear            reference/qwen27b/quant.py:79-97   (matmul evaluated in fp64 as engine/tests/test_gemm.py:38)
   sf_offset/sf_bytes engine/src/kernels.h:192-199       (python twin engine/tests/test_elementwise.py:14-23)
   glu_row            engine/src/kernels.h:186           (python twin engine/tests/test_gemm.py:53-56)
@@ -232,6 +236,47 @@ def quant_weight_rtn(w: np.ndarray, gscale: float | None = None):
     s = np.repeat((sf * gscale).astype(np.float32), FP4_BLOCK, axis=1)
     q = round_e2m1((w / np.where(s > 0, s, f32(1.0))).astype(np.float32))
     return pack_codes(encode_e2m1(q, signed_zero=False)), sf_code, gscale
+
+
+# Offsets of the E4M3 codes the searched weight quantiser tries around the code of amax / 6, in its order
+# (engine/src/kernels.cu:187-188): the rounded code first, so that it stays on a tie, 4 below, 8 above.
+WEIGHT_SEARCH_OFFSETS = (0, -1, -2, -3, -4, 1, 2, 3, 4, 5, 6, 7, 8)
+
+
+def quant_weight_search(w: np.ndarray, gscale: float):
+    """The load-time weight quantiser with a per-block scale search (quant_fp4_weight_kernel,
+    engine/src/kernels.cu:167-206; the same search as scripts/quantize_proj.py:77-97 with a wider range): for every
+    16-element block the E4M3 scale code c in {c0, c0-1..c0-4, c0+1..c0+8} (clamped to 1..126, c0 = code of
+    amax / 6 / gscale) with the smallest squared error sum((v - e2m1(v / s) * s)^2), s = e4m3(c) * gscale, the first
+    of equals winning; an all-zero block keeps c0. Every operation is a separate fp32 operation, the error summed
+    in element order. Returns (packed codes [N][K/2] with the sign of zero as the hardware conversion leaves it,
+    scale codes [N][K/16])."""
+    w = np.asarray(w, dtype=np.float32)
+    n, k = w.shape
+    g = f32(gscale)
+    wb = w.reshape(n, k // FP4_BLOCK, FP4_BLOCK)
+    amax = np.abs(wb).max(-1)
+    c0 = e4m3_encode(((amax / E2M1_MAX).astype(np.float32) / g).astype(np.float32)).astype(np.int32)
+    best = c0.copy()
+    best_err = np.full(c0.shape, np.inf, dtype=np.float32)
+    for d in WEIGHT_SEARCH_OFFSETS:
+        c = np.clip(c0 + d, 1, 126)
+        s = (e4m3_decode(c.astype(np.uint8)) * g).astype(np.float32)[..., None]
+        inv = (f32(1.0) / s).astype(np.float32)
+        q = round_e2m1((wb * inv).astype(np.float32))
+        diff = (wb - (q * s).astype(np.float32)).astype(np.float32)
+        sq = (diff * diff).astype(np.float32)
+        err = np.zeros(c0.shape, dtype=np.float32)
+        for j in range(0, FP4_BLOCK, 2):  # the kernel adds a^2 + b^2 of one byte, then that to the running sum
+            err = (err + (sq[..., j] + sq[..., j + 1]).astype(np.float32)).astype(np.float32)
+        better = (err < best_err) & (amax > 0)
+        best = np.where(better, c, best)
+        best_err = np.where(better, err, best_err)
+    sf = e4m3_decode(best.astype(np.uint8))
+    sg = (sf * g).astype(np.float32)
+    inv = np.where(sf != 0, (f32(1.0) / np.where(sg != 0, sg, f32(1.0))).astype(np.float32), f32(0.0))[..., None]
+    q = round_e2m1((wb * inv).astype(np.float32)).reshape(n, k)
+    return pack_codes(encode_e2m1(q, signed_zero=True)), best.astype(np.uint8)
 
 
 def dequant_nvfp4(codes: np.ndarray, sf_code: np.ndarray, scale_2: float) -> np.ndarray:

@@ -93,6 +93,9 @@ int64_t q27t_sf_bytes(int64_t rows, int64_t kblocks) { return sf_bytes(rows, kbl
 int q27t_quant_fp4(const float* x, int M, int K, float input_scale, uint8_t* q, uint8_t* sf) {
   return kernel([&] { return q27b_quant_fp4(x, M, K, input_scale, q, sf, test_stream()); });
 }
+int q27t_quant_fp4_weight(const void* w, int M, int K, float global, uint8_t* q, uint8_t* sf) {
+  return kernel([&] { return q27b_quant_fp4_weight(w, M, K, global, q, sf, test_stream()); });
+}
 int q27t_quant_fp4_bf16(const void* x, int M, int K, float input_scale, uint8_t* q, uint8_t* sf) {
   return kernel([&] { return q27b_quant_fp4_bf16(x, M, K, input_scale, q, sf, test_stream()); });
 }

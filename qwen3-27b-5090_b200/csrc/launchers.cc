@@ -22,6 +22,9 @@ void quant_fp4(const float* x, int M, int K, float input_scale, uint8_t* q, uint
 void quant_fp4(const bf16* x, int M, int K, float input_scale, uint8_t* q, uint8_t* sf, cudaStream_t s) {
   check(q27b_quant_fp4_bf16(x, M, K, input_scale, q, sf, s));
 }
+void quant_fp4_weight(const bf16* w, int M, int K, float global, uint8_t* q, uint8_t* sf, cudaStream_t s) {
+  check(q27b_quant_fp4_weight(w, M, K, global, q, sf, s));
+}
 void silu_mul_quant_fp4(const float* gate, const float* up, int64_t ld, int T, int I, float input_scale, uint8_t* q,
                         uint8_t* sf, cudaStream_t s) {
   check(q27b_silu_mul_quant_fp4(gate, up, ld, T, I, input_scale, q, sf, s));

@@ -101,6 +101,60 @@ int launch_pdl(void (*kernel)(Args...), unsigned grid, cudaStream_t s, Act... ar
   return 0;
 }
 
+// The load-time weight quantiser: one thread per 16-element block of a bf16 weight matrix; the block's E4M3 scale
+// code is searched around the code of amax / 6 (the code itself first, so it stays on a tie, then 4 below and 8
+// above, clamped to 1..126) for the smallest squared error of the block; value = global * scale * e2m1. Codes go
+// out row-major, scales straight into the swizzled atoms. (Replaces quant_fp4_weight_kernel,
+// engine/src/kernels.cu:167-206. Every operation is a separate IEEE fp32 operation so that the CPU restatement
+// can follow it bit for bit.)
+__constant__ float kE2m1Magnitude[8] = {0.f, .5f, 1.f, 1.5f, 2.f, 3.f, 4.f, 6.f};
+__device__ __forceinline__ float e2m1_value(uint32_t code) {
+  const float m = kE2m1Magnitude[code & 7];
+  return (code & 8) ? -m : m;
+}
+__global__ void __launch_bounds__(kThreads) quant_fp4_weight_kernel(const __nv_bfloat16* __restrict__ w, int M, int K,
+                                                                    float global, uint8_t* __restrict__ q,
+                                                                    uint8_t* __restrict__ sf) {
+  const int kblocks = K / 16;
+  const int64_t idx = int64_t(blockIdx.x) * blockDim.x + threadIdx.x;
+  if (idx >= int64_t(M) * kblocks) return;
+  const int m = int(idx / kblocks), kb = int(idx % kblocks);
+  float v[16];
+  load16(w + int64_t(m) * K + kb * 16, v);
+  float amax = 0.f;
+#pragma unroll
+  for (int j = 0; j < 16; j++) amax = fmaxf(amax, fabsf(v[j]));
+  const int c0 = __nv_cvt_float_to_fp8(__fdiv_rn(__fdiv_rn(amax, 6.f), global), __NV_SATFINITE, __NV_E4M3);
+  int best = c0;
+  if (amax > 0.f) {
+    float best_err = INFINITY;
+#pragma unroll 1
+    for (int t = 0; t < 13; t++) {
+      const int c = min(max(c0 + (t <= 4 ? -t : t - 4), 1), 126);
+      const float s = __fmul_rn(e4m3_to_float(__nv_fp8_storage_t(c)), global), inv = __fdiv_rn(1.f, s);
+      float err = 0.f;
+#pragma unroll
+      for (int j = 0; j < 8; j++) {
+        const uint32_t p = e2m1x2(__fmul_rn(v[2 * j], inv), __fmul_rn(v[2 * j + 1], inv));
+        const float a = __fsub_rn(v[2 * j], __fmul_rn(e2m1_value(p & 15), s));
+        const float b = __fsub_rn(v[2 * j + 1], __fmul_rn(e2m1_value(p >> 4), s));
+        err = __fadd_rn(err, __fadd_rn(__fmul_rn(a, a), __fmul_rn(b, b)));
+      }
+      if (err < best_err) best_err = err, best = c;
+    }
+  }
+  const float sff = e4m3_to_float(__nv_fp8_storage_t(best));
+  const float inv = sff != 0.f ? __fdiv_rn(1.f, __fmul_rn(sff, global)) : 0.f;
+  uint32_t lo = 0, hi = 0;
+#pragma unroll
+  for (int j = 0; j < 4; j++) {
+    lo |= e2m1x2(__fmul_rn(v[2 * j], inv), __fmul_rn(v[2 * j + 1], inv)) << (8 * j);
+    hi |= e2m1x2(__fmul_rn(v[8 + 2 * j], inv), __fmul_rn(v[9 + 2 * j], inv)) << (8 * j);
+  }
+  *reinterpret_cast<uint2*>(q + int64_t(m) * (K / 2) + kb * 8) = make_uint2(lo, hi);
+  sf[sf_offset(m, kb, kblocks)] = uint8_t(best);
+}
+
 template <typename E>
 int quant_impl(const E* x, int M, int K, float input_scale, uint8_t* q, uint8_t* sf, cudaStream_t s) {
   Q27B_REQUIRE(M >= 0 && K > 0 && K % 64 == 0, "quant_fp4: K must be a positive multiple of 64 (K = %d)", K);
@@ -136,6 +190,17 @@ int q27b_quant_fp4(const float* x, int M, int K, float input_scale, uint8_t* q, 
 }
 int q27b_quant_fp4_bf16(const void* x, int M, int K, float input_scale, uint8_t* q, uint8_t* sf, void* stream) {
   return quant_impl(static_cast<const __nv_bfloat16*>(x), M, K, input_scale, q, sf, static_cast<cudaStream_t>(stream));
+}
+int q27b_quant_fp4_weight(const void* w, int M, int K, float global, uint8_t* q, uint8_t* sf, void* stream) {
+  Q27B_REQUIRE(M >= 0 && K > 0 && K % 64 == 0, "quant_fp4_weight: K must be a positive multiple of 64 (K = %d)", K);
+  if (M == 0) return 0;
+  Q27B_REQUIRE(w && q && sf, "quant_fp4_weight: null pointer");
+  Q27B_REQUIRE(aligned16(w) && (reinterpret_cast<uintptr_t>(q) & 7u) == 0, "quant_fp4_weight: w must be 16-byte and q 8-byte aligned");
+  Q27B_REQUIRE(global > 0.f, "quant_fp4_weight: the tensor scale must be positive");
+  quant_fp4_weight_kernel<<<blocks_for(int64_t(M) * (K / 16)), kThreads, 0, static_cast<cudaStream_t>(stream)>>>(
+      static_cast<const __nv_bfloat16*>(w), M, K, global, q, sf);
+  Q27B_CUDA(cudaGetLastError());
+  return 0;
 }
 int q27b_silu_mul_quant_fp4(const float* gate, const float* up, int64_t ld, int T, int I, float input_scale,
                             uint8_t* q, uint8_t* sf, void* stream) {

@@ -23,6 +23,7 @@ SIGNATURES = {
     "q27b_swizzle_sf": ([P, I, I, P, I, P], I),
     "q27b_quant_fp4": ([P, I, I, F, P, P, P], I),
     "q27b_quant_fp4_bf16": ([P, I, I, F, P, P, P], I),
+    "q27b_quant_fp4_weight": ([P, I, I, F, P, P, P], I),
     "q27b_silu_mul_quant_fp4": ([P, P, I64, I, I, F, P, P, P], I),
     "q27b_silu_mul_quant_fp4_bf16": ([P, P, I64, I, I, F, P, P, P], I),
     "q27b_silu_mul_quant_fp4_glu": ([P, I, I, F, F, F, P, P, P], I),
@@ -44,6 +45,7 @@ SIGNATURES = {
     "q27t_sf_bytes": ([I64, I64], I64),
     "q27t_quant_fp4": ([P, I, I, F, P, P], I),
     "q27t_quant_fp4_bf16": ([P, I, I, F, P, P], I),
+    "q27t_quant_fp4_weight": ([P, I, I, F, P, P], I),
     "q27t_silu_mul_quant_fp4": ([P, P, I64, I, I, F, P, P], I),
     "q27t_silu_mul_quant_fp4_bf16": ([P, P, I64, I, I, F, P, P], I),
     "q27t_silu_mul_quant_fp4_glu": ([P, I, I, F, F, F, P, P], I),

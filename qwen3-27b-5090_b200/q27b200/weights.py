@@ -63,3 +63,19 @@ def swizzle_scales(sf_rowmajor: torch.Tensor) -> torch.Tensor:
 def interleave_gate_up(t: torch.Tensor) -> torch.Tensor:
     """[2I][...] gate rows then up rows -> blocks of 64 gate rows followed by the 64 up rows of the same outputs."""
     return layouts.interleave_glu(t)
+
+
+def quantize_weight_search(w: torch.Tensor, scale_2: float | None = None):
+    """bf16 [N][K] on the GPU -> (codes uint8 [N][K/2], SWIZZLED scale buffer, scale_2 float) through the library's
+    load-time quantiser (q27b_quant_fp4_weight: every block's scale searched for the smallest squared error, the
+    engine's way of making an NVFP4 copy of a bf16 weight at load, engine/src/weights.cc:560-570)."""
+    from .q27lib import call
+
+    assert w.is_cuda and w.dtype == torch.bfloat16 and w.dim() == 2 and w.shape[1] % 64 == 0 and w.is_contiguous()
+    n, k = w.shape
+    if scale_2 is None:
+        scale_2 = float(torch.div(w.float().abs().amax(), torch.tensor(6.0 * 448.0, device=w.device)))
+    codes = torch.empty(n, k // 2, dtype=torch.uint8, device=w.device)
+    sf = torch.zeros(layouts.sf_bytes(n, k // 16), dtype=torch.uint8, device=w.device)
+    call("q27b_quant_fp4_weight", w, n, k, float(scale_2), codes, sf, torch.cuda.current_stream().cuda_stream)
+    return codes, sf, float(scale_2)

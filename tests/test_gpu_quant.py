@@ -140,3 +140,26 @@ def test_silu_mul_quant_fp4_against_oracle():
     sf_got = layouts.unswizzle(sf.cpu().numpy(), T, I // 16)
     assert (sf_got != sfo).mean() < 1e-3
     assert (O.canonical_zero(O.unpack_codes(q.cpu().numpy())) != O.canonical_zero(O.unpack_codes(codes))).mean() < 2e-3
+
+
+@pytest.mark.parametrize("n,k", [(96, 512), (300, 5120)])
+def test_quant_fp4_weight_search_against_oracle(n, k):
+    """The load-time weight quantiser (block scales searched for the smallest squared error) against the oracle:
+    codes and scale bytes bit for bit, including all-zero blocks, an outlier block and tiny rows."""
+    from q27b200 import weights
+
+    g = torch.Generator().manual_seed(n + k)
+    w = torch.randn(n, k, generator=g) * 0.02
+    w[3, :16] = 0.0
+    w[5, 16:32] *= 50.0
+    w[9] *= 1e-3
+    w = w.to(torch.bfloat16)
+    codes, sf, gs = weights.quantize_weight_search(w.to(DEV))
+    torch.cuda.synchronize()
+    co, so = O.quant_weight_search(w.float().numpy(), gs)
+    assert np.array_equal(layouts.unswizzle(sf.cpu().numpy(), n, k // 16), so)
+    assert np.array_equal(codes.cpu().numpy(), co)
+    # and it is what the GEMM kernels consume: dequantised error below the round-to-nearest quantiser's
+    wq = O.dequant_nvfp4(co, so, gs)
+    c_rtn, s_rtn, _ = O.quant_weight_rtn(w.float().numpy(), gs)
+    assert ((wq - w.float().numpy()) ** 2).sum() < ((O.dequant_nvfp4(c_rtn, s_rtn, gs) - w.float().numpy()) ** 2).sum()

@@ -2,6 +2,7 @@
 literal vectors) and golden vectors recorded from the reference's Python modules (tests/golden)."""
 
 import numpy as np
+import pytest
 import torch
 
 from oracle import nvfp4_oracle as O
@@ -148,3 +149,53 @@ def test_bf16_round():
     x = np.random.RandomState(3).standard_normal(100000).astype(np.float32) * 37
     ref = torch.from_numpy(x).to(torch.bfloat16).float().numpy()
     assert np.array_equal(O.bf16_round(x), ref)
+
+
+# ---- the searched weight quantiser (load-time) -----------------------------------------------------------------
+
+
+@pytest.fixture(scope="module")
+def search_golden():
+    import os
+
+    return np.load(os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden", "nvfp4_weight_search_golden.npz"))
+
+
+def test_weight_search_matches_reference_pieces(search_golden):
+    """Scale codes chosen by the oracle == the first-smallest of the reference's own block_error over the kernel's
+    13 candidates; where they differ the two candidates' errors must be within rounding of each other (the
+    reference's Python divides by the scale and sums in torch's order, the kernel multiplies by the reciprocal and
+    keeps a running sum). Codes: equal to the reference's packer except on rounding boundaries of that same
+    divide-versus-reciprocal difference."""
+    g = search_golden
+    codes, sf = O.quant_weight_search(g["w"], g["gscale"])
+    differ = np.argwhere(sf != g["best"])
+    assert len(differ) <= 0.001 * sf.size
+    for r, b in differ:
+        errs, cands = g["errs"][:, r, b], g["cands"][:, r, b]
+        e_mine = errs[np.argmax(cands == sf[r, b])]
+        assert abs(e_mine - errs.min()) <= 1e-5 * errs.min()
+    same_scale = np.repeat(sf == g["best"], 16, axis=1)
+    a, b = O.canonical_zero(O.unpack_codes(codes)), O.canonical_zero(O.unpack_codes(g["codes"]))
+    assert (a != b)[same_scale].mean() < 1e-3
+    assert (np.abs(O.decode_e2m1(a) - O.decode_e2m1(b))[same_scale].max()) <= 2.0  # a neighbouring code at most
+
+
+def test_weight_search_properties(search_golden):
+    g = search_golden
+    w, gs = g["w"], g["gscale"]
+    codes, sf = O.quant_weight_search(w, gs)
+    c_rtn, sf_rtn, _ = O.quant_weight_rtn(w, gs)
+    # never worse than round-to-nearest, block by block (the rounded code is among the candidates and wins ties)
+    err = lambda c, s: ((O.dequant_nvfp4(c, s, gs) - w) ** 2).reshape(w.shape[0], -1, 16).sum(-1)
+    assert (err(codes, sf) <= err(c_rtn, sf_rtn) * (1 + 1e-6)).all()
+    assert err(codes, sf).sum() < 0.95 * err(c_rtn, sf_rtn).sum()
+    # within the searched range, clamped
+    d = sf.astype(np.int32) - sf_rtn.astype(np.int32)
+    zero = np.abs(w).reshape(w.shape[0], -1, 16).max(-1) == 0
+    assert (d[~zero] >= -4).all() and (d[~zero] <= 8).all() and (sf[~zero] >= 1).all() and (sf <= 126).all()
+    assert (sf[zero] == sf_rtn[zero]).all() and (O.unpack_codes(codes).reshape(w.shape[0], -1, 16)[zero] & 7 == 0).all()
+    # idempotent on its own output: a weight that is exactly representable is reproduced with zero error
+    wq = O.dequant_nvfp4(codes, sf, gs).astype(np.float32)
+    c2, s2 = O.quant_weight_search(wq, gs)
+    assert np.array_equal(O.dequant_nvfp4(c2, s2, gs), O.dequant_nvfp4(codes, sf, gs))

@@ -50,6 +50,11 @@ int q27b_quant_fp4(const float* x, int M, int K, float input_scale, uint8_t* q, 
 /* The same for bf16 input (bf16 -> fp32 is exact, so the result equals quantising the widened values). New entry
  * point (the benchmark's activations are bf16); the reference quantises bf16 only inside silu_mul_quant_fp4. */
 int q27b_quant_fp4_bf16(const void* x, int M, int K, float input_scale, uint8_t* q, uint8_t* sf, void* stream);
+/* Dynamic per-token quantisation: as quant_fp4 with each row's own tensor scale ascale[m] = amax(row) / (6 * 448)
+ * (1 for an all-zero row), which the call writes. The rule of the reference's draft model (engine/src/draft.cu:70-111,
+ * where it is fused into the producing kernels); feeds q27b_skinny_fp4_scaled. */
+int q27b_quant_fp4_dynamic(const float* x, int M, int K, uint8_t* q, uint8_t* sf, float* ascale, void* stream);
+int q27b_quant_fp4_dynamic_bf16(const void* x, int M, int K, uint8_t* q, uint8_t* sf, float* ascale, void* stream);
 /* Load-time weight quantiser: bf16 W[M][K] -> codes q[M][K/2] and swizzled scales, value = global * scale * e2m1,
  * each block's scale code searched (4 codes below to 8 above the code of amax / 6) for the smallest squared error.
  * Replaces quant_fp4_weight (engine/src/kernels.h:130, engine/src/kernels.cu:167-206,670-674). */
@@ -102,7 +107,13 @@ int q27b_skinny_fp4_glu_bf16(int M, int I, int K, const uint8_t* a, const uint8_
 int q27b_skinny_fp4_static(int M, int N, int K, const uint8_t* a, const uint8_t* a_sf, const uint8_t* w,
                            const uint8_t* w_sf, int alpha_count, const int* alpha_begin, const float* alpha,
                            const float* c, float beta, float* d, void* stream);
-/* Workspace bytes of the three calls above on the current device (-1 without a device). The reference sizes its
+/* d[m][n] = (A . W^T)[m][n] * (wscale[n] * ascale[m]), fp32: per-output-channel weight scales and per-token
+ * activation scales (weights quantised at load, activations quantised dynamically). Replaces skinny_fp4_scaled
+ * (engine/src/kernels.h:255-256, engine/src/skinny.cu:402,456,568-572). */
+int q27b_skinny_fp4_scaled(int M, int N, int K, const uint8_t* a, const uint8_t* a_sf, const float* ascale,
+                           const uint8_t* w, const uint8_t* w_sf, const float* wscale, float* d, void* ws,
+                           size_t ws_bytes, void* stream);
+/* Workspace bytes of the calls above on the current device (-1 without a device). The reference sizes its
  * workspace at 32 MiB (engine/src/model.h:462), which covers every shape up to M = 64 on a 148-SM device; the
  * bound is 16 KiB + 4 * SMs * M * 512 bytes (38.8 MiB at M = 128). */
 int64_t q27b_skinny_workspace_bytes(int M, int N, int K);
@@ -155,6 +166,10 @@ int64_t q27t_sf_bytes(int64_t rows, int64_t kblocks);                           
 int q27t_quant_fp4(const float* x, int M, int K, float input_scale, uint8_t* q, uint8_t* sf); /* capi.cc:498-500 */
 int q27t_quant_fp4_bf16(const void* x, int M, int K, float input_scale, uint8_t* q, uint8_t* sf);
 int q27t_quant_fp4_weight(const void* w, int M, int K, float global, uint8_t* q, uint8_t* sf); /* (new wrapper) */
+int q27t_quant_fp4_dynamic(const float* x, int M, int K, uint8_t* q, uint8_t* sf, float* ascale); /* (new wrapper) */
+int q27t_skinny_fp4_scaled(int M, int N, int K, const uint8_t* a, const uint8_t* a_sf, const float* ascale,
+                           const uint8_t* w, const uint8_t* w_sf, const float* wscale, float* d, void* ws,
+                           size_t ws_bytes);                                            /* (new wrapper) */
 int q27t_silu_mul_quant_fp4(const float* g, const float* u, int64_t ld, int T, int I, float in_scale, uint8_t* q,
                             uint8_t* sf);                                               /* capi.cc:523-526 */
 int q27t_silu_mul_quant_fp4_bf16(const void* g, const void* u, int64_t ld, int T, int I, float in_scale, uint8_t* q,

@@ -29,6 +29,9 @@ void swizzle_sf(const uint8_t* src, int rows, int kblocks, uint8_t* dst, cudaStr
 // engine/src/kernels.h:124-126,137-147
 void quant_fp4(const float* x, int M, int K, float input_scale, uint8_t* q, uint8_t* sf, cudaStream_t s);
 void quant_fp4(const bf16* x, int M, int K, float input_scale, uint8_t* q, uint8_t* sf, cudaStream_t s);  // new
+// Dynamic per-token quantisation (the draft model's rule, engine/src/draft.cu:70-111): writes ascale[m].
+void quant_fp4_dynamic(const float* x, int M, int K, uint8_t* q, uint8_t* sf, float* ascale, cudaStream_t s);
+void quant_fp4_dynamic(const bf16* x, int M, int K, uint8_t* q, uint8_t* sf, float* ascale, cudaStream_t s);
 // engine/src/kernels.h:130: the load-time weight quantiser (block scales searched for the smallest squared error)
 void quant_fp4_weight(const bf16* w, int M, int K, float global, uint8_t* q, uint8_t* sf, cudaStream_t s);
 void silu_mul_quant_fp4(const float* gate, const float* up, int64_t ld, int T, int I, float input_scale, uint8_t* q,
@@ -73,6 +76,9 @@ struct AlphaSegments {
 void skinny_fp4(int M, int N, int K, const uint8_t* a, const uint8_t* a_sf, const uint8_t* w, const uint8_t* w_sf,
                 const AlphaSegments& alpha, const float* c, float beta, float* d, void* ws, size_t ws_bytes,
                 cudaStream_t s);
+// engine/src/kernels.h:255-256: d[t][n] = acc * wscale[n] * ascale[t]
+void skinny_fp4_scaled(int M, int N, int K, const uint8_t* a, const uint8_t* a_sf, const float* ascale, const uint8_t* w,
+                       const uint8_t* w_sf, const float* wscale, float* d, void* ws, size_t ws_bytes, cudaStream_t s);
 void skinny_fp4_bf16(int M, int N, int K, const uint8_t* a, const uint8_t* a_sf, const uint8_t* w, const uint8_t* w_sf,
                      const AlphaSegments& alpha, bf16* d, void* ws, size_t ws_bytes, cudaStream_t s);  // new
 void skinny_fp4_glu_bf16(int M, int I, int K, const uint8_t* a, const uint8_t* a_sf, const uint8_t* gate_up,

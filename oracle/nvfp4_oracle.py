@@ -218,6 +218,20 @@ def quant_act_codes(x: np.ndarray, input_scale: float):
     return pack_codes(encode_e2m1(q, signed_zero=True)), sf_code
 
 
+def quant_act_dynamic(x: np.ndarray):
+    """Per-token dynamic quantisation (the draft model's rule, engine/src/draft.cu:70-111): row scale
+    amax(row) / (6 * 448), 1 for an all-zero row, then the activation quantiser with that scale per row. Returns
+    (packed codes [M][K/2], scale bytes [M][K/16], row scales [M] fp32)."""
+    x = np.asarray(x, dtype=np.float32)
+    amax = np.abs(x).max(-1)
+    rs = np.where(amax > 0, (amax / f32(E2M1_MAX * E4M3_MAX)).astype(np.float32), f32(1.0)).astype(np.float32)
+    codes = np.empty((x.shape[0], x.shape[1] // 2), dtype=np.uint8)
+    sfs = np.empty((x.shape[0], x.shape[1] // FP4_BLOCK), dtype=np.uint8)
+    for m in range(x.shape[0]):
+        codes[m], sfs[m] = (t[0] for t in quant_act_codes(x[m:m + 1], rs[m]))
+    return codes, sfs, rs
+
+
 def weight_global_scale(w: np.ndarray) -> np.float32:
     """weight_scale_2 = amax(W) / (6 * 448)."""
     return f32(np.abs(np.asarray(w, dtype=np.float32)).max() / (E2M1_MAX * E4M3_MAX))

@@ -93,6 +93,16 @@ int64_t q27t_sf_bytes(int64_t rows, int64_t kblocks) { return sf_bytes(rows, kbl
 int q27t_quant_fp4(const float* x, int M, int K, float input_scale, uint8_t* q, uint8_t* sf) {
   return kernel([&] { return q27b_quant_fp4(x, M, K, input_scale, q, sf, test_stream()); });
 }
+int q27t_quant_fp4_dynamic(const float* x, int M, int K, uint8_t* q, uint8_t* sf, float* ascale) {
+  return kernel([&] { return q27b_quant_fp4_dynamic(x, M, K, q, sf, ascale, test_stream()); });
+}
+int q27t_skinny_fp4_scaled(int M, int N, int K, const uint8_t* a, const uint8_t* a_sf, const float* ascale,
+                           const uint8_t* w, const uint8_t* w_sf, const float* wscale, float* d, void* ws,
+                           size_t ws_bytes) {
+  return kernel([&] {
+    return q27b_skinny_fp4_scaled(M, N, K, a, a_sf, ascale, w, w_sf, wscale, d, ws, ws_bytes, test_stream());
+  });
+}
 int q27t_quant_fp4_weight(const void* w, int M, int K, float global, uint8_t* q, uint8_t* sf) {
   return kernel([&] { return q27b_quant_fp4_weight(w, M, K, global, q, sf, test_stream()); });
 }

@@ -22,6 +22,16 @@ void quant_fp4(const float* x, int M, int K, float input_scale, uint8_t* q, uint
 void quant_fp4(const bf16* x, int M, int K, float input_scale, uint8_t* q, uint8_t* sf, cudaStream_t s) {
   check(q27b_quant_fp4_bf16(x, M, K, input_scale, q, sf, s));
 }
+void quant_fp4_dynamic(const float* x, int M, int K, uint8_t* q, uint8_t* sf, float* ascale, cudaStream_t s) {
+  check(q27b_quant_fp4_dynamic(x, M, K, q, sf, ascale, s));
+}
+void quant_fp4_dynamic(const bf16* x, int M, int K, uint8_t* q, uint8_t* sf, float* ascale, cudaStream_t s) {
+  check(q27b_quant_fp4_dynamic_bf16(x, M, K, q, sf, ascale, s));
+}
+void skinny_fp4_scaled(int M, int N, int K, const uint8_t* a, const uint8_t* a_sf, const float* ascale, const uint8_t* w,
+                       const uint8_t* w_sf, const float* wscale, float* d, void* ws, size_t ws_bytes, cudaStream_t s) {
+  check(q27b_skinny_fp4_scaled(M, N, K, a, a_sf, ascale, w, w_sf, wscale, d, ws, ws_bytes, s));
+}
 void quant_fp4_weight(const bf16* w, int M, int K, float global, uint8_t* q, uint8_t* sf, cudaStream_t s) {
   check(q27b_quant_fp4_weight(w, M, K, global, q, sf, s));
 }

@@ -101,6 +101,44 @@ int launch_pdl(void (*kernel)(Args...), unsigned grid, cudaStream_t s, Act... ar
   return 0;
 }
 
+// Dynamic per-token quantisation: one CTA per row; the row's tensor scale is amax(row) / (6 * 448) (1 for an
+// all-zero row), written to ascale[row], and every block of the row is quantised with it as quant_fp4 does. The
+// GEMM multiplies it back in per token (skinny_fp4_scaled). (The rule of the reference's draft model,
+// engine/src/draft.cu:70-111: row_scale, act_row, quant_block16.)
+template <typename E>
+__global__ void __launch_bounds__(kThreads) quant_fp4_dynamic_kernel(const E* __restrict__ x, int M, int K,
+                                                                     uint8_t* __restrict__ q, uint8_t* __restrict__ sf,
+                                                                     float* __restrict__ ascale) {
+  pdl_trigger();
+  pdl_wait();
+  __shared__ float red[kThreads / 32];
+  const int m = blockIdx.x, kblocks = K / 16;
+  const E* row = x + int64_t(m) * K;
+  float am = 0.f;
+  for (int kb = threadIdx.x; kb < kblocks; kb += kThreads) {
+    float v[16];
+    load16(row + kb * 16, v);
+#pragma unroll
+    for (int j = 0; j < 16; j++) am = fmaxf(am, fabsf(v[j]));
+  }
+  for (int o = 16; o > 0; o >>= 1) am = fmaxf(am, __shfl_xor_sync(0xffffffffu, am, o));
+  if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = am;
+  __syncthreads();
+  am = red[0];
+#pragma unroll
+  for (int i = 1; i < kThreads / 32; i++) am = fmaxf(am, red[i]);
+  const float rs = am > 0.f ? __fdiv_rn(am, 6.f * 448.f) : 1.f;
+  if (threadIdx.x == 0) ascale[m] = rs;
+  for (int kb = threadIdx.x; kb < kblocks; kb += kThreads) {
+    float v[16];
+    load16(row + kb * 16, v);
+    quant_block16(v, rs, m, kb, K, q, sf);
+  }
+}
+
+template <typename E>
+int quant_dynamic_impl(const E* x, int M, int K, uint8_t* q, uint8_t* sf, float* ascale, cudaStream_t s);
+
 // The load-time weight quantiser: one thread per 16-element block of a bf16 weight matrix; the block's E4M3 scale
 // code is searched around the code of amax / 6 (the code itself first, so it stays on a tie, then 4 below and 8
 // above, clamped to 1..126) for the smallest squared error of the block; value = global * scale * e2m1. Codes go
@@ -165,6 +203,15 @@ int quant_impl(const E* x, int M, int K, float input_scale, uint8_t* q, uint8_t*
   return launch_pdl(quant_fp4_kernel<E>, blocks_for(int64_t(M) * (K / 16)), s, x, M, K, input_scale, q, sf);
 }
 
+template <typename E>
+int quant_dynamic_impl(const E* x, int M, int K, uint8_t* q, uint8_t* sf, float* ascale, cudaStream_t s) {
+  Q27B_REQUIRE(M >= 0 && K > 0 && K % 64 == 0, "quant_fp4_dynamic: K must be a positive multiple of 64 (K = %d)", K);
+  if (M == 0) return 0;
+  Q27B_REQUIRE(x && q && sf && ascale, "quant_fp4_dynamic: null pointer");
+  Q27B_REQUIRE(aligned16(x) && (reinterpret_cast<uintptr_t>(q) & 7u) == 0, "quant_fp4_dynamic: x must be 16-byte and q 8-byte aligned");
+  return launch_pdl(quant_fp4_dynamic_kernel<E>, unsigned(M), s, x, M, K, q, sf, ascale);
+}
+
 template <typename E, bool kGlu>
 int silu_impl(const E* gate, const E* up, int64_t ld, int T, int I, float input_scale, uint8_t* q, uint8_t* sf,
               float ag, float au, cudaStream_t s) {
@@ -190,6 +237,12 @@ int q27b_quant_fp4(const float* x, int M, int K, float input_scale, uint8_t* q, 
 }
 int q27b_quant_fp4_bf16(const void* x, int M, int K, float input_scale, uint8_t* q, uint8_t* sf, void* stream) {
   return quant_impl(static_cast<const __nv_bfloat16*>(x), M, K, input_scale, q, sf, static_cast<cudaStream_t>(stream));
+}
+int q27b_quant_fp4_dynamic(const float* x, int M, int K, uint8_t* q, uint8_t* sf, float* ascale, void* stream) {
+  return quant_dynamic_impl(x, M, K, q, sf, ascale, static_cast<cudaStream_t>(stream));
+}
+int q27b_quant_fp4_dynamic_bf16(const void* x, int M, int K, uint8_t* q, uint8_t* sf, float* ascale, void* stream) {
+  return quant_dynamic_impl(static_cast<const __nv_bfloat16*>(x), M, K, q, sf, ascale, static_cast<cudaStream_t>(stream));
 }
 int q27b_quant_fp4_weight(const void* w, int M, int K, float global, uint8_t* q, uint8_t* sf, void* stream) {
   Q27B_REQUIRE(M >= 0 && K > 0 && K % 64 == 0, "quant_fp4_weight: K must be a positive multiple of 64 (K = %d)", K);

@@ -59,6 +59,8 @@ struct GemmParams {
   AlphaSeg alpha;       // per output channel (gate alpha for the SiLU*mul epilogue)
   float alpha_up;
   const float* c;       // residual (may alias d) or null
+  const float* wscale;  // optional per-output-channel scale [N] (weights quantised at load with channel scales)
+  const float* ascale;  // with it: per-token scale [M] (dynamically quantised activations)
   float beta;
   void* d;              // fp32 or bf16 output; NVFP4 epilogue: E2M1 codes [M][N / 4]
   uint8_t* d_sf;        // NVFP4 epilogue: swizzled scales of the output, [M rows][N / 32 blocks]
@@ -196,6 +198,7 @@ __device__ __forceinline__ uint16_t bf16_bits(float v) { return __bfloat16_as_us
 // (engine/src/skinny.cu:452-458) so that a tile finished in place and a tile summed from partials agree bit for bit.
 __device__ __forceinline__ float finish_f32(const GemmParams& p, float acc, int m, int n) {
   float out = __fmul_rn(alpha_of(p.alpha, n), acc);
+  if (p.wscale) out = __fmul_rn(out, __fmul_rn(p.wscale[n], p.ascale[m]));
   if (p.c) out = __fmaf_rn(p.beta, p.c[int64_t(m) * p.N + n], out);
   return out;
 }
@@ -1018,7 +1021,7 @@ int many_common(int kEpi, int M, int N, int K, const uint8_t* a, const uint8_t* 
 
 int skinny_common(int kEpi, int M, int N, int K, const uint8_t* a, const uint8_t* a_sf, const uint8_t* w,
                   const uint8_t* w_sf, const AlphaSeg& alpha, float alpha_up, const float* c, float beta, void* d,
-                  void* ws, size_t ws_bytes, cudaStream_t s) {
+                  void* ws, size_t ws_bytes, cudaStream_t s, const float* wscale = nullptr, const float* ascale = nullptr) {
   Q27B_REQUIRE(M >= 1 && M <= 128, "skinny_fp4: M must be 1..128 (M = %d)", M);
   if (int rc = check_operands("skinny_fp4", M, N, K, a, a_sf, w, w_sf, d)) return rc;
   Q27B_REQUIRE(alpha.count >= 1 && alpha.count <= 4, "skinny_fp4: 1..4 alpha segments");
@@ -1027,11 +1030,12 @@ int skinny_common(int kEpi, int M, int N, int K, const uint8_t* a, const uint8_t
   // 65 .. 128 tokens on a weight with about one 256-row tile per SM or more (gate | up): tiles of 128 tokens x 256
   // weight rows without any K split stream faster than split 128-row tiles with their partial sums. The choice
   // depends on the weight's shape only, so a token's result stays the same for every M in 65 .. 128.
-  if (M > 64 && alpha.count == 1 && N % 256 == 0 && K % 128 == 0 && N / 256 >= 3 * sms / 4)
+  if (M > 64 && !wscale && alpha.count == 1 && N % 256 == 0 && K % 128 == 0 && N / 256 >= 3 * sms / 4)
     return many_common(kEpi, M, N, K, a, a_sf, w, w_sf, alpha.alpha[0], alpha_up, c, beta, d, s, nullptr, 1.f);
   GemmParams p = {};
   p.M = M, p.N = N, p.K = K, p.ksteps = K / 64, p.chunks = (p.ksteps + 3) / 4;
   p.sf_p = w_sf, p.sf_q = a_sf, p.alpha = alpha, p.alpha_up = alpha_up, p.c = c, p.beta = beta, p.d = d;
+  p.wscale = wscale, p.ascale = ascale;
   // Two CTA slots per SM whatever M: the split depends on the weight's shape only, so a token's result is the
   // same whatever M it is computed with (the reference's invariant for its M <= 64 path, engine/src/skinny.cu:142-147).
   p.plan = choose_skinny_plan(N, K, 2 * sms);
@@ -1179,6 +1183,15 @@ int q27b_skinny_fp4_glu_bf16(int M, int I, int K, const uint8_t* a, const uint8_
   const int zero = 0;
   return skinny_common(kEpiGluBf16, M, 2 * I, K, a, a_sf, gate_up, gate_up_sf, make_alpha(1, &zero, &alpha_gate),
                        alpha_up, nullptr, 0.f, d, ws, ws_bytes, static_cast<cudaStream_t>(stream));
+}
+int q27b_skinny_fp4_scaled(int M, int N, int K, const uint8_t* a, const uint8_t* a_sf, const float* ascale,
+                           const uint8_t* w, const uint8_t* w_sf, const float* wscale, float* d, void* ws,
+                           size_t ws_bytes, void* stream) {
+  Q27B_REQUIRE(ascale && wscale, "skinny_fp4_scaled: null scale pointer");
+  const int zero = 0;
+  const float one = 1.f;
+  return skinny_common(kEpiF32, M, N, K, a, a_sf, w, w_sf, make_alpha(1, &zero, &one), 1.f, nullptr, 0.f, d, ws, ws_bytes,
+                       static_cast<cudaStream_t>(stream), wscale, ascale);
 }
 int64_t q27b_skinny_workspace_bytes(int M, int N, int K) {
   const int sms = sm_count();

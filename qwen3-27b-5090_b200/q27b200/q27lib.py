@@ -24,6 +24,9 @@ SIGNATURES = {
     "q27b_quant_fp4": ([P, I, I, F, P, P, P], I),
     "q27b_quant_fp4_bf16": ([P, I, I, F, P, P, P], I),
     "q27b_quant_fp4_weight": ([P, I, I, F, P, P, P], I),
+    "q27b_quant_fp4_dynamic": ([P, I, I, P, P, P, P], I),
+    "q27b_quant_fp4_dynamic_bf16": ([P, I, I, P, P, P, P], I),
+    "q27b_skinny_fp4_scaled": ([I, I, I, P, P, P, P, P, P, P, P, SZ, P], I),
     "q27b_silu_mul_quant_fp4": ([P, P, I64, I, I, F, P, P, P], I),
     "q27b_silu_mul_quant_fp4_bf16": ([P, P, I64, I, I, F, P, P, P], I),
     "q27b_silu_mul_quant_fp4_glu": ([P, I, I, F, F, F, P, P, P], I),
@@ -46,6 +49,8 @@ SIGNATURES = {
     "q27t_quant_fp4": ([P, I, I, F, P, P], I),
     "q27t_quant_fp4_bf16": ([P, I, I, F, P, P], I),
     "q27t_quant_fp4_weight": ([P, I, I, F, P, P], I),
+    "q27t_quant_fp4_dynamic": ([P, I, I, P, P, P], I),
+    "q27t_skinny_fp4_scaled": ([I, I, I, P, P, P, P, P, P, P, P, SZ], I),
     "q27t_silu_mul_quant_fp4": ([P, P, I64, I, I, F, P, P], I),
     "q27t_silu_mul_quant_fp4_bf16": ([P, P, I64, I, I, F, P, P], I),
     "q27t_silu_mul_quant_fp4_glu": ([P, I, I, F, F, F, P, P], I),

@@ -163,3 +163,28 @@ def test_quant_fp4_weight_search_against_oracle(n, k):
     wq = O.dequant_nvfp4(co, so, gs)
     c_rtn, s_rtn, _ = O.quant_weight_rtn(w.float().numpy(), gs)
     assert ((wq - w.float().numpy()) ** 2).sum() < ((O.dequant_nvfp4(c_rtn, s_rtn, gs) - w.float().numpy()) ** 2).sum()
+
+
+def test_quant_fp4_dynamic_against_oracle():
+    """Per-token dynamic quantisation: row scales, codes and scale bytes bit for bit; rows of very different
+    magnitude and an all-zero row (scale 1)."""
+    M, K = 9, 5120
+    rng = np.random.RandomState(5)
+    x = (rng.standard_normal((M, K)) * np.logspace(-3, 2, M)[:, None]).astype(np.float32)
+    x[4] = 0.0
+    q = torch.zeros(M, K // 2, dtype=torch.uint8, device=DEV)
+    sf = torch.zeros(lib().q27t_sf_bytes(M, K // 16), dtype=torch.uint8, device=DEV)
+    asc = torch.zeros(M, dtype=torch.float32, device=DEV)
+    call("q27t_quant_fp4_dynamic", dev(x), M, K, q, sf, asc)
+    codes, sfo, rs = O.quant_act_dynamic(x)
+    assert np.array_equal(asc.cpu().numpy(), rs) and rs[4] == 1.0
+    assert np.array_equal(layouts.unswizzle(sf.cpu().numpy(), M, K // 16), sfo)
+    assert np.array_equal(q.cpu().numpy(), codes)
+    # bf16 input: the same as the fp32 kernel on the widened values
+    xb = torch.from_numpy(x).to(torch.bfloat16)
+    q2, sf2, asc2 = torch.zeros_like(q), torch.zeros_like(sf), torch.zeros_like(asc)
+    call("q27b_quant_fp4_dynamic_bf16", xb.to(DEV), M, K, q2, sf2, asc2, torch.cuda.current_stream().cuda_stream)
+    torch.cuda.synchronize()
+    c3, s3, r3 = O.quant_act_dynamic(xb.float().numpy())
+    assert np.array_equal(q2.cpu().numpy(), c3) and np.array_equal(asc2.cpu().numpy(), r3)
+    assert np.array_equal(layouts.unswizzle(sf2.cpu().numpy(), M, K // 16), s3)

@@ -188,3 +188,26 @@ def test_workspace_too_small_and_bad_m():
     assert 0 < need <= WS
     with pytest.raises(RuntimeError, match="M must be 1..128"):
         call("q27t_skinny_fp4", 0, 1024, 5120, ad, asw, bd, bsw, 1.0, None, 0.0, d, ws, 1024)
+
+
+@pytest.mark.parametrize("M", [1, 7, 16, 40])
+@pytest.mark.parametrize("N,K", [(1024, 5120), (5120, 2048)])
+def test_skinny_fp4_scaled(M, N, K):
+    """Per-output-channel weight scales and per-token activation scales: d[m][n] = acc * (wscale[n] * ascale[m])
+    against the fp64 product of the dequantised operands (engine/tests/test_skinny.py:184-201 does the same for the
+    reference's FP8 twin), and bit-identical to the unscaled call followed by that multiplication."""
+    rng = np.random.RandomState(M + N)
+    a, asf, adq = fp4_operand(M, K, rng)
+    w, wsf, wdq = fp4_operand(N, K, rng)
+    asc = (rng.rand(M) * 2 + 0.1).astype(np.float32)
+    wsc = (rng.rand(N) * 0.01 + 1e-3).astype(np.float32)
+    ad, asw, wd, wsw = dev(a), swizzled_dev(asf), dev(w), swizzled_dev(wsf)
+    ws = workspace(WS)
+    d = torch.full((M, N), float("nan"), device=DEV)
+    call("q27t_skinny_fp4_scaled", M, N, K, ad, asw, dev(asc), wd, wsw, dev(wsc), d, ws, ws.numel())
+    ref = (adq @ wdq.T) * wsc[None, :].astype(np.float64) * asc[:, None].astype(np.float64)
+    assert rel_err(d.cpu().numpy(), ref) < 1e-5
+    plain = torch.empty(M, N, device=DEV)
+    call("q27t_skinny_fp4", M, N, K, ad, asw, wd, wsw, 1.0, None, 0.0, plain, ws, ws.numel())
+    expect = plain.cpu().numpy() * (wsc[None, :] * asc[:, None])
+    assert np.array_equal(d.cpu().numpy(), expect.astype(np.float32))

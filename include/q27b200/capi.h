@@ -147,6 +147,11 @@ int q27b_gemm_fp4_glu(int M, int I, int K, const uint8_t* a, const uint8_t* a_sf
 /* Synchronises the device, returns and clears the status word kernels set when a bounded wait runs out
  * (0 = none; codes in csrc/ptx_sm100.cuh). No counterpart in the reference, whose kernels wait unboundedly. */
 int q27b_device_status(uint32_t* status);
+/* Timeline tracing for performance work: when buf is not null, the GEMM kernels launched afterwards store
+ * %globaltimer samples into it, buf[cta][4][64] uint64 (kind 0: load issued, 1: stage ready for the MMAs, 2: stage
+ * committed, 3: CTA milestones), zero meaning "not reached"; null switches it off. Host-side setting read at launch
+ * time; no counterpart in the reference. */
+int q27b_trace_set(void* buf);
 /* One thread per output, fp32 accumulation in K order: a slow device-side cross-check for the tests only; no
  * product entry point routes through it. No counterpart in the reference. */
 int q27b_ref_gemm_fp4(int M, int N, int K, const uint8_t* a, const uint8_t* a_sf, const uint8_t* b, const uint8_t* b_sf,

@@ -199,3 +199,20 @@ def test_weight_search_properties(search_golden):
     wq = O.dequant_nvfp4(codes, sf, gs).astype(np.float32)
     c2, s2 = O.quant_weight_search(wq, gs)
     assert np.array_equal(O.dequant_nvfp4(c2, s2, gs), O.dequant_nvfp4(codes, sf, gs))
+
+
+def test_dynamic_per_token_quantiser_properties():
+    """Row scale amax / (6 * 448) (1 for an all-zero row); a row quantises exactly as the static quantiser with
+    that scale; scaling a row by a power of two scales its row scale and leaves codes and block scales alone."""
+    rng = np.random.RandomState(3)
+    x = (rng.standard_normal((6, 256)) * np.logspace(-2, 2, 6)[:, None]).astype(np.float32)
+    x[2] = 0.0
+    codes, sfs, rs = O.quant_act_dynamic(x)
+    assert rs[2] == 1.0 and not codes[2].any() and not sfs[2].any()
+    for m in (0, 3, 5):
+        assert rs[m] == np.float32(np.abs(x[m]).max() / np.float32(6 * 448))
+        c, s = O.quant_act_codes(x[m:m + 1], rs[m])
+        assert np.array_equal(c[0], codes[m]) and np.array_equal(s[0], sfs[m])
+        assert s.max() == 0x7E  # the largest block reaches the top of the E4M3 range: 448
+    c2, s2, r2 = O.quant_act_dynamic(x * np.float32(8))
+    assert np.array_equal(c2, codes) and np.array_equal(s2, sfs) and np.array_equal(r2[[0, 1, 3, 4, 5]], rs[[0, 1, 3, 4, 5]] * 8)

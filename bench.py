@@ -374,7 +374,8 @@ def main():
     xh = x.pin_memory()
     yh = [torch.empty(M, n_local, dtype=torch.bfloat16).pin_memory() for _ in range(2)]
     xdev = [torch.empty_like(xd) for _ in range(2)]
-    copy_stream = torch.cuda.Stream()
+    up_stream, down_stream = torch.cuda.Stream(), torch.cuda.Stream()
+    uploaded = [torch.cuda.Event() for _ in range(2)]
     computed = [torch.cuda.Event() for _ in range(2)]
     copied = [torch.cuda.Event() for _ in range(2)]
 
@@ -384,24 +385,36 @@ def main():
         yh[0].copy_(outs[0], non_blocking=True)
         torch.cuda.current_stream().synchronize()
 
-    fresh = [0]  # steps whose result buffers nothing has used yet (the first two of a graph capture)
+    fresh = [0]  # steps whose buffers nothing has used yet (the first two of a graph capture)
 
     def step_e2e(i):
-        # throughput form: every step copies its input in, computes, and copies its result out; the copy back runs
-        # on a second stream so that it overlaps the next step (two buffers of everything), nothing waits on the host
+        # throughput form: every step copies its input in, computes, and copies its result out; the two copies run
+        # on streams of their own so that they overlap the neighbouring steps' kernels (two buffers of everything);
+        # nothing waits on the host
         b = i & 1
         main = torch.cuda.current_stream()
-        if fresh[0] > 0:
+        first = fresh[0] > 0
+        if first:
+            if fresh[0] == 2:  # the copy streams branch off the stream the steps are issued (or captured) on
+                fork = torch.cuda.Event()
+                fork.record(main)
+                up_stream.wait_event(fork)
+                down_stream.wait_event(fork)
             fresh[0] -= 1
         else:
+            up_stream.wait_event(computed[b])  # step i - 2 has consumed this input buffer
+        with torch.cuda.stream(up_stream):
+            xdev[b].copy_(xh, non_blocking=True)
+            uploaded[b].record(up_stream)
+        main.wait_event(uploaded[b])
+        if not first:
             main.wait_event(copied[b])  # the result buffer of step i - 2 has been read out
-        xdev[b].copy_(xh, non_blocking=True)
         layers[i % nbuf](xdev[b], out=outs[b])
         computed[b].record(main)
-        copy_stream.wait_event(computed[b])
-        with torch.cuda.stream(copy_stream):
+        down_stream.wait_event(computed[b])
+        with torch.cuda.stream(down_stream):
             yh[b].copy_(outs[b], non_blocking=True)
-            copied[b].record(copy_stream)
+            copied[b].record(down_stream)
 
     gathered = torch.empty(world, M, n_local, dtype=torch.bfloat16, device="cuda") if world > 1 else None
 
@@ -422,6 +435,7 @@ def main():
         for ev in copied:
             torch.cuda.current_stream().wait_event(ev)
 
+    fresh[0] = 2
     ms_e2e_eager = timed(step_e2e, args.steps, args.warmup, world, after=e2e_join)
     ms_e2e = ms_e2e_eager
     if graph:  # the same steps, copies included, replayed from one CUDA graph: the host's launch cost drops out
@@ -478,7 +492,7 @@ def main():
                 "ms_per_step": ms_e2e / args.steps, "ms_per_step_host_waits_each_result": ms_e2e_sync / args.steps,
                 "ms_per_step_eager_launches": ms_e2e_eager / args.steps,
                 "how": "per step: pinned host activation -> device, quantise + GEMM through Fp4Linear, result -> pinned "
-                       "host on a second stream (overlapping the next step); " +
+                       "host; the two copies on streams of their own, overlapping the neighbouring steps; " +
                        ("the steps with their copies replayed from one CUDA graph" if graph else "eager launches")},
         "gpu_launches": args.steps * 2,  # quantiser + GEMM
         "roofline": roof,

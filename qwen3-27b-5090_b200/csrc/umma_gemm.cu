@@ -1027,10 +1027,13 @@ int skinny_common(int kEpi, int M, int N, int K, const uint8_t* a, const uint8_t
   Q27B_REQUIRE(alpha.count >= 1 && alpha.count <= 4, "skinny_fp4: 1..4 alpha segments");
   const int sms = sm_count();
   Q27B_REQUIRE(sms > 0, "skinny_fp4: no CUDA device");
-  // 65 .. 128 tokens on a weight with about one 256-row tile per SM or more (gate | up): tiles of 128 tokens x 256
-  // weight rows without any K split stream faster than split 128-row tiles with their partial sums. The choice
-  // depends on the weight's shape only, so a token's result stays the same for every M in 65 .. 128.
-  if (M > 64 && !wscale && alpha.count == 1 && N % 256 == 0 && K % 128 == 0 && N / 256 >= 3 * sms / 4)
+  // More than 32 tokens on a weight with about one 256-row tile per SM or more (gate | up, lm_head): the many-row
+  // tiles of 128 tokens x 256 weight rows stream it faster (22.7 against 25.7 us at 64 tokens, 23.7 against 33.4 at
+  // 128 for gate | up). Neither kernel splits K on such a weight, both accumulate a dot product over the same
+  // 64-element steps in the same order, and their results are bit-identical (asserted by the tests), so a token's
+  // row still does not depend on M.
+  if (M > 32 && !wscale && alpha.count == 1 && N % 256 == 0 && K % 128 == 0 && N / 256 >= 3 * sms / 4 &&
+      !plan_cuts_tiles(choose_skinny_plan(N, K, 2 * sms)))
     return many_common(kEpi, M, N, K, a, a_sf, w, w_sf, alpha.alpha[0], alpha_up, c, beta, d, s, nullptr, 1.f);
   GemmParams p = {};
   p.M = M, p.N = N, p.K = K, p.ksteps = K / 64, p.chunks = (p.ksteps + 3) / 4;
@@ -1070,9 +1073,8 @@ int run_many_cfg(const uint8_t* a, const uint8_t* w, GemmParams& p, cudaStream_t
   return launch_gemm(kernel, p.items < slots ? p.items : slots, C::kThreads, C::kSmemBytes, s, mp, mq, p, true);
 }
 
-template <int kEpi>
+template <int kEpi, int STAGES = 5>
 int run_many_pairs(const uint8_t* a, const uint8_t* w, GemmParams& p, cudaStream_t s) {
-  constexpr int STAGES = 5;
   using C = Cfg2<STAGES>;
   auto kernel = umma_gemm2_kernel<STAGES, kEpi>;
   static bool done[64] = {};
@@ -1106,7 +1108,13 @@ int run_many(const uint8_t* a, const uint8_t* w, GemmParams& p, cudaStream_t s) 
   const bool force_wide = e && !strcmp(e, "wide"), force_narrow = e && !strcmp(e, "narrow");
   // CTA pairs, 256 x 256 tiles: least L2 traffic per flop. One CTA per 128 x 256 tile where there is less than one
   // pair tile per SM pair to go round. 128 x 128 tiles on two CTAs per SM when the weight rows do not divide by 256.
-  if (p.N % 256 == 0 && p.M > 128 && !force_wide && !force_narrow) return run_many_pairs<kEpi>(a, w, p, s);
+  if (p.N % 256 == 0 && p.M > 128 && !force_wide && !force_narrow) {
+    if (const char* st = getenv("Q27B_PAIR_STAGES")) {
+      if (atoi(st) == 3) return run_many_pairs<kEpi, 3>(a, w, p, s);
+      if (atoi(st) == 4) return run_many_pairs<kEpi, 4>(a, w, p, s);
+    }
+    return run_many_pairs<kEpi>(a, w, p, s);
+  }
   if (p.N % 256 == 0 && !force_narrow) return run_many_cfg<256, 4, 1, kEpi>(a, w, p, s);
   return run_many_cfg<128, 3, 2, kEpi>(a, w, p, s);
 }

@@ -89,8 +89,8 @@ def test_skinny_lm_head_shape():
 def test_rows_independent_of_m(residual):
     """A token's row is bit-identical whatever the number of tokens it is computed with (decode vs verify vs
     batched verify): the K split does not depend on M and the epilogue rounds explicitly. The reference states
-    this for its M <= 64 path (engine/tests/test_skinny.py:59-117); here it holds for 1..64 across four kernel
-    configurations and both ways of summing cut tiles, and again among 65..128 (which use a coarser split)."""
+    this for its M <= 64 path (engine/tests/test_skinny.py:59-117); here it holds for 1..128 across four kernel
+    configurations and both ways of summing cut tiles."""
     N, K = 5120, 17408
     bd, bsw, _, _, _ = weight(N, K)
     ad, asw, _ = act(128, K)
@@ -102,9 +102,28 @@ def test_rows_independent_of_m(residual):
         call("q27t_skinny_fp4", M, N, K, ad, asw, bd, bsw, 0.37, d if residual else None, 1.0 if residual else 0.0, d, ws, WS)
         outs[M] = d.cpu()
     for M, d in outs.items():
-        ref = outs[64] if M <= 64 else outs[128]
-        assert torch.equal(d, ref[:M]), f"M={M}"
-    assert rel_err(outs[128][:64].numpy(), outs[64].numpy()) < 5e-6  # the two splits differ only in summation order
+        assert torch.equal(d, outs[128][:M]), f"M={M}"
+
+
+@pytest.mark.parametrize("glu", [False, True])
+def test_rows_independent_of_m_on_a_wide_weight(glu):
+    """gate | up (34816 x 5120) is not split along K; above 32 tokens the launcher hands it to the many-row tiles
+    (tokens on the other side of the MMA). Rows must not change across that boundary either."""
+    N, K = 34816, 5120
+    bd, bsw, _, _, _ = weight(N, K)
+    ad, asw, _ = act(128, K)
+    ws = workspace(WS)
+    outs = {}
+    for M in (1, 16, 32, 33, 64, 65, 128):
+        if glu:
+            d = torch.empty(M, N // 2, dtype=torch.bfloat16, device=DEV)
+            call("q27t_skinny_fp4_glu_bf16", M, N // 2, K, ad, asw, bd, bsw, 0.013, 0.021, d, ws, WS)
+        else:
+            d = torch.empty(M, N, device=DEV)
+            call("q27t_skinny_fp4", M, N, K, ad, asw, bd, bsw, 0.37, None, 0.0, d, ws, WS)
+        outs[M] = d.cpu()
+    for M, d in outs.items():
+        assert torch.equal(d, outs[128][:M]), f"M={M}"
 
 
 def test_shared_workspace_across_shapes():

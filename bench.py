@@ -472,11 +472,16 @@ def main():
         # (block-scaled FP4 runs at 4 x the bf16 rate; nominal dense FP4 is 9000 TFLOP/s).
         pk = json.load(open(os.path.join(ROOT, "MEASURED_PEAKS.json"))) if os.path.exists(os.path.join(ROOT, "MEASURED_PEAKS.json")) else {}
         tpeak = 4.0 * float(pk.get("bf16_tflops", 1590.0))
+        tpeak_sustained = 4.0 * float(pk.get("bf16_tflops_sustained", 1400.0))
         launch_flops = 2 * M * n_rows_local * cfg.K
         achieved = launch_flops / gemm_s / 1e12
         roof = {"bound": "tensor", "achieved": achieved, "peak": tpeak, "unit": "TFLOP/s", "frac": achieved / tpeak,
                 "traffic": None, "algorithmic_flops": launch_flops, "kernel": "umma_gemm_kernel (many rows)",
                 "us_per_launch": gemm_s * 1e6,
+                # the timed region is a long run of back-to-back GEMMs under the power cap: the sustained cuBLAS
+                # figure (seconds-long loop, clocks settled) is the like-for-like denominator; the burst one is kept
+                # as `peak`
+                "peak_sustained": tpeak_sustained, "frac_of_sustained": achieved / tpeak_sustained,
                 "peak_source": "4 x bf16_tflops of MEASURED_PEAKS.json (no measured FP4 peak; nominal dense FP4 9000)"
                 if pk else "4 x fallback bf16 1590 (no measured FP4 peak; nominal dense FP4 9000)"}
     line = {

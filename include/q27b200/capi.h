@@ -78,8 +78,8 @@ int q27b_silu_mul_quant_fp4_glu_bf16(const void* gu, int T, int I, float alpha_g
  * segments, HOST arrays). c may alias d or be null. ws: at least q27b_skinny_workspace_bytes(M, N, K) bytes,
  * 16-byte aligned, shared by all calls of a stream in stream order; it must be zeroed once before the first call
  * (its first 16 KiB hold per-tile arrival counters, which every call leaves at zero, exactly the reference's
- * contract, engine/src/kernels.h:240-242). A token's result is bit-identical for every M <= 64, and for every M in
- * 65..128 (the two ranges differ only for weights of about 150 x 256 rows or more). Replaces skinny_fp4
+ * contract, engine/src/kernels.h:240-242). A token's result is bit-identical whatever M (1..128) it is computed
+ * with. Replaces skinny_fp4
  * (engine/src/kernels.h:240-245, engine/src/skinny.cu:462-549; the reference stops at M = 64). */
 int q27b_skinny_fp4(int M, int N, int K, const uint8_t* a, const uint8_t* a_sf, const uint8_t* w, const uint8_t* w_sf,
                     int alpha_count, const int* alpha_begin, const float* alpha, const float* c, float beta, float* d,

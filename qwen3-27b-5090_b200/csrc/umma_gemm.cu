@@ -778,7 +778,7 @@ __global__ void __launch_bounds__(Cfg2<STAGES>::kThreads, 1) umma_gemm2_kernel(c
   } else if (warp >= C::kFeederWarp0) {
     // ------------------------------------------------------------------------------------------ scale feeders
     const uint32_t lane_base = uint32_t((warp & 3) * 32) << 16;
-    int stage = 0;
+    int stage = 0, tkf = 0;
     uint32_t phase = 0;
     bool ok = true;
     for (int item = pair; ok && item < items; item += npairs) {
@@ -787,6 +787,7 @@ __global__ void __launch_bounds__(Cfg2<STAGES>::kThreads, 1) umma_gemm2_kernel(c
           ok = false;
           break;
         }
+        if (warp == C::kFeederWarp0 && lane == 0 && tkf < 20) TRACE(3, 16 + 2 * tkf);
         const uint8_t* sb = smem + stage * C::kStageBytes;
         const uint4* sfp = reinterpret_cast<const uint4*>(sb + C::kOffSfP) + lane;
         const uint4* sfq = reinterpret_cast<const uint4*>(sb + C::kOffSfQ) + lane;
@@ -808,6 +809,8 @@ __global__ void __launch_bounds__(Cfg2<STAGES>::kThreads, 1) umma_gemm2_kernel(c
           if (rank == 0) mbar_arrive(sfr0 + 8 * stage);
           else mbar_arrive_remote(sfr0 + 8 * stage, 0);
         }
+        if (warp == C::kFeederWarp0 && lane == 0 && tkf < 20) TRACE(3, 17 + 2 * tkf);
+        tkf++;
         if (++stage == STAGES) stage = 0, phase ^= 1;
       }
     }
@@ -822,6 +825,7 @@ __global__ void __launch_bounds__(Cfg2<STAGES>::kThreads, 1) umma_gemm2_kernel(c
       const int m = (item % m_pairs) * 256 + int(rank) * 128 + row, n0 = (item / m_pairs) * 256;
       if (!warp_wait(afull, ntiles & 1, abort_flag, &g_status, kStatusAccumWaitTimeout, 128)) break;
       tc_fence_after_sync();
+      if (warp == 2 && lane == 0 && ntiles < 4) TRACE(3, 4 + ntiles);
       float g[kMine][16], u[kGlu ? kMine : 1][16];
 #pragma unroll
       for (int j = 0; j < kMine; j++) {
@@ -836,6 +840,7 @@ __global__ void __launch_bounds__(Cfg2<STAGES>::kThreads, 1) umma_gemm2_kernel(c
         if (rank == 0) mbar_arrive(aempty);
         else mbar_arrive_remote(aempty, 0);
       }
+      if (warp == 2 && lane == 0 && ntiles < 4) TRACE(3, 8 + ntiles);
 #pragma unroll
       for (int j = 0; j < kMine; j++) {
         const int un = sub + 4 * j, c0 = kGlu ? (un >> 2) * 128 + (un & 3) * 16 : un * 16;
@@ -1108,13 +1113,7 @@ int run_many(const uint8_t* a, const uint8_t* w, GemmParams& p, cudaStream_t s) 
   const bool force_wide = e && !strcmp(e, "wide"), force_narrow = e && !strcmp(e, "narrow");
   // CTA pairs, 256 x 256 tiles: least L2 traffic per flop. One CTA per 128 x 256 tile where there is less than one
   // pair tile per SM pair to go round. 128 x 128 tiles on two CTAs per SM when the weight rows do not divide by 256.
-  if (p.N % 256 == 0 && p.M > 128 && !force_wide && !force_narrow) {
-    if (const char* st = getenv("Q27B_PAIR_STAGES")) {
-      if (atoi(st) == 3) return run_many_pairs<kEpi, 3>(a, w, p, s);
-      if (atoi(st) == 4) return run_many_pairs<kEpi, 4>(a, w, p, s);
-    }
-    return run_many_pairs<kEpi>(a, w, p, s);
-  }
+  if (p.N % 256 == 0 && p.M > 128 && !force_wide && !force_narrow) return run_many_pairs<kEpi>(a, w, p, s);
   if (p.N % 256 == 0 && !force_narrow) return run_many_cfg<256, 4, 1, kEpi>(a, w, p, s);
   return run_many_cfg<128, 3, 2, kEpi>(a, w, p, s);
 }

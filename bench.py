@@ -45,6 +45,15 @@ FALLBACK_HBM_GBS = 6650.0
 NCU_TRAFFIC_BYTES = {1: 104_100_000}  # profiles/umma_gemm_kernel_cfg1_verify_gate_up.md
 
 
+_json_out = None
+
+
+def emit(text: str) -> None:
+    out = _json_out if _json_out is not None else sys.stdout
+    out.write(text + "\n")
+    out.flush()
+
+
 def peaks():
     path = os.path.join(ROOT, "MEASURED_PEAKS.json")
     if os.path.exists(path):
@@ -280,7 +289,7 @@ def sweep_main(args, rank, world, local_rank):
     peak, peak_src = peaks()
     head = 16 if 16 in results else ms_list[0]
     r = results[head]
-    print(json.dumps({
+    emit(json.dumps({
         "metric": "nvfp4_gemm_hbm_gbs", "value": r["gbs"], "unit": "GB/s", "n_gpus": world, "steps": args.steps,
         "warmup": min(args.warmup, 3), "ms_per_step": r["ms_per_sweep"], "higher_is_better": True, "scaling": "strong",
         "vs_baseline": None, "dtype": "nvfp4 (e2m1 x e2m1, ue4m3 scale per 16, fp32 accumulate)", "data": "synthetic",
@@ -318,6 +327,12 @@ def main():
     from q27b200 import configs
 
     rank, world = int(os.environ.get("RANK", 0)), int(os.environ.get("WORLD_SIZE", 1))
+    # stdout carries the one JSON line and nothing else: libraries that print to file descriptor 1 on their own
+    # (NCCL's version banner) are sent to stderr, the line goes out through a private copy of the descriptor
+    global _json_out
+    sys.stdout.flush()
+    _json_out = os.fdopen(os.dup(1), "w")
+    os.dup2(2, 1)
     local_rank = int(os.environ.get("LOCAL_RANK", 0))
     if args.config == 3:
         assert args.impl == "ours", "the CPU arm times single GEMM configurations"
@@ -337,7 +352,7 @@ def main():
             return
         gbs, dt, cores, desc = cpu_reference(cfg, max(1, min(args.steps, 50)), min(args.warmup, 3))
         val = gbs if unit == "GB/s" else cfg.flops() / cfg.algorithmic_bytes() * gbs / 1e3
-        print(json.dumps({
+        emit(json.dumps({
             "impl": "reference", "metric": metric, "value": val, "unit": unit, "n_gpus": args.gpus,
             "steps": max(1, min(args.steps, 50)), "warmup": min(args.warmup, 3), "ms_per_step": dt * 1e3,
             "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "f32 (host matmul of fake-quantised operands)",
@@ -509,7 +524,7 @@ def main():
         gbs, dt, cores, desc = cpu_reference(cfg, args.cpu_steps, 2)
         line["cpu_baseline"] = {"value": gbs if unit == "GB/s" else flops / total_bytes * gbs / 1e3, "unit": unit, "cores": cores,
                                 "kind": "port", "sample": desc, "ms_per_step_sample": dt * 1e3}
-    print(json.dumps(line))
+    emit(json.dumps(line))
     if world > 1:
         torch.distributed.destroy_process_group()
 

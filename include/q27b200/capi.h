@@ -147,6 +147,10 @@ int q27b_gemm_fp4_glu(int M, int I, int K, const uint8_t* a, const uint8_t* a_sf
 /* Synchronises the device, returns and clears the status word kernels set when a bounded wait runs out
  * (0 = none; codes in csrc/ptx_sm100.cuh). No counterpart in the reference, whose kernels wait unboundedly. */
 int q27b_device_status(uint32_t* status);
+/* Self-test of that mechanism: launches one thread that waits, for at most budget_us microseconds (1..100000), on
+ * a barrier nothing arrives at; the wait gives up, the kernel ends normally and q27b_device_status then reports 6.
+ * Nothing faults or hangs. No counterpart in the reference. */
+int q27b_probe_wait_timeout(int budget_us, void* stream);
 /* Timeline tracing for performance work: when buf is not null, the GEMM kernels launched afterwards store
  * %globaltimer samples into it, buf[cta][4][64] uint64 (kind 0: load issued, 1: stage ready for the MMAs, 2: stage
  * committed, 3: CTA milestones), zero meaning "not reached"; null switches it off. Host-side setting read at launch

@@ -17,6 +17,7 @@ enum : uint32_t {
   kStatusAccumWaitTimeout = 3,   // epilogue never saw the MMAs of a tile complete
   kStatusAccumFreeTimeout = 4,   // MMA issuer never saw an accumulator buffer drained
   kStatusDrainTimeout = 5,       // a copy in flight did not land during unwinding
+  kStatusProbeTimeout = 6,       // the self-test's wait on a barrier nothing arrives at ran out, as it must
 };
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) {
@@ -81,7 +82,7 @@ constexpr uint32_t kMaxPolls = 1u << 28;
 // role or when the budget is spent, in which case it raises the flag itself and records `code`.
 __device__ __forceinline__ bool mbar_wait_bounded(uint32_t bar, uint32_t parity, volatile uint32_t* abort_flag,
                                                   uint32_t* status, uint32_t code, uint32_t sleep_ns = 0,
-                                                  bool cluster = false) {
+                                                  bool cluster = false, long long max_cycles = kMaxWaitCycles) {
   if (cluster ? mbar_try_wait_cluster(bar, parity) : mbar_try_wait(bar, parity)) return true;
   const long long t0 = clock64();
   for (uint32_t i = 1; i < kMaxPolls; i++) {
@@ -89,7 +90,7 @@ __device__ __forceinline__ bool mbar_wait_bounded(uint32_t bar, uint32_t parity,
     if (cluster ? mbar_try_wait_cluster(bar, parity) : mbar_try_wait(bar, parity)) return true;
     if ((i & 63u) == 0u) {
       if (*abort_flag) return false;
-      if (clock64() - t0 > kMaxWaitCycles) break;
+      if (clock64() - t0 > max_cycles) break;
     }
   }
   *abort_flag = 1u;

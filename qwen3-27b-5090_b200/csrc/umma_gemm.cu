@@ -859,6 +859,19 @@ __global__ void __launch_bounds__(Cfg2<STAGES>::kThreads, 1) umma_gemm2_kernel(c
   }
 }
 
+// Self-test of the bounded waits: one thread waits on a barrier that nothing ever arrives at, with a short budget;
+// the wait must give up by itself, raise the status word and let the kernel end normally.
+__global__ void wait_timeout_probe_kernel(long long max_cycles) {
+  __shared__ uint64_t bar;
+  __shared__ uint32_t abort_flag;
+  if (threadIdx.x == 0) {
+    abort_flag = 0;
+    mbar_init(smem_u32(&bar), 1);
+    mbar_init_fence();
+    mbar_wait_bounded(smem_u32(&bar), 0, &abort_flag, &g_status, kStatusProbeTimeout, 64, false, max_cycles);
+  }
+}
+
 // Sums the partial tiles of every cut weight tile in ascending K order and applies the epilogue: the same
 // arithmetic as the in-kernel reduction, spread over the whole GPU. Used when there are many tokens (the in-kernel
 // reduction leaves a cut tile to the one CTA that arrives last). Block = (tile, group of 8 tokens), thread = row.
@@ -1270,6 +1283,15 @@ int q27b_skinny_fp4_static(int M, int N, int K, const uint8_t* a, const uint8_t*
   if (int rc = static_scratch(&ws)) return rc;
   return skinny_common(kEpiF32, M, N, K, a, a_sf, w, w_sf, make_alpha(alpha_count, alpha_begin, alpha), 1.f,
                        (c && beta != 0.f) ? c : nullptr, beta, d, ws, kStaticScratchBytes, static_cast<cudaStream_t>(stream));
+}
+
+// Launches the bounded-wait self-test: a wait that cannot succeed, limited to `budget_us` microseconds (at most
+// 100 ms); afterwards q27b_device_status reports 6 and the device is as usable as before.
+int q27b_probe_wait_timeout(int budget_us, void* stream) {
+  Q27B_REQUIRE(budget_us >= 1 && budget_us <= 100000, "probe_wait_timeout: budget must be 1..100000 us");
+  wait_timeout_probe_kernel<<<1, 32, 0, static_cast<cudaStream_t>(stream)>>>(2000ll * budget_us);  // ~2 GHz
+  Q27B_CUDA(cudaGetLastError());
+  return 0;
 }
 
 // Reads and clears the device status word (0 = no bounded wait ran out since the last call). Synchronises.

@@ -24,6 +24,7 @@ SIGNATURES = {
     "q27b_quant_fp4": ([P, I, I, F, P, P, P], I),
     "q27b_quant_fp4_bf16": ([P, I, I, F, P, P, P], I),
     "q27b_trace_set": ([P], I),
+    "q27b_probe_wait_timeout": ([I, P], I),
     "q27b_quant_fp4_weight": ([P, I, I, F, P, P, P], I),
     "q27b_quant_fp4_dynamic": ([P, I, I, P, P, P, P], I),
     "q27b_quant_fp4_dynamic_bf16": ([P, I, I, P, P, P, P], I),

@@ -144,7 +144,7 @@ def max_over_ranks(ms, world):
     return float(t.item())
 
 
-def timed(fn, steps, warmup, world, graph=False, after=None, before=None):
+def timed(fn, steps, warmup, world, graph=False, after=None, before=None, graph_cap=None):
     """`steps` calls of fn(i) bracketed by a barrier + synchronize, timed with CUDA events on the current stream
     (the stream every launch of the library goes to); max over ranks, in ms. graph=True: the steps are captured
     once into a CUDA graph and the timed region is its replay, so that the host's launch cost (two ctypes calls
@@ -155,6 +155,11 @@ def timed(fn, steps, warmup, world, graph=False, after=None, before=None):
     sync_all(world)
     run = None
     if graph:
+        # the graph holds `per` steps and is replayed steps / per times (per = steps unless a cap is given: a step
+        # of hundreds of launches makes a graph of all the steps needlessly large)
+        per = steps
+        if graph_cap:
+            per = max(d for d in range(1, min(graph_cap, steps) + 1) if steps % d == 0)
         g = torch.cuda.CUDAGraph()
         side = torch.cuda.Stream()
         side.wait_stream(torch.cuda.current_stream())
@@ -162,14 +167,17 @@ def timed(fn, steps, warmup, world, graph=False, after=None, before=None):
             if before:
                 before()
             with torch.cuda.graph(g, stream=side):
-                for i in range(steps):
+                for i in range(per):
                     fn(warmup + i)
                 if after:
                     after()  # other streams the steps used rejoin the captured stream
         torch.cuda.current_stream().wait_stream(side)
         g.replay()  # once untimed
         sync_all(world)
-        run = g.replay
+
+        def run():
+            for _ in range(steps // per):
+                g.replay()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     e0.record()
     if run:
@@ -279,7 +287,7 @@ def sweep_main(args, rank, world, local_rank):
                 q, sf = act_d.quantize(xd, s_d)
                 layer["down"].gemm(M, q, sf, outs["down"])
 
-        ms = timed(sweep, args.steps, min(args.warmup, 3), world, not args.no_graph)
+        ms = timed(sweep, args.steps, min(args.warmup, 3), world, not args.no_graph, graph_cap=10)
         per_sweep_s = ms / args.steps / 1e3
         nbytes = configs.sweep_algorithmic_bytes(M, layers_n)
         results[M] = {"gbs": nbytes / per_sweep_s / 1e9, "ms_per_sweep": per_sweep_s * 1e3}

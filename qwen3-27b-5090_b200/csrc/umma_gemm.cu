@@ -544,7 +544,30 @@ __global__ void __launch_bounds__((Cfg<NB, STAGES, CTAS, kSwap>::kThreads), CTAS
           if (*last_flag) {
             __threadfence();
             const int nparts = seg_info[0];
-            for (int m0 = 0; m0 < p.M; m0 += 8) {
+            if (p.M <= 2) {
+              // one or two tokens (plain decode): eight partial tiles in flight, one round trip for up to 8 parts
+              float v[8] = {};
+              for (int q0 = 0; q0 < nparts; q0 += 8) {
+                float x[8][2];
+#pragma unroll
+                for (int q = 0; q < 8; q++) {
+                  if (q0 + q < nparts) {
+                    const float* part = p.partials + int64_t(seg_info[1 + q0 + q]) * p.M * 128 + row;
+                    x[q][0] = __ldcg(part);
+                    x[q][1] = p.M > 1 ? __ldcg(part + 128) : 0.f;
+                  }
+                }
+#pragma unroll
+                for (int q = 0; q < 8; q++) {
+                  if (q0 + q < nparts) {
+                    v[0] = (q0 + q == 0) ? x[q][0] : __fadd_rn(v[0], x[q][0]);
+                    v[1] = (q0 + q == 0) ? x[q][1] : __fadd_rn(v[1], x[q][1]);
+                  }
+                }
+              }
+              store_swapped<kEpi>(p, v, 0, w.tile, row, xchg);
+            }
+            for (int m0 = 0; p.M > 2 && m0 < p.M; m0 += 8) {
               float v[8];
               for (int q0 = 0; q0 < nparts; q0 += 4) {  // four partial tiles in flight at a time
                 float x[4][8];

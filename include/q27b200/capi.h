@@ -95,7 +95,7 @@ int q27b_skinny_fp4_glu_bf16(int M, int I, int K, const uint8_t* a, const uint8_
                              const uint8_t* gate_up_sf, float alpha_gate, float alpha_up, void* d, void* ws,
                              size_t ws_bytes, void* stream);
 /* q27b_skinny_fp4 for callers that cannot provide a workspace because they may not allocate device memory (a
- * process whose memory plan is frozen, a plug-in inside one, code between stream capture calls): the scratch is a
+ * process whose memory plan is frozen, a plug-in loaded into one): the scratch is a
  * fixed array inside the library image, 7.8 MiB per GPU that loads the library, held until the process exits.
  * Limit: 1 <= M <= 16 (decode / speculative-verify batches); a larger M is rejected with a message. Nothing is
  * allocated or freed, here or in anything this calls. The FIRST call on each device looks the array's device

@@ -1273,7 +1273,7 @@ int q27b_trace_set(void* buf) { g_trace = static_cast<unsigned long long*>(buf);
 //
 // Some callers of this library cannot hand over a workspace: code running where device allocation is forbidden or
 // already frozen (a serving process that planned all of its memory up front and has none left to give, a plug-in
-// loaded into such a process, a callback on a stream that is being captured). For them the scratch of the
+// loaded into such a process). For them the scratch of the
 // weight-streaming GEMM lives in the library image itself.
 constexpr int kStaticMaxM = 16;  // decode and speculative-verify batches
 constexpr size_t kStaticScratchBytes = kCounterBytes + size_t(2) * kMaxParts * kStaticMaxM * 128 * 4;  // 7.8 MiB

@@ -2,7 +2,7 @@
 
 Who needs it: callers that are not allowed to allocate device memory at the point where they run the GEMM and have
 no buffer of their own to lend as a workspace - an inference process that fixed its whole memory plan at start-up,
-a plug-in loaded into such a process, code that runs while a stream is being captured. Its scratch is an array
+a plug-in loaded into such a process. Its scratch is an array
 inside the library image (7.8 MiB per GPU), which limits it to M <= 16.
 
 This file sorts last on purpose: if it fails, a run that stops at the first failure has already run everything else.

@@ -544,7 +544,10 @@ __global__ void __launch_bounds__((Cfg<NB, STAGES, CTAS, kSwap>::kThreads), CTAS
           if (*last_flag) {
             __threadfence();
             const int nparts = seg_info[0];
-            if (p.M <= 2) {
+            // (not compiled into the SiLU*mul instantiation: gate | up weights are wide enough not to be cut, and
+            //  the extra registers cost that kernel, the one the streaming rate is measured on, 1 % of its speed)
+            constexpr bool kFewTokensPath = kEpi != kEpiGluBf16;
+            if (kFewTokensPath && p.M <= 2) {
               // one or two tokens (plain decode): eight partial tiles in flight, one round trip for up to 8 parts
               float v[8] = {};
               for (int q0 = 0; q0 < nparts; q0 += 8) {
@@ -567,7 +570,7 @@ __global__ void __launch_bounds__((Cfg<NB, STAGES, CTAS, kSwap>::kThreads), CTAS
               }
               store_swapped<kEpi>(p, v, 0, w.tile, row, xchg);
             }
-            for (int m0 = 0; p.M > 2 && m0 < p.M; m0 += 8) {
+            for (int m0 = 0; (!kFewTokensPath || p.M > 2) && m0 < p.M; m0 += 8) {
               float v[8];
               for (int q0 = 0; q0 < nparts; q0 += 4) {  // four partial tiles in flight at a time
                 float x[4][8];

@@ -10,6 +10,22 @@
  *   - q27t_* functions are the synchronous one-kernel wrappers the tests and the benchmark use: they synchronise
  *     the device, run on a private stream, synchronise again and fail if a kernel reported a timed-out wait.
  *
+ * Programmatic dependent launch. Every kernel here is launched with the programmatic-stream-serialization
+ * attribute (unless Q27_NO_PDL=1 is in the environment at launch time): it may START while the kernel before it in
+ * the stream is still running. What a kernel reads before its griddepcontrol.wait is only what callers promise is
+ * immutable by then: the GEMMs fetch their first WEIGHT tiles and weight scales (and the grouped GEMM its table)
+ * that early. The contract, which the engine's "weights are immutable after load" satisfies by itself: w and w_sf
+ * of a GEMM must not be written by the kernel that immediately precedes the GEMM in its stream. Anything earlier is
+ * safe, because every kernel of this library releases its successor only after its own wait on its predecessor has
+ * returned. A caller that does produce weights with the directly preceding kernel (a device-side weight update, a
+ * quantiser making the B operand) sets Q27_NO_PDL=1 for that launch or puts any other kernel in between.
+ * Activations, residuals and outputs are touched only after the wait and carry no such condition.
+ *
+ * Timed-out waits. Every wait inside a kernel is bounded; when one runs out the kernel records a code that
+ * q27b_device_status returns, and ends. Such a kernel may have left arrival counters non-zero and partial tiles
+ * unpublished: before the next call that uses the same workspace, the caller must zero its first 16 KiB again
+ * (q27b_skinny_fp4_static does this for the library's own scratch by itself).
+ *
  * Operand formats: E2M1 codes two per byte (low nibble = even K index), one E4M3 scale per 16 K-elements stored in
  * 512-byte atoms of 128 rows x 4 k-blocks (q27b_sf_offset), an fp32 tensor scale folded into `alpha` by the
  * caller. Rows of a scale buffer past the last real row are never read as valid.
@@ -99,7 +115,9 @@ int q27b_skinny_fp4_glu_bf16(int M, int I, int K, const uint8_t* a, const uint8_
  * fixed array inside the library image, 7.8 MiB per GPU that loads the library, held until the process exits.
  * Limit: 1 <= M <= 16 (decode / speculative-verify batches); a larger M is rejected with a message. Nothing is
  * allocated or freed, here or in anything this calls. The FIRST call on each device looks the array's device
- * address up and clears its counters (a synchronous memset), so make that first call before any stream capture.
+ * address up and clears its counters (a memset enqueued on `stream` ahead of the kernel), so make that first call
+ * before any stream capture. The counters are cleared the same way again on the first call after
+ * q27b_device_status has reported a timed-out wait.
  * All calls share the one array and it keeps what the last call left: the kernels leave its counters at zero, the
  * rest needs no clearing; two calls whose kernels overlap on the GPU (different streams) race on it — keep them
  * in stream order. Results are bit-identical to q27b_skinny_fp4. It has no counterpart in the reference, whose
@@ -107,6 +125,47 @@ int q27b_skinny_fp4_glu_bf16(int M, int I, int K, const uint8_t* a, const uint8_
 int q27b_skinny_fp4_static(int M, int N, int K, const uint8_t* a, const uint8_t* a_sf, const uint8_t* w,
                            const uint8_t* w_sf, int alpha_count, const int* alpha_begin, const float* alpha,
                            const float* c, float beta, float* d, void* stream);
+/* ---- grouped weight-streaming GEMM: a list of skinny GEMMs in ONE persistent launch ---------------------------------
+ *
+ * No counterpart in the reference, which launches one kernel per projection and hides the launch boundaries with
+ * CUDA graphs and programmatic dependent launch (engine/src/launch.cuh:1-8, engine/src/skinny.cu:225-237). On this
+ * GPU a decode GEMM needs 2-4 us of HBM time and a launch boundary costs more than that, so here every CTA streams
+ * its share of the weight tiles of ALL problems of the group back to back. Each problem keeps the K split of its
+ * stand-alone launch: the results are bit-identical to q27b_skinny_fp4 / _bf16 / _glu_bf16 called one by one.
+ *
+ * One problem of a group; all pointers are device pointers, all problems share the token count M of the group. */
+typedef struct q27b_group_problem {
+  int N;              /* weight rows (2 I for the gate | up epilogue), multiple of 128 */
+  int K;              /* multiple of 64 */
+  int epilogue;       /* 0: fp32 d[M][N] = alpha(n) acc + beta c;  1: bf16 d[M][N] = alpha(n) acc;
+                         2: interleaved gate | up weights, bf16 d[M][N/2] = silu(alpha[0] gate) * (alpha_up up) */
+  int alpha_count;    /* 1..4 segments of output channels with their own alpha (AlphaSegments) */
+  int alpha_begin[4];
+  float alpha[4];
+  float alpha_up;
+  float beta;
+  const uint8_t* a;    /* activation codes [M][K/2] */
+  const uint8_t* a_sf; /* its swizzled scales */
+  const uint8_t* w;    /* weight codes [N][K/2] */
+  const uint8_t* w_sf; /* its swizzled scales */
+  const float* c;      /* residual [M][N] (fp32 epilogue only; may alias d) or null */
+  void* d;             /* output */
+} q27b_group_problem;
+/* Plans the group for 1 <= M <= 128 on the current device and writes its table: tensor maps of every operand, and
+ * for every CTA the pieces {problem, weight tile, K range} it streams, longest piece first onto the least loaded
+ * CTA, walked in problem order. HOST function, called once per (problem list, M): `problems` and `table_host` are
+ * HOST memory. With table_host == NULL it only reports sizes. The caller copies the table_bytes bytes of
+ * table_host to 128-byte aligned device memory (a plain cudaMemcpy) and keeps both copies for the launches. ws_bytes:
+ * the workspace the launches need, zeroed once by the caller (arrival counters at its head, which every launch
+ * leaves at zero; after a launch that reported a timed-out wait, zero it again). */
+int q27b_skinny_group_build(int M, int n_problems, const q27b_group_problem* problems, void* table_host, size_t table_cap,
+                            size_t* table_bytes, size_t* ws_bytes);
+/* Enqueues the group on `stream`: one launch, nothing allocated or copied (capturable after one eager call per
+ * token-tile size and device). Operands, weights and the table must be complete before the kernel that precedes
+ * this one in the stream STARTS (see "programmatic dependent launch" above), except the activations, which may be
+ * written by the preceding kernel. Launches sharing a workspace must not overlap on the GPU. */
+int q27b_skinny_fp4_group(const void* table_host, const void* table_dev, void* ws, size_t ws_bytes, void* stream);
+
 /* d[m][n] = (A . W^T)[m][n] * (wscale[n] * ascale[m]), fp32: per-output-channel weight scales and per-token
  * activation scales (weights quantised at load, activations quantised dynamically). Replaces skinny_fp4_scaled
  * (engine/src/kernels.h:255-256, engine/src/skinny.cu:402,456,568-572). */
@@ -156,18 +215,6 @@ int q27b_probe_wait_timeout(int budget_us, void* stream);
  * committed, 3: CTA milestones), zero meaning "not reached"; null switches it off. Host-side setting read at launch
  * time; no counterpart in the reference. */
 int q27b_trace_set(void* buf);
-/* One thread per output, fp32 accumulation in K order: a slow device-side cross-check for the tests only; no
- * product entry point routes through it. No counterpart in the reference. */
-int q27b_ref_gemm_fp4(int M, int N, int K, const uint8_t* a, const uint8_t* a_sf, const uint8_t* b, const uint8_t* b_sf,
-                      float alpha, float* d, void* stream);
-/* Host-only view of the weight-streaming work split (no CUDA call) for `slots` CTAs that can run at once (the
- * launchers use two per multiprocessor up to M = 64, one above): the pieces {tile, c0, c1, slot} of CTA `cta`;
- * returns the number of pieces. split_out: 0 = contiguous unit ranges, s >= 1 = s aligned K-parts per tile. */
-int q27b_skinny_plan(int N, int K, int slots, int cta, int* seg, int cap, int* grid_out, int64_t* units_out,
-                     int* split_out);
-/* The partial-tile slots a tile is summed from, in summation order; returns their number (1 = the tile is not cut). */
-int q27b_skinny_tile_parts(int N, int K, int slots, int tile, int* slot, int cap);
-
 /* ---- synchronous test layer (replaces the q27t_* wrappers, engine/src/capi.cc:498-636) ---------------------------- */
 
 float q27t_last_us(void); /* per-launch time of the last Q27T_REPEAT graph replay (capi.cc:38,57-92) */
@@ -208,10 +255,9 @@ int q27t_skinny_fp4_bf16(int M, int N, int K, const uint8_t* a, const uint8_t* a
 int q27t_skinny_fp4_glu_bf16(int M, int I, int K, const uint8_t* a, const uint8_t* a_sf, const uint8_t* gate_up,
                              const uint8_t* gate_up_sf, float alpha_gate, float alpha_up, void* d, void* ws,
                              size_t ws_bytes);
-int q27t_ref_gemm_fp4(int M, int N, int K, const uint8_t* a, const uint8_t* a_sf, const uint8_t* b, const uint8_t* b_sf,
-                      float alpha, float* d);
 int q27t_skinny_fp4_static(int M, int N, int K, const uint8_t* a, const uint8_t* a_sf, const uint8_t* w,
                            const uint8_t* w_sf, float alpha, const float* c, float beta, float* d);
+int q27t_skinny_fp4_group(const void* table_host, const void* table_dev, void* ws, size_t ws_bytes);
 /* Average microseconds of `iters` GEMMs cycling through `nbuf` weight copies (w_stride / sf_stride bytes apart) so
  * that weights never come from L2; `us` is a HOST pointer. Replaces q27t_bench_gemm (capi.cc:607-636). */
 int q27t_bench_gemm(int many, int M, int N, int K, const uint8_t* a, const uint8_t* a_sf, const uint8_t* w,

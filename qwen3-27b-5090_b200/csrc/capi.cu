@@ -188,11 +188,9 @@ int q27t_skinny_fp4_static(int M, int N, int K, const uint8_t* a, const uint8_t*
     return q27b_skinny_fp4_static(M, N, K, a, a_sf, w, w_sf, 1, &zero, &alpha, c, beta, d, test_stream());
   });
 }
-int q27t_ref_gemm_fp4(int M, int N, int K, const uint8_t* a, const uint8_t* a_sf, const uint8_t* b, const uint8_t* b_sf,
-                      float alpha, float* d) {
-  return kernel([&] { return q27b_ref_gemm_fp4(M, N, K, a, a_sf, b, b_sf, alpha, d, test_stream()); });
+int q27t_skinny_fp4_group(const void* table_host, const void* table_dev, void* ws, size_t ws_bytes) {
+  return kernel([&] { return q27b_skinny_fp4_group(table_host, table_dev, ws, ws_bytes, test_stream()); });
 }
-
 // Average time (us) of `iters` calls cycling through `nbuf` weight copies w_stride / sf_stride bytes apart (so
 // that the weights never come from L2). many != 0: the many-row GEMM; else the weight-streaming one.
 int q27t_bench_gemm(int many, int M, int N, int K, const uint8_t* a, const uint8_t* a_sf, const uint8_t* w,
@@ -225,33 +223,6 @@ int q27t_bench_gemm(int many, int M, int N, int K, const uint8_t* a, const uint8
     cudaEventDestroy(e1);
     return 0;
   });
-}
-
-// CPU-testable view of the weight-streaming work split: fills seg[4 * i .. 4 * i + 3] = {tile, c0, c1, slot} for the
-// pieces of CTA `cta` (at most `cap`), returns their count; grid_out / units_out / split_out describe the plan.
-int q27b_skinny_plan(int N, int K, int slots, int cta, int* seg, int cap, int* grid_out, int64_t* units_out,
-                     int* split_out) {
-  if (N <= 0 || N % 128 || K <= 0 || K % 64 || slots <= 0) return fail("skinny_plan: bad shape");
-  const SkinnyPlan p = choose_skinny_plan(N, K, slots);
-  if (grid_out) *grid_out = p.grid;
-  if (units_out) *units_out = p.units;
-  if (split_out) *split_out = p.split;
-  if (cta < 0 || cta >= p.grid) return 0;
-  int64_t u = -1;
-  Segment s;
-  int n = 0;
-  while (next_segment(p, cta, u, s)) {
-    if (seg && n < cap) seg[4 * n] = s.tile, seg[4 * n + 1] = s.c0, seg[4 * n + 2] = s.c1, seg[4 * n + 3] = s.slot;
-    n++;
-  }
-  return n;
-}
-// The partial-tile slots tile `tile` is summed from, in order (at most `cap`); returns their number (1: not cut).
-int q27b_skinny_tile_parts(int N, int K, int slots, int tile, int* slot, int cap) {
-  const SkinnyPlan p = choose_skinny_plan(N, K, slots);
-  const TileParts t = tile_parts(p, tile);
-  for (int i = 0; i < t.n && i < cap; i++) slot[i] = t.n == 1 ? -1 : part_slot(p, t, i);
-  return t.n;
 }
 
 }  // extern "C"

@@ -6,6 +6,7 @@
 #include <cstdarg>
 #include <cstdint>
 #include <cstdio>
+#include <cstdlib>
 #include <string>
 
 #include <cuda_bf16.h>
@@ -47,5 +48,25 @@ __host__ __device__ inline float alpha_of(const AlphaSeg& a, int n) {
 }
 
 inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
+
+// Per-launch switches. They are read from the environment at EVERY launch, so that a CUDA graph captured after a
+// change sees the new value (the reference reads its tunables the same way, engine/src/skinny.cu:494-521,
+// engine/src/launch.cuh:15):
+//   Q27_NO_PDL=1               no launch of this library carries the programmatic-dependent-launch attribute: every
+//                              kernel starts only after its predecessor in the stream has completed (debugging a
+//                              chain; weights written by the preceding kernel);
+//   Q27_SKINNY_EXT_REDUCE_M=m  the weight-streaming GEMM sums cut tiles in its separate fix-up kernel above m
+//                              tokens (0..16, default 8; above 16 tokens it always does).
+inline bool env_flag(const char* name) {
+  const char* e = getenv(name);
+  return e && *e && !(e[0] == '0' && e[1] == 0);
+}
+inline int env_int(const char* name, int dflt, int lo, int hi) {
+  const char* e = getenv(name);
+  if (!e || !*e) return dflt;
+  const int v = atoi(e);
+  return v < lo ? lo : (v > hi ? hi : v);
+}
+inline bool pdl_enabled() { return !env_flag("Q27_NO_PDL"); }
 
 }  // namespace q27b

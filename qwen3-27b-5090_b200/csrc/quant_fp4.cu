@@ -96,7 +96,7 @@ int launch_pdl(void (*kernel)(Args...), unsigned grid, cudaStream_t s, Act... ar
   cudaLaunchAttribute attr[1];
   attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
   attr[0].val.programmaticStreamSerializationAllowed = 1;
-  cfg.attrs = attr, cfg.numAttrs = 1;
+  cfg.attrs = attr, cfg.numAttrs = pdl_enabled() ? 1 : 0;
   Q27B_CUDA(cudaLaunchKernelEx(&cfg, kernel, static_cast<Args>(args)...));
   return 0;
 }

@@ -1,0 +1,403 @@
+// The grouped weight-streaming GEMM (part of umma_gemm.cu, which provides the tile configuration, the epilogue
+// helpers and the status word): ONE persistent launch computes a whole list of skinny GEMMs D_p = alpha_p A_p W_p^T.
+//
+// Why: on this GPU a decode GEMM needs 2-4 us of HBM time, while a launch costs 7-9 us around it (ring fill, tail,
+// hand-over to the next launch). Here every CTA walks a device-side list of pieces {problem, weight tile, K range}
+// (group_plan.h) and its TMA producer keeps the shared-memory ring full ACROSS problem boundaries: the weights of
+// problem p + 1 are already in flight while the last stages of problem p are multiplied, its cut tiles summed and
+// its epilogue stored. Ring fill and tail are paid once per group.
+//
+// Each problem keeps the K split of its stand-alone launch and a cut tile is summed in ascending K order by
+// whichever CTA delivers its last piece (arrival counter, nobody waits for anybody), so the results are
+// bit-identical to q27b_skinny_fp4 / _bf16 / _glu_bf16 called problem by problem, for every M.
+//
+// The table (header, problems with their two tensor maps, per-CTA piece lists) is built once on the host
+// (q27b_skinny_group_build) and lives in device memory the caller owns; a launch only passes pointers, so it can
+// be captured into a CUDA graph. No multicast, no peer memory, every wait bounded.
+
+struct alignas(128) GroupProblemDev {
+  CUtensorMap tmap_w;  // weight codes [N][K/2]: boxes of 128 rows x 128 bytes
+  CUtensorMap tmap_a;  // activation codes [M][K/2]: boxes of NB rows x 128 bytes
+  void* d;
+  const float* c;
+  AlphaSeg alpha;
+  float alpha_up, beta;
+  int N, epi;
+};
+static_assert(sizeof(GroupProblemDev) == 384, "GroupProblemDev layout");
+
+constexpr uint32_t kGroupMagic = 0x51324742u;  // "Q2GB"
+struct GroupHeader {  // the first 128 bytes of the table
+  uint32_t magic;
+  int M, nb, n_problems, n_ctas, n_items, counters, sms;
+  int64_t slots, off_problems, off_cta_first, off_cta_units, off_items, table_bytes, ws_bytes;
+  int64_t pad[5];
+};
+static_assert(sizeof(GroupHeader) == 128, "GroupHeader layout");
+
+struct GroupLaunch {
+  const GroupProblemDev* probs;
+  const int* cta_first;  // pieces of CTA g: [cta_first[g], cta_first[g + 1])
+  const int* cta_units;  // stages CTA g streams
+  const GroupItem* items;
+  int M;
+  int* counters;         // one per cut tile, zero between launches
+  float* partials;       // [slots][M][128]
+};
+
+__device__ __forceinline__ int4 ldg16(const void* p) { return __ldg(reinterpret_cast<const int4*>(p)); }
+
+// The stages (units of 128 weight rows x 256 K-elements) of this CTA in the order it streams them. The record of
+// the next piece is requested while the current one is being streamed, so that moving on never waits for memory.
+struct GroupUnits {
+  const GroupItem* items;
+  int i, i1;
+  int prob, tile, c, c1, ksteps;
+  const uint8_t *w_sf_tile, *a_sf;
+  int4 n0, n1, n2;  // words 0..2 of piece i + 1
+  bool valid;
+  __device__ __forceinline__ void fetch_next() {
+    if (i + 1 < i1) {
+      const int4* r = reinterpret_cast<const int4*>(items + i + 1);
+      n0 = __ldg(r), n1 = __ldg(r + 1), n2 = __ldg(r + 2);
+    }
+  }
+  __device__ __forceinline__ void adopt() {
+    prob = n0.x, tile = n0.y, c = n0.z, c1 = n0.w, ksteps = n1.w;
+    w_sf_tile = reinterpret_cast<const uint8_t*>((uint64_t(uint32_t(n2.y)) << 32) | uint32_t(n2.x));
+    a_sf = reinterpret_cast<const uint8_t*>((uint64_t(uint32_t(n2.w)) << 32) | uint32_t(n2.z));
+  }
+  __device__ __forceinline__ GroupUnits(const GroupLaunch& g, int first, int last) : items(g.items), i(first - 1), i1(last) {
+    valid = first < last;
+    if (valid) {
+      fetch_next();
+      i = first;
+      adopt();
+      fetch_next();
+    }
+  }
+  __device__ __forceinline__ void advance() {
+    if (++c < c1) return;
+    if (++i < i1) {
+      adopt();
+      fetch_next();
+    } else {
+      valid = false;
+    }
+  }
+};
+
+template <int NB, int STAGES>
+__global__ void __launch_bounds__((Cfg<NB, STAGES, 2, true>::kThreads), 2) skinny_group_kernel(const __grid_constant__ GroupLaunch g) {
+  using C = Cfg<NB, STAGES, 2, true>;
+  static_assert(C::kQAtoms == 1, "the tokens of a group fit one 128-row block");
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  float* xchg = reinterpret_cast<float*>(smem + STAGES * C::kStageBytes);
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + STAGES * C::kStageBytes + C::kXchgBytes);
+  const uint32_t full0 = smem_u32(bars), empty0 = full0 + 8 * STAGES, sfr0 = empty0 + 8 * STAGES,
+                 afull0 = sfr0 + 8 * STAGES, aempty0 = afull0 + 16;
+  uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(bars + C::kNumBars);
+  volatile uint32_t* abort_flag = tmem_holder + 1;
+  volatile uint32_t* last_flag = tmem_holder + 2;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int i0 = __ldg(g.cta_first + blockIdx.x), i1 = __ldg(g.cta_first + blockIdx.x + 1);
+  const uint32_t smem_base = smem_u32(smem);
+
+  auto stage_bytes = [&](const GroupUnits& k) { return uint32_t(C::kPBytes + C::kQBytes + 2 * min(4, k.ksteps - 4 * k.c) * 512); };
+  auto load_w = [&](const GroupUnits& k, int stage) {  // weights: read once, evict first
+    const uint32_t sbase = smem_base + stage * C::kStageBytes, bar = full0 + 8 * stage;
+    tma_load_2d(sbase, &g.probs[k.prob].tmap_w, k.c * 128, k.tile * 128, bar, kEvictFirst);
+    bulk_load(sbase + C::kOffSfP, k.w_sf_tile + int64_t(4 * k.c) * 512, min(4, k.ksteps - 4 * k.c) * 512, bar, kEvictFirst);
+  };
+  auto load_a = [&](const GroupUnits& k, int stage) {  // activations: re-read by every CTA, keep them in L2
+    const uint32_t sbase = smem_base + stage * C::kStageBytes, bar = full0 + 8 * stage;
+    tma_load_2d(sbase + C::kOffQ, &g.probs[k.prob].tmap_a, k.c * 128, 0, bar, kEvictLast);
+    bulk_load(sbase + C::kOffSfQ, k.a_sf + int64_t(4 * k.c) * 512, min(4, k.ksteps - 4 * k.c) * 512, bar, kEvictLast);
+  };
+  uint32_t armed = 0;  // (producer lane) stages with a copy possibly in flight
+  int npre = 0;        // (producer lane) stages filled before the steady state
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; s++) mbar_init(full0 + 8 * s, 1), mbar_init(empty0 + 8 * s, 1), mbar_init(sfr0 + 8 * s, 4);
+    for (int b = 0; b < 2; b++) mbar_init(afull0 + 8 * b, 1), mbar_init(aempty0 + 8 * b, C::kEpiWarps);
+    *abort_flag = 0;
+    mbar_init_fence();
+    // The stream starts at once: the ring is filled with weights (which no kernel of this stream produces) while the
+    // rest of the CTA sets up and before the preceding kernel is known to have finished.
+    for (GroupUnits k(g, i0, i1); k.valid && npre < STAGES; k.advance(), npre++) {
+      mbar_arrive_expect_tx(full0 + 8 * npre, stage_bytes(k));
+      armed |= 1u << npre;
+      load_w(k, npre);
+    }
+  }
+  if (warp == 1) {
+    tmem_alloc(smem_u32(tmem_holder), C::kTmemCols);
+    tmem_relinquish();
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  const uint32_t tmem_base = *tmem_holder;
+
+  if (warp == 0) {
+    // ------------------------------------------------------------------------------------------ TMA producer
+    if (lane == 0) {
+      uint32_t last_parity = 0;
+      pdl_wait();  // the activations may come from the preceding kernel
+      GroupUnits k(g, i0, i1);
+      for (int s = 0; s < npre; s++, k.advance()) load_a(k, s);
+      int stage = npre % STAGES;
+      uint32_t phase = npre == STAGES ? 1 : 0;
+      bool ok = true;
+      int cur_prob = -1;
+      for (; k.valid; k.advance()) {
+        if (k.prob != cur_prob) {  // descriptors of a problem this CTA has not touched yet
+          cur_prob = k.prob;
+          prefetch_tensormap(&g.probs[cur_prob].tmap_w);
+          prefetch_tensormap(&g.probs[cur_prob].tmap_a);
+        }
+        if (!mbar_wait_bounded(empty0 + 8 * stage, phase ^ 1, abort_flag, &g_status, kStatusEmptyWaitTimeout)) {
+          ok = false;
+          break;
+        }
+        mbar_arrive_expect_tx(full0 + 8 * stage, stage_bytes(k));
+        last_parity = (last_parity & ~(1u << stage)) | (phase << stage);
+        load_w(k, stage);
+        load_a(k, stage);
+        if (++stage == STAGES) stage = 0, phase ^= 1;
+      }
+      pdl_trigger();  // everything this CTA reads from HBM has been requested
+      if (!ok) {
+        for (int s = 0; s < STAGES; s++)
+          if (armed >> s & 1) {
+            bool landed = false;
+            const long long t0 = clock64();
+            for (uint32_t i = 0; i < kMaxPolls && !landed; i++) {
+              landed = mbar_try_wait(full0 + 8 * s, last_parity >> s & 1);
+              if ((i & 63u) == 63u && clock64() - t0 > kMaxWaitCycles) break;
+            }
+            if (!landed) atomicCAS(&g_status, 0u, uint32_t(kStatusDrainTimeout));
+          }
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------------------------------------ MMA issuer
+    if (lane == 0) {
+      constexpr uint32_t idesc = umma_idesc_nvfp4(NB);
+      int stage = 0, nseg = 0;
+      uint32_t phase = 0;
+      bool ok = true;
+      for (int i = i0; ok && i < i1; i++) {
+        const int4 w0 = ldg16(g.items + i), w1 = ldg16(reinterpret_cast<const int4*>(g.items + i) + 1);
+        const int c0 = w0.z, c1 = w0.w, ksteps = w1.w, n = i - i0;
+        const int buf = n % C::kAccBufs, use = n / C::kAccBufs;
+        if (!mbar_wait_bounded(aempty0 + 8 * buf, (use & 1) ^ 1, abort_flag, &g_status, kStatusAccumFreeTimeout)) break;
+        tc_fence_after_sync();
+        const uint32_t d_tmem = tmem_base + buf * NB;
+        uint32_t accumulate = 0;
+        for (int c = c0; c < c1; c++) {
+          if (!mbar_wait_bounded(sfr0 + 8 * stage, phase, abort_flag, &g_status, kStatusFullWaitTimeout)) {
+            ok = false;
+            break;
+          }
+          tc_fence_after_sync();
+          const int nsteps = min(4, ksteps - 4 * c);
+          const uint32_t sbase = smem_base + stage * C::kStageBytes;
+          const uint64_t desc_p = umma_desc_k_sw128(sbase), desc_q = umma_desc_k_sw128(sbase + C::kOffQ);
+          const uint32_t sf_col = tmem_base + C::kSfCol0 + C::kSfCols * stage;
+          for (int ks = 0; ks < nsteps; ks++) {
+            umma_nvfp4(d_tmem, desc_p + 2 * ks, desc_q + 2 * ks, idesc, sf_col + 4 * ks, sf_col + 16 + 4 * ks, accumulate);
+            accumulate = 1;
+          }
+          umma_commit(empty0 + 8 * stage);
+          if (++stage == STAGES) stage = 0, phase ^= 1;
+        }
+        if (ok) umma_commit(afull0 + 8 * buf);
+        nseg = n + 1;
+      }
+      for (int j = nseg - 1; ok && j >= 0 && j >= nseg - C::kAccBufs; j--)
+        ok = mbar_wait_bounded(aempty0 + 8 * (j % C::kAccBufs), (j / C::kAccBufs) & 1, abort_flag, &g_status,
+                               kStatusAccumFreeTimeout, 64);
+    }
+  } else if (warp >= C::kFeederWarp0) {
+    // ------------------------------------------------------------------------------------------ scale feeders
+    const uint32_t lane_base = uint32_t((warp & 3) * 32) << 16;
+    const int units = __ldg(g.cta_units + blockIdx.x);
+    int stage = 0;
+    uint32_t phase = 0;
+    for (int u = 0; u < units; u++) {
+      if (!warp_wait(full0 + 8 * stage, phase, abort_flag, &g_status, kStatusFullWaitTimeout, 32)) break;
+      const uint8_t* sb = smem + stage * C::kStageBytes;
+      const uint4* sfp = reinterpret_cast<const uint4*>(sb + C::kOffSfP) + lane;
+      const uint4* sfq = reinterpret_cast<const uint4*>(sb + C::kOffSfQ) + lane;
+      const uint32_t taddr = tmem_base + lane_base + C::kSfCol0 + C::kSfCols * stage;
+      uint4 a[4];
+#pragma unroll
+      for (int ks = 0; ks < 4; ks++) a[ks] = sfp[32 * ks];
+      tmem_st16(taddr, a);
+#pragma unroll
+      for (int ks = 0; ks < 4; ks++) a[ks] = sfq[32 * ks];
+      tmem_st16(taddr + 16, a);
+      tmem_st_wait();
+      tc_fence_before_sync();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(sfr0 + 8 * stage);
+      if (++stage == STAGES) stage = 0, phase ^= 1;
+    }
+  } else {
+    // ------------------------------------------------------------------------------------------ epilogue
+    const int quarter = warp & 3;
+    const int row = quarter * 32 + lane;  // weight row of the tile = output channel
+    GemmParams p = {};                    // the epilogue's view of the current problem
+    p.M = g.M;
+    int cur_prob = -1, epi = 0;
+    for (int i = i0; i < i1; i++) {
+      const int4 w0 = ldg16(g.items + i), w1 = ldg16(reinterpret_cast<const int4*>(g.items + i) + 1);
+      const int tile = w0.y, slot = w1.x, nparts = w1.y, slot0 = w1.z;
+      const int counter = __ldg(&g.items[i].counter);
+      if (w0.x != cur_prob) {
+        cur_prob = w0.x;
+        const GroupProblemDev* q = g.probs + cur_prob;
+        p.d = q->d, p.c = q->c, p.alpha = q->alpha, p.alpha_up = q->alpha_up, p.beta = q->beta, p.N = q->N, epi = q->epi;
+      }
+      auto store = [&](const float(&v)[8], int m0) {
+        if (epi == kEpiGluBf16) store_swapped<kEpiGluBf16>(p, v, m0, tile, row, xchg);
+        else if (epi == kEpiBf16) store_swapped<kEpiBf16>(p, v, m0, tile, row, xchg);
+        else store_swapped<kEpiF32>(p, v, m0, tile, row, xchg);
+      };
+      const int n = i - i0, buf = n % C::kAccBufs;
+      if (!warp_wait(afull0 + 8 * buf, (n / C::kAccBufs) & 1, abort_flag, &g_status, kStatusAccumWaitTimeout, 128)) break;
+      tc_fence_after_sync();
+      const uint32_t taddr = tmem_base + (uint32_t(quarter * 32) << 16) + buf * NB;
+      if (slot < 0) {
+        for (int m0 = 0; m0 < p.M; m0 += 8) {
+          float v[8];
+          tmem_ld8(taddr + m0, v);
+          tmem_ld_wait();
+          store(v, m0);
+        }
+        tc_fence_before_sync();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(aempty0 + 8 * buf);
+        continue;
+      }
+      // A piece of a cut tile: leave the partial sums, count the arrival; whoever delivers the last piece sums all of
+      // them in ascending K order (whatever the order of arrival) and finishes the tile.
+      for (int m0 = 0; m0 < p.M; m0 += 8) {
+        float v[8];
+        tmem_ld8(taddr + m0, v);
+        tmem_ld_wait();
+        float* part = g.partials + (int64_t(slot) * p.M + m0) * 128 + row;
+#pragma unroll
+        for (int j = 0; j < 8; j++)
+          if (m0 + j < p.M) __stcg(part + j * 128, v[j]);
+      }
+      tc_fence_before_sync();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(aempty0 + 8 * buf);
+      epi_bar();  // every partial sum of this CTA is written ...
+      if (threadIdx.x == 64) {
+        __threadfence();  // ... and published device-wide before the arrival is counted
+        *last_flag = atomicAdd(g.counters + counter, 1) == nparts - 1;
+      }
+      epi_bar();
+      if (!*last_flag) continue;
+      __threadfence();
+      if (p.M <= 2) {
+        // one or two tokens (plain decode): up to eight pieces in flight, one round trip
+        float v[8] = {};
+        for (int q0 = 0; q0 < nparts; q0 += 8) {
+          float x[8][2];
+#pragma unroll
+          for (int q = 0; q < 8; q++) {
+            if (q0 + q < nparts) {
+              const float* part = g.partials + int64_t(slot0 + q0 + q) * p.M * 128 + row;
+              x[q][0] = __ldcg(part);
+              x[q][1] = p.M > 1 ? __ldcg(part + 128) : 0.f;
+            }
+          }
+#pragma unroll
+          for (int q = 0; q < 8; q++) {
+            if (q0 + q < nparts) {
+              v[0] = (q0 + q == 0) ? x[q][0] : __fadd_rn(v[0], x[q][0]);
+              v[1] = (q0 + q == 0) ? x[q][1] : __fadd_rn(v[1], x[q][1]);
+            }
+          }
+        }
+        store(v, 0);
+      } else {
+        for (int m0 = 0; m0 < p.M; m0 += 8) {
+          float v[8];
+          for (int q0 = 0; q0 < nparts; q0 += 4) {  // four pieces in flight at a time
+            float x[4][8];
+#pragma unroll
+            for (int q = 0; q < 4; q++) {
+              if (q0 + q < nparts) {
+                const float* part = g.partials + (int64_t(slot0 + q0 + q) * p.M + m0) * 128 + row;
+#pragma unroll
+                for (int j = 0; j < 8; j++) x[q][j] = m0 + j < p.M ? __ldcg(part + j * 128) : 0.f;
+              }
+            }
+#pragma unroll
+            for (int q = 0; q < 4; q++) {
+              if (q0 + q < nparts) {
+#pragma unroll
+                for (int j = 0; j < 8; j++) v[j] = (q0 + q == 0) ? x[q][j] : __fadd_rn(v[j], x[q][j]);
+              }
+            }
+          }
+          store(v, m0);
+        }
+      }
+      if (threadIdx.x == 64) g.counters[counter] = 0;  // the counters are zero again when the kernel ends
+    }
+  }
+
+  __syncwarp();
+  tc_fence_before_sync();
+  __syncthreads();
+  if (warp == 1) {
+    __syncwarp();
+    tc_fence_after_sync();
+    tmem_dealloc(tmem_base, C::kTmemCols);
+  }
+}
+
+// ------------------------------------------------------------------------------------------------ host side
+
+constexpr int kGroupMaxProblems = 4096;
+
+int group_tokens_tile(int M) { return M <= 16 ? 16 : M <= 32 ? 32 : M <= 64 ? 64 : 128; }
+
+int64_t align_up(int64_t v, int64_t a) { return (v + a - 1) / a * a; }
+
+int check_group_problem(int i, const q27b_group_problem& q) {
+  Q27B_REQUIRE(q.N > 0 && q.N % 128 == 0, "skinny_group: problem %d: N must be a positive multiple of 128 (N = %d)", i, q.N);
+  Q27B_REQUIRE(q.K > 0 && q.K % 64 == 0, "skinny_group: problem %d: K must be a positive multiple of 64 (K = %d)", i, q.K);
+  Q27B_REQUIRE(q.epilogue >= 0 && q.epilogue <= 2, "skinny_group: problem %d: epilogue must be 0 (fp32), 1 (bf16) or 2 (SiLU*mul -> bf16)", i);
+  Q27B_REQUIRE(q.alpha_count >= 1 && q.alpha_count <= 4, "skinny_group: problem %d: 1..4 alpha segments", i);
+  Q27B_REQUIRE(q.epilogue == 0 || !q.c, "skinny_group: problem %d: a residual needs the fp32 epilogue", i);
+  return 0;
+}
+
+template <int NB, int STAGES>
+int launch_group(const GroupLaunch& gl, int ctas, cudaStream_t s) {
+  using C = Cfg<NB, STAGES, 2, true>;
+  auto kernel = skinny_group_kernel<NB, STAGES>;
+  static bool done[64] = {};
+  int dev = 0;
+  Q27B_CUDA(cudaGetDevice(&dev));
+  if (!(dev < 64 && done[dev])) {
+    Q27B_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, C::kSmemBytes));
+    if (dev < 64) done[dev] = true;
+  }
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(ctas), cfg.blockDim = dim3(C::kThreads), cfg.dynamicSmemBytes = C::kSmemBytes, cfg.stream = s;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr, cfg.numAttrs = pdl_enabled() ? 1 : 0;
+  Q27B_CUDA(cudaLaunchKernelEx(&cfg, kernel, gl));
+  return 0;
+}

@@ -28,8 +28,11 @@
 #include <algorithm>
 #include <cstdlib>
 #include <cstring>
+#include <vector>
 
+#include "../../include/q27b200/capi.h"
 #include "common.cuh"
+#include "group_plan.h"
 #include "layout.h"
 #include "ptx_sm100.cuh"
 #include "quant_block.cuh"
@@ -38,7 +41,9 @@ namespace q27b {
 
 __device__ uint32_t g_status;  // first bounded-wait timeout code since the last clear (0 = none)
 
-unsigned long long* g_trace = nullptr;  // optional device buffer for in-kernel time stamps (q27b_trace_set)
+#ifdef Q27B_TRACE
+unsigned long long* g_trace = nullptr;  // device buffer for in-kernel time stamps (q27b_trace_set; -DQ27B_TRACE builds only)
+#endif
 
 namespace {
 
@@ -71,7 +76,9 @@ struct GemmParams {
   int m_tiles, items;   // many rows
   int n_tile;           // many rows: weight rows per tile (128 or 256)
   int ext_reduce;       // weight streaming: cut tiles are summed by skinny_fixup_kernel, not by the last CTA to arrive
-  unsigned long long* trace;  // optional [cta][4][64] globaltimer samples (null: off)
+#ifdef Q27B_TRACE
+  unsigned long long* trace;  // [cta][4][64] globaltimer samples (null: off)
+#endif
 };
 
 // CTAS = CTAs of this configuration that fit on one SM (2: half the shared and tensor memory each, so that the
@@ -173,6 +180,10 @@ struct ChunkIter {
   }
 };
 
+// In-kernel time stamps for performance work exist only in builds made with -DQ27B_TRACE (make TRACE=1), as the
+// reference compiles its trace points in only under -DQ27_TRACE (engine/src/launch.cuh:17-44): the product kernels
+// carry neither the pointer nor the checks.
+#ifdef Q27B_TRACE
 __device__ __forceinline__ unsigned long long gtime() {
   unsigned long long t;
   asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
@@ -182,6 +193,11 @@ __device__ __forceinline__ unsigned long long gtime() {
   do {                                                                                                    \
     if (p.trace && (idx) < 64) p.trace[(size_t(blockIdx.x) * 4 + (kind)) * 64 + (idx)] = gtime();         \
   } while (0)
+#else
+#define TRACE(kind, idx) \
+  do {                   \
+  } while (0)
+#endif
 
 // silu(g) * u with the fast exponential and reciprocal (the reference's fused epilogue uses the same pair,
 // engine/src/gemm_mma.cu:362-378): no division slow path, and 1 / (1 + inf) = 0 for very negative gates.
@@ -1000,7 +1016,7 @@ int launch_gemm(Kern kernel, int grid, int threads, int smem, cudaStream_t s, co
   cudaLaunchAttribute attr[1];
   attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
   attr[0].val.programmaticStreamSerializationAllowed = 1;
-  cfg.attrs = attr, cfg.numAttrs = pdl ? 1 : 0;
+  cfg.attrs = attr, cfg.numAttrs = (pdl && pdl_enabled()) ? 1 : 0;
   Q27B_CUDA(cudaLaunchKernelEx(&cfg, kernel, mp, mq, p));
   return 0;
 }
@@ -1034,7 +1050,7 @@ int run_skinny(const uint8_t* a, const uint8_t* w, GemmParams& p, cudaStream_t s
     cudaLaunchAttribute attr[1];
     attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
     attr[0].val.programmaticStreamSerializationAllowed = 1;
-    cfg.attrs = attr, cfg.numAttrs = 1;
+    cfg.attrs = attr, cfg.numAttrs = pdl_enabled() ? 1 : 0;
     Q27B_CUDA(cudaLaunchKernelEx(&cfg, skinny_fixup_kernel<kEpi>, p));
   }
   return 0;
@@ -1087,8 +1103,9 @@ int skinny_common(int kEpi, int M, int N, int K, const uint8_t* a, const uint8_t
   // same whatever M it is computed with (the reference's invariant for its M <= 64 path, engine/src/skinny.cu:142-147).
   p.plan = choose_skinny_plan(N, K, 2 * sms);
   // Cut tiles: up to 8 tokens the last CTA to arrive sums them inside the kernel; above, a second small kernel
-  // does it across the whole GPU (measured cross-over on B200).
-  p.ext_reduce = plan_cuts_tiles(p.plan) && M > 8;
+  // does it across the whole GPU (measured cross-over on B200; Q27_SKINNY_EXT_REDUCE_M moves it, as the reference's
+  // switch of the same name does, engine/src/skinny.cu:494-521). Both ways add the parts in ascending K order.
+  p.ext_reduce = plan_cuts_tiles(p.plan) && M > env_int("Q27_SKINNY_EXT_REDUCE_M", 8, 0, 16);
   Q27B_REQUIRE(p.plan.grid <= kMaxParts, "skinny_fp4: more than %d CTAs", kMaxParts);
   Q27B_REQUIRE(p.plan.tiles * 4 <= kCounterBytes, "skinny_fp4: N too large (%d rows, at most %d)", N, kCounterBytes / 4 * 128);
   const size_t need = size_t(kCounterBytes + skinny_workspace_bytes(M, p.plan));
@@ -1096,7 +1113,9 @@ int skinny_common(int kEpi, int M, int N, int K, const uint8_t* a, const uint8_t
                need);
   p.counters = static_cast<int*>(ws);
   p.partials = reinterpret_cast<float*>(static_cast<uint8_t*>(ws) + kCounterBytes);
+#ifdef Q27B_TRACE
   p.trace = g_trace;
+#endif
   switch (kEpi) {
     case kEpiF32: return skinny_dispatch<kEpiF32>(a, w, p, s);
     case kEpiBf16: return skinny_dispatch<kEpiBf16>(a, w, p, s);
@@ -1139,7 +1158,7 @@ int run_many_pairs(const uint8_t* a, const uint8_t* w, GemmParams& p, cudaStream
   attr[0].val.clusterDim.x = 2, attr[0].val.clusterDim.y = 1, attr[0].val.clusterDim.z = 1;
   attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
   attr[1].val.programmaticStreamSerializationAllowed = 1;
-  cfg.attrs = attr, cfg.numAttrs = 2;
+  cfg.attrs = attr, cfg.numAttrs = pdl_enabled() ? 2 : 1;
   Q27B_CUDA(cudaLaunchKernelEx(&cfg, kernel, ma, mw, p));
   return 0;
 }
@@ -1171,7 +1190,9 @@ int many_common(int kEpi, int M, int N, int K, const uint8_t* a, const uint8_t* 
   p.c = (c && beta != 0.f) ? c : nullptr, p.beta = beta, p.d = d;
   p.m_tiles = (M + 127) / 128;
   p.d_sf = d_sf, p.out_gs = 1.f / out_scale;  // (IEEE division, as the quantiser kernels compute it)
+#ifdef Q27B_TRACE
   p.trace = g_trace;
+#endif
   switch (kEpi) {
     case kEpiF32: return run_many<kEpiF32>(a, w, p, s);
     case kEpiBf16: return run_many<kEpiBf16>(a, w, p, s);
@@ -1179,6 +1200,8 @@ int many_common(int kEpi, int M, int N, int K, const uint8_t* a, const uint8_t* 
     default: return run_many<kEpiGluBf16>(a, w, p, s);
   }
 }
+
+#include "skinny_group.inl"
 
 AlphaSeg make_alpha(int count, const int* begin, const float* alpha) {
   AlphaSeg a = {};
@@ -1270,7 +1293,101 @@ int q27b_gemm_fp4_glu(int M, int I, int K, const uint8_t* a, const uint8_t* a_sf
                      static_cast<cudaStream_t>(stream), q_sf, out_scale);
 }
 
-int q27b_trace_set(void* buf) { g_trace = static_cast<unsigned long long*>(buf); return 0; }
+int q27b_trace_set(void* buf) {
+#ifdef Q27B_TRACE
+  g_trace = static_cast<unsigned long long*>(buf);
+  return 0;
+#else
+  Q27B_REQUIRE(!buf, "trace_set: this library was built without the trace points (build with make TRACE=1)");
+  return 0;
+#endif
+}
+
+// ---- the grouped weight-streaming GEMM ------------------------------------------------------------------------------
+
+int q27b_skinny_group_build(int M, int n_problems, const q27b_group_problem* problems, void* table_host, size_t table_cap,
+                            size_t* table_bytes, size_t* ws_bytes) {
+  Q27B_REQUIRE(M >= 1 && M <= 128, "skinny_group: M must be 1..128 (M = %d)", M);
+  Q27B_REQUIRE(n_problems >= 1 && n_problems <= kGroupMaxProblems && problems, "skinny_group: 1..%d problems", kGroupMaxProblems);
+  const int sms = sm_count();
+  Q27B_REQUIRE(sms > 0, "skinny_group: no CUDA device");
+  std::vector<GroupShape> shapes(n_problems);
+  for (int i = 0; i < n_problems; i++) {
+    if (int rc = check_group_problem(i, problems[i])) return rc;
+    shapes[i] = {problems[i].N, problems[i].K};
+  }
+  const GroupSchedule sch = schedule_group(shapes.data(), n_problems, 2 * sms);
+  const int ctas = int(sch.cta_units.size());
+  GroupHeader h = {};
+  h.magic = kGroupMagic, h.M = M, h.nb = group_tokens_tile(M), h.n_problems = n_problems, h.n_ctas = ctas;
+  h.n_items = int(sch.items.size()), h.counters = sch.counters, h.sms = sms, h.slots = sch.slots;
+  h.off_problems = sizeof(GroupHeader);
+  h.off_cta_first = h.off_problems + int64_t(n_problems) * sizeof(GroupProblemDev);
+  h.off_cta_units = align_up(h.off_cta_first + int64_t(ctas + 1) * 4, 16);
+  h.off_items = align_up(h.off_cta_units + int64_t(ctas) * 4, 128);
+  h.table_bytes = h.off_items + int64_t(h.n_items) * sizeof(GroupItem);
+  h.ws_bytes = align_up(int64_t(sch.counters) * 4, 256) + sch.slots * M * 512;
+  if (table_bytes) *table_bytes = size_t(h.table_bytes);
+  if (ws_bytes) *ws_bytes = size_t(h.ws_bytes);
+  if (!table_host) return 0;  // size query
+  Q27B_REQUIRE(table_cap >= size_t(h.table_bytes), "skinny_group: table buffer too small (%zu bytes, need %lld)", table_cap,
+               (long long)h.table_bytes);
+  uint8_t* base = static_cast<uint8_t*>(table_host);
+  memset(base, 0, size_t(h.table_bytes));
+  memcpy(base, &h, sizeof h);
+  for (int i = 0; i < n_problems; i++) {
+    const q27b_group_problem& q = problems[i];
+    Q27B_REQUIRE(q.a && q.a_sf && q.w && q.w_sf && q.d, "skinny_group: problem %d: null pointer", i);
+    Q27B_REQUIRE(aligned16(q.a) && aligned16(q.a_sf) && aligned16(q.w) && aligned16(q.w_sf) && aligned16(q.d) && aligned16(q.c),
+                 "skinny_group: problem %d: operands, scales, residual and output must be 16-byte aligned", i);
+    GroupProblemDev d = {};
+    if (int rc = make_operand_map(&d.tmap_w, q.w, q.N, q.K, 128)) return rc;
+    if (int rc = make_operand_map(&d.tmap_a, q.a, M, q.K, h.nb)) return rc;
+    d.d = q.d, d.c = (q.c && q.beta != 0.f) ? q.c : nullptr, d.beta = q.beta;
+    d.alpha = make_alpha(q.alpha_count, q.alpha_begin, q.alpha), d.alpha_up = q.alpha_up;
+    d.N = q.N, d.epi = q.epilogue == 2 ? kEpiGluBf16 : q.epilogue == 1 ? kEpiBf16 : kEpiF32;
+    memcpy(base + h.off_problems + int64_t(i) * sizeof d, &d, sizeof d);
+  }
+  memcpy(base + h.off_cta_first, sch.cta_first.data(), size_t(ctas + 1) * 4);
+  int* units = reinterpret_cast<int*>(base + h.off_cta_units);
+  for (int g = 0; g < ctas; g++) units[g] = int(sch.cta_units[g]);
+  GroupItem* items = reinterpret_cast<GroupItem*>(base + h.off_items);
+  for (int i = 0; i < h.n_items; i++) {
+    GroupItem it = sch.items[i];
+    const q27b_group_problem& q = problems[it.prob];
+    it.w_sf_tile = q.w_sf + int64_t(it.tile) * it.ksteps * 512;
+    it.a_sf = q.a_sf;
+    items[i] = it;
+  }
+  return 0;
+}
+
+int q27b_skinny_fp4_group(const void* table_host, const void* table_dev, void* ws, size_t ws_bytes, void* stream) {
+  Q27B_REQUIRE(table_host && table_dev, "skinny_group: null table");
+  GroupHeader h;
+  memcpy(&h, table_host, sizeof h);
+  Q27B_REQUIRE(h.magic == kGroupMagic, "skinny_group: table_host does not hold a table made by q27b_skinny_group_build");
+  Q27B_REQUIRE((reinterpret_cast<uintptr_t>(table_dev) & 127u) == 0, "skinny_group: the device copy of the table must be 128-byte aligned");
+  Q27B_REQUIRE(h.sms == sm_count(), "skinny_group: the table was built for a device with %d multiprocessors", h.sms);
+  Q27B_REQUIRE(ws && aligned16(ws) && ws_bytes >= size_t(h.ws_bytes), "skinny_group: workspace too small (%zu bytes, need %lld)",
+               ws_bytes, (long long)h.ws_bytes);
+  const uint8_t* base = static_cast<const uint8_t*>(table_dev);
+  GroupLaunch gl = {};
+  gl.probs = reinterpret_cast<const GroupProblemDev*>(base + h.off_problems);
+  gl.cta_first = reinterpret_cast<const int*>(base + h.off_cta_first);
+  gl.cta_units = reinterpret_cast<const int*>(base + h.off_cta_units);
+  gl.items = reinterpret_cast<const GroupItem*>(base + h.off_items);
+  gl.M = h.M;
+  gl.counters = static_cast<int*>(ws);
+  gl.partials = reinterpret_cast<float*>(static_cast<uint8_t*>(ws) + align_up(int64_t(h.counters) * 4, 256));
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  switch (h.nb) {
+    case 16: return launch_group<16, 4>(gl, h.n_ctas, s);
+    case 32: return launch_group<32, 4>(gl, h.n_ctas, s);
+    case 64: return launch_group<64, 3>(gl, h.n_ctas, s);
+    default: return launch_group<128, 3>(gl, h.n_ctas, s);
+  }
+}
 
 // ---- the entry point that allocates nothing ---------------------------------------------------------------------
 //
@@ -1284,18 +1401,26 @@ static __device__ __align__(256) uint8_t g_static_scratch[kStaticScratchBytes];
 
 // Device address of the array above on the current device; resolved (and the counters cleared) on the first call
 // per device. In host code the array's name is only a handle for cudaGetSymbolAddress, never a pointer to pass on.
-static int static_scratch(void** out) {
-  static void* ptr[64] = {};
+// A wait that ran out inside a kernel can leave arrival counters non-zero; q27b_device_status sets `dirty` for the
+// device when it reports such a status, and the next call clears the counters again before its kernel.
+static void* g_static_ptr[64] = {};
+static bool g_static_dirty[64] = {};
+static int static_scratch(void** out, cudaStream_t stream) {
   int dev = 0;
   Q27B_CUDA(cudaGetDevice(&dev));
   Q27B_REQUIRE(dev >= 0 && dev < 64, "skinny_fp4_static: device index %d out of range", dev);
-  if (!ptr[dev]) {
+  if (!g_static_ptr[dev]) {
     void* p = nullptr;
     Q27B_CUDA(cudaGetSymbolAddress(&p, g_static_scratch));
-    Q27B_CUDA(cudaMemset(p, 0, kCounterBytes));  // (a module's globals start at zero; this also covers a reload)
-    ptr[dev] = p;
+    g_static_ptr[dev] = p;
+    g_static_dirty[dev] = true;  // (a module's globals start at zero; clearing once also covers a reload)
   }
-  *out = ptr[dev];
+  if (g_static_dirty[dev]) {
+    // on the caller's stream, so that it is ordered before the kernel whatever kind of stream that is
+    Q27B_CUDA(cudaMemsetAsync(g_static_ptr[dev], 0, kCounterBytes, stream));
+    g_static_dirty[dev] = false;
+  }
+  *out = g_static_ptr[dev];
   return 0;
 }
 
@@ -1306,7 +1431,7 @@ int q27b_skinny_fp4_static(int M, int N, int K, const uint8_t* a, const uint8_t*
                "with a caller-provided workspace", kStaticMaxM, M);
   Q27B_REQUIRE(alpha_count >= 1 && alpha_count <= 4 && alpha_begin && alpha, "skinny_fp4_static: 1..4 alpha segments");
   void* ws = nullptr;
-  if (int rc = static_scratch(&ws)) return rc;
+  if (int rc = static_scratch(&ws, static_cast<cudaStream_t>(stream))) return rc;
   return skinny_common(kEpiF32, M, N, K, a, a_sf, w, w_sf, make_alpha(alpha_count, alpha_begin, alpha), 1.f,
                        (c && beta != 0.f) ? c : nullptr, beta, d, ws, kStaticScratchBytes, static_cast<cudaStream_t>(stream));
 }
@@ -1327,6 +1452,12 @@ int q27b_device_status(uint32_t* status) {
   Q27B_CUDA(cudaMemcpyFromSymbol(status, g_status, sizeof(uint32_t)));
   const uint32_t zero = 0;
   Q27B_CUDA(cudaMemcpyToSymbol(g_status, &zero, sizeof(uint32_t)));
+  if (*status != 0) {
+    // a kernel gave up half-way: arrival counters may be non-zero. The library's own scratch is cleared by the next
+    // q27b_skinny_fp4_static call; a caller-owned workspace must be re-zeroed by the caller (its first 16 KiB).
+    int dev = 0;
+    if (cudaGetDevice(&dev) == cudaSuccess && dev >= 0 && dev < 64) g_static_dirty[dev] = true;
+  }
   return 0;
 }
 

@@ -38,14 +38,14 @@ SIGNATURES = {
     "q27b_skinny_fp4_glu_bf16": ([I, I, I, P, P, P, P, F, F, P, P, SZ, P], I),
     "q27b_skinny_fp4_static": ([I, I, I, P, P, P, P, I, P, P, P, F, P, P], I),
     "q27b_skinny_workspace_bytes": ([I, I, I], I64),
+    "q27b_skinny_group_build": ([I, I, P, P, SZ, P, P], I),
+    "q27b_skinny_fp4_group": ([P, P, P, SZ, P], I),
+    "q27t_skinny_fp4_group": ([P, P, P, SZ], I),
     "q27b_gemm_fp4": ([I, I, I, P, P, P, P, F, P, F, P, P], I),
     "q27b_gemm_fp4_bf16": ([I, I, I, P, P, P, P, F, P, P], I),
     "q27b_gemm_fp4_glu_bf16": ([I, I, I, P, P, P, P, F, F, P, P], I),
     "q27b_gemm_fp4_glu": ([I, I, I, P, P, P, P, F, F, F, P, P, P], I),
     "q27b_device_status": ([U32P], I),
-    "q27b_ref_gemm_fp4": ([I, I, I, P, P, P, P, F, P, P], I),
-    "q27b_skinny_plan": ([I, I, I, I, P, I, P, P, P], I),
-    "q27b_skinny_tile_parts": ([I, I, I, I, P, I], I),
     "q27t_last_us": ([], F),
     "q27t_sf_bytes": ([I64, I64], I64),
     "q27t_quant_fp4": ([P, I, I, F, P, P], I),
@@ -67,12 +67,23 @@ SIGNATURES = {
     "q27t_skinny_fp4_segments": ([I, I, I, P, P, P, P, I, P, P, P, F, P, P, SZ], I),
     "q27t_skinny_fp4_bf16": ([I, I, I, P, P, P, P, F, P, P, SZ], I),
     "q27t_skinny_fp4_glu_bf16": ([I, I, I, P, P, P, P, F, F, P, P, SZ], I),
-    "q27t_ref_gemm_fp4": ([I, I, I, P, P, P, P, F, P], I),
     "q27t_skinny_fp4_static": ([I, I, I, P, P, P, P, F, P, F, P], I),
     "q27t_bench_gemm": ([I, I, I, I, P, P, P, P, I64, I64, I, I, P, P, SZ, P], I),
 }
 
+# the test-scaffolding library (include/q27b200/testing.h); only the test suite loads it
+TEST_LIB_PATH = os.path.join(HERE, "libq27b200_test.so")
+TEST_SIGNATURES = {
+    "q27b_skinny_plan": ([I, I, I, I, P, I, P, P, P], I),
+    "q27b_skinny_tile_parts": ([I, I, I, I, P, I], I),
+    "q27b_skinny_group_plan": ([I, P, P, I, P, I, P, P, P], I),
+    "q27t_ref_gemm_fp4": ([I, I, I, P, P, P, P, F, P], I),
+    "q27t_cxx_launchers": ([P, I, I, F, P, P, I, P, P, I, P, P, P, P, SZ, I, P, P, F, F, F, P, P], I),
+    "q27t_cxx_throws": ([], I),
+}
+
 _lib = None
+_test_lib = None
 
 
 def build(verbose: bool = False) -> str:
@@ -97,6 +108,20 @@ def lib():
     return _lib
 
 
+def scaffold_lib():
+    """The scaffolding library of the test suite; it resolves its references to the product library, loaded first."""
+    global _test_lib
+    if _test_lib is None:
+        lib()
+        if not os.path.exists(TEST_LIB_PATH):
+            raise RuntimeError(f"{TEST_LIB_PATH} is missing: build it with `make -C {CSRC}`")
+        _test_lib = ctypes.CDLL(TEST_LIB_PATH)
+        for name, (args, res) in TEST_SIGNATURES.items():
+            fn = getattr(_test_lib, name)
+            fn.argtypes, fn.restype = args, res
+    return _test_lib
+
+
 def _arg(x):
     if x is None:
         return None
@@ -113,7 +138,7 @@ def last_error() -> str:
 
 def call(name, *args):
     """Calls an entry point that returns a status; raises RuntimeError with the library's message on failure."""
-    rc = getattr(lib(), name)(*map(_arg, args))
+    rc = getattr(scaffold_lib() if name in TEST_SIGNATURES else lib(), name)(*map(_arg, args))
     if rc != 0:
         raise RuntimeError(f"{name}: {last_error()}")
 

@@ -12,13 +12,13 @@ import torch
 
 from oracle import nvfp4_oracle as O
 from q27b200 import configs, layouts, shard, weights
-from q27b200.q27lib import SIGNATURES, call, last_error, lib
+from q27b200.q27lib import SIGNATURES, TEST_SIGNATURES, call, last_error, lib, scaffold_lib
 
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 
 
-def declared_functions():
-    text = open(os.path.join(ROOT, "include", "q27b200", "capi.h")).read()
+def declared_functions(header="capi.h"):
+    text = open(os.path.join(ROOT, "include", "q27b200", header)).read()
     text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
     return sorted(set(re.findall(r"\b(q27[bt]?_[a-z0-9_]+)\s*\(", text)))
 
@@ -31,6 +31,11 @@ def test_library_exports_every_declared_symbol():
         assert hasattr(l, n), f"{n} is declared in capi.h but not exported"
         assert n in SIGNATURES, f"{n} has no ctypes signature"
     assert sorted(SIGNATURES) == names  # and nothing is bound that the header does not declare
+    # the scaffolding of the test suite lives in a library of its own, which the product library does not export
+    scaffolding = declared_functions("testing.h")
+    assert sorted(TEST_SIGNATURES) == scaffolding
+    for n in scaffolding:
+        assert hasattr(scaffold_lib(), n) and not hasattr(l, n), n
 
 
 def test_sf_layout_matches_oracle():
@@ -50,7 +55,7 @@ def test_sf_layout_matches_oracle():
 
 
 def plan(N, K, slots):
-    l = lib()
+    l = scaffold_lib()
     grid, units, split = ctypes.c_int(), ctypes.c_int64(), ctypes.c_int()
     seg = (ctypes.c_int * (4 * 2048))()
     l.q27b_skinny_plan(N, K, slots, -1, None, 0, ctypes.byref(grid), ctypes.byref(units), ctypes.byref(split))
@@ -72,7 +77,7 @@ def test_skinny_plan_covers_every_unit_once(N, K, slots):
     cover = np.zeros((tiles, chunks), dtype=np.int32)
     slot_of = {}
     sizes = []
-    l = lib()
+    l = scaffold_lib()
     for g, segs in enumerate(pieces):
         sizes.append(sum(c1 - c0 for _, c0, c1, _ in segs))
         for t, c0, c1, slot in segs:
@@ -112,11 +117,74 @@ def test_skinny_plan_choices():
     assert plan(248320, 5120, 296)[2] == 0     # lm_head: contiguous ranges (no wave quantisation)
 
 
-def test_plan_is_independent_of_m():
-    # the split takes no M argument at all: rows cannot depend on the number of tokens
-    import inspect
-    assert "M" not in [a for a in inspect.signature(plan).parameters]
-    assert plan(5120, 17408, 296)[:3] == plan(5120, 17408, 296)[:3]
+def group_plan(shapes, slots):
+    n = len(shapes)
+    Ns, Ks = (ctypes.c_int * n)(*[s[0] for s in shapes]), (ctypes.c_int * n)(*[s[1] for s in shapes])
+    ctas, nslots, counters = ctypes.c_int(), ctypes.c_int64(), ctypes.c_int()
+    l = scaffold_lib()
+    count = l.q27b_skinny_group_plan(n, Ns, Ks, slots, None, 0, ctypes.byref(ctas), ctypes.byref(nslots), ctypes.byref(counters))
+    buf = (ctypes.c_int * (8 * count))()
+    assert l.q27b_skinny_group_plan(n, Ns, Ks, slots, buf, count, None, None, None) == count
+    pieces = [tuple(buf[8 * i:8 * i + 8]) for i in range(count)]
+    return ctas.value, nslots.value, counters.value, pieces
+
+
+LAYER_SHAPES = [(7168, 5120), (5120, 5120), (34816, 5120), (5120, 17408)]  # q|k|v stacked, o, gate|up, down
+
+
+@pytest.mark.parametrize("shapes,slots", [(LAYER_SHAPES, 296), (LAYER_SHAPES * 3, 296), ([(384, 448), (128, 5120), (248320, 5120)], 296),
+                                          (LAYER_SHAPES, 7), ([(1024, 5120)], 264)])
+def test_group_schedule_keeps_each_problems_own_split(shapes, slots):
+    """The grouped launch deals the pieces of all problems to the CTAs, but every problem is cut exactly as its
+    stand-alone launch cuts it (same pieces, and the pieces of a cut tile in consecutive slots in ascending K order):
+    that is what makes the grouped results bit-identical to per-GEMM calls."""
+    ctas, nslots, counters, pieces = group_plan(shapes, slots)
+    assert 1 <= ctas <= slots
+    by_problem = {}
+    loads = np.zeros(ctas, dtype=np.int64)
+    last_key = {}
+    for cta, prob, tile, c0, c1, slot, nparts, slot0 in pieces:
+        assert 0 <= cta < ctas
+        by_problem.setdefault(prob, []).append((tile, c0, c1, slot, nparts, slot0))
+        loads[cta] += c1 - c0
+        assert last_key.get(cta, (-1, -1, -1)) < (prob, tile, c0)  # a CTA walks its pieces in problem order
+        last_key[cta] = (prob, tile, c0)
+    used_slots = set()
+    cut_tiles = 0
+    for prob, (N, K) in enumerate(shapes):
+        _, _, _, alone = plan(N, K, slots)
+        want = sorted((t, c0, c1) for segs in alone for t, c0, c1, _ in segs)
+        got = sorted(by_problem[prob])
+        assert [g[:3] for g in got] == want  # the same pieces as the stand-alone launch
+        chunks = (K + 255) // 256
+        tiles = {}
+        for t, c0, c1, slot, nparts, slot0 in got:
+            tiles.setdefault(t, []).append((c0, c1, slot, nparts, slot0))
+        for t, parts in tiles.items():
+            assert all(p[3] == len(parts) for p in parts)
+            assert parts[0][0] == 0 and parts[-1][1] == chunks and all(a[1] == b[0] for a, b in zip(parts, parts[1:]))
+            if len(parts) == 1:
+                assert parts[0][2] == -1
+            else:
+                cut_tiles += 1
+                assert [p[2] for p in parts] == list(range(parts[0][4], parts[0][4] + len(parts)))  # ascending K = ascending slot
+                for p in parts:
+                    assert p[2] not in used_slots
+                    used_slots.add(p[2])
+    assert used_slots == set(range(nslots)) and counters == cut_tiles
+    total = sum(N // 128 * ((K + 255) // 256) for N, K in shapes)
+    assert loads.sum() == total
+    biggest = max(c1 - c0 for _, _, _, c0, c1, _, _, _ in pieces)
+    assert loads.max() - loads.min() <= biggest  # longest-first dealing: no CTA is more than one piece ahead
+
+
+def test_group_schedule_balance_on_a_layer():
+    """One layer of the model on 296 CTA slots: every CTA streams 34 +- 2 of the 10080 stages."""
+    ctas, _, _, pieces = group_plan(LAYER_SHAPES, 296)
+    loads = np.zeros(ctas, dtype=np.int64)
+    for cta, _, _, c0, c1, *_ in pieces:
+        loads[cta] += c1 - c0
+    assert ctas == 296 and loads.sum() == 10080 and loads.max() <= 36 and loads.min() >= 32
 
 
 def test_weight_quantiser_matches_oracle(golden):

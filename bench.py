@@ -1,31 +1,38 @@
 """Benchmark of the NVFP4 weight-GEMM path.
 
-One "step" is one pass of the hot path over one batch: quantise the bf16 activation to NVFP4, then the
-weight-streaming GEMM with its fused epilogue. At one GPU the workload is the speculative-verify gate | up
-projection (x bf16 [16, 5120], W NVFP4 [34816, 5120], SiLU*mul -> bf16 [16, 17408]); with N > 1 GPUs the weight
-rows are sharded N ways (every rank computes its block of output columns, no reduction) and one NCCL all-gather
-of the bf16 output is timed separately.
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+                    [--only sweep,cfg0,cfg1,cfg2,cfg4] [--m M] [--layers L] [--group-layers G] [--no-cpu]
 
-    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--config 0|1|2|3|4]
-                    [--m M] [--layers L] [--separate-qkv] [--no-graph] [--no-cpu]
+Prints ONE JSON line (rank 0). The headline is the configuration the bandwidth target is stated on: the whole-model
+decode weight sweep (64 layers x {q|k|v stacked, o, gate|up with SiLU*mul, down}, every projection in its own device
+memory, 11.9 GB in all) at M = 16 tokens. One "step" is one sweep: per group of G layers one launch that quantises
+the layers' bf16 activations to NVFP4 and one launch of the grouped weight-streaming GEMM over all their projections
+(G = 64 by default: the whole sweep is one persistent launch). `value` = algorithmic bytes of a sweep / device time,
+inputs resident in HBM, exactly K steps replayed from a CUDA graph and timed with CUDA events. The same line carries
 
-Prints one JSON line (rank 0). `value` = algorithmic bytes of the step / device time with everything resident in
-HBM and the weights rotating through more than L2-size of distinct copies (the steps are replayed from a CUDA
-graph unless --no-graph); `e2e` = the same step through the host API with the activation coming from pinned host
-memory and the result copied back to pinned host memory every step, copies inside the timed region. `--impl
-reference` times the CPU restatement of the reference's own path (fake-quantise, fp32 matmul against the
-dequantised weight, SiLU*mul) on the host cores instead.
+  "sweep":   GB/s and fraction of the measured HBM peak for every M in 1..128 (same mode as the headline),
+  "modes":   the M = 16 sweep run per GEMM (one launch per projection, chained with programmatic dependent launch,
+             the way the reference's engine runs a decode step) and in groups of 1, 8 and 64 layers,
+  "configs": the single-GEMM configurations cfg0 (decode GEMV), cfg1 (verify gate|up), cfg2 (batched verify down)
+             and cfg4 (prefill, tensor-bound), each with its roofline and clocks,
+  "e2e":     the headline sweep driven from HOST buffers: activations copied from pinned host memory and the last
+             layer's outputs copied back every step, copies inside the timed region,
+  "verified": after every timed region the outputs left by the LAST timed step are compared bit for bit with the
+             same step run one kernel at a time (device synchronised in between, programmatic launch off).
 
---config 0 / 2 / 4 run the other single-GEMM configurations (decode GEMV, batched verify down-projection, prefill
-chunk: reported in TFLOP/s against the tensor roof). --config 3 is the whole-model decode weight sweep: 64 layers
-(--layers) x {q|k|v stacked, o, gate_up, down} at M = 1 ... 128 (--m for one M), every projection in its own
-device memory; its line carries the GB/s of every M under "sweep".
+With N > 1 GPUs the weight rows are sharded N ways (no reduction anywhere); the step then ends with ONE NCCL
+all-gather of all outputs of the sweep (captured in the same graph), and `value` includes it.
+
+--impl reference times the CPU restatement of the reference's own path (fake-quantise, fp32 matmul against the
+once-dequantised weight, SiLU*mul) on the host cores for the same workload, on a bounded sample of it.
 """
 
 from __future__ import annotations
 
 import argparse
+import ctypes
 import json
+import math
 import os
 import subprocess
 import sys
@@ -40,10 +47,9 @@ import torch  # noqa: E402
 
 L2_BYTES = 126 * 1024 * 1024
 FALLBACK_HBM_GBS = 6650.0
-# dram__bytes_read.sum + dram__bytes_write.sum of one launch of the GEMM kernel on the benchmark workload, from the
-# ncu capture summarised in profiles/ (None where no capture has been taken).
-NCU_TRAFFIC_BYTES = {1: 104_100_000}  # profiles/umma_gemm_kernel_cfg1_verify_gate_up.md
-
+FALLBACK_BF16_TFLOPS = 1590.0
+DTYPE = "nvfp4 (e2m1 x e2m1, ue4m3 scale per 16, fp32 accumulate)"
+MIN_REGION_MS = 60.0  # sub-configurations are replayed until their timed region is at least this long
 
 _json_out = None
 
@@ -54,12 +60,26 @@ def emit(text: str) -> None:
     out.flush()
 
 
-def peaks():
+def log(*a):
+    print(*a, file=sys.stderr, flush=True)
+
+
+def measured_peaks():
     path = os.path.join(ROOT, "MEASURED_PEAKS.json")
     if os.path.exists(path):
         p = json.load(open(path))
-        return float(p["hbm_gbs"]), "measured (MEASURED_PEAKS.json: copy bandwidth)"
-    return FALLBACK_HBM_GBS, "fallback (6.65 TB/s, earlier measurement on this pool)"
+        return {"hbm_gbs": float(p["hbm_gbs"]), "bf16_tflops": float(p["bf16_tflops"]),
+                "bf16_tflops_sustained": float(p.get("bf16_tflops_sustained", p["bf16_tflops"])),
+                "source": "measured (MEASURED_PEAKS.json)"}
+    return {"hbm_gbs": FALLBACK_HBM_GBS, "bf16_tflops": FALLBACK_BF16_TFLOPS, "bf16_tflops_sustained": 1400.0,
+            "source": "fallback (6.65 TB/s, 1.59 PFLOP/s: earlier measurements on this pool)"}
+
+
+def ncu_traffic():
+    """dram bytes per launch from the ncu captures summarised under profiles/ (a record of those captures, keyed by
+    configuration; null where none was taken). Not measured by this run."""
+    path = os.path.join(ROOT, "profiles", "ncu_traffic.json")
+    return json.load(open(path)) if os.path.exists(path) else {}
 
 
 class ClockSampler:
@@ -73,7 +93,7 @@ class ClockSampler:
 
     def __enter__(self):
         try:
-            self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits", "-lms", "50",
+            self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits", "-lms", "25",
                                           "-i", str(self.index)], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
             self.thread = threading.Thread(target=lambda: self.lines.extend(self.proc.stdout), daemon=True)
             self.thread.start()
@@ -84,50 +104,32 @@ class ClockSampler:
 
     def __exit__(self, *a):
         if self.proc:
-            time.sleep(0.1)
+            time.sleep(0.05)
             self.proc.terminate()
             self.thread.join(timeout=2)
 
     def summary(self):
-        sm, mx, reasons = [], 0.0, set()
+        rows, mx, reasons = [], 0.0, set()
         names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
         for ln in self.lines:
             f = [x.strip() for x in ln.split(",")]
             if len(f) < 7:
                 continue
             try:
-                sm.append(float(f[0])), (mx := max(mx, float(f[1])))
+                rows.append((float(f[0]), float(f[2])))
+                mx = max(mx, float(f[1]))
             except ValueError:
                 continue
             for n, v in zip(names, f[3:7]):
                 if v.lower().startswith("active"):
                     reasons.add(n)
-        return {"sm_mhz": float(np.median(sm)) if sm else None, "sm_max_mhz": mx or None, "reasons": sorted(reasons),
-                "samples": len(sm)}
-
-
-def build_layers(cfg, rank, world, nbuf_min_bytes):
-    """The rank's shard of the configuration's weight, quantised on the GPU, in `nbuf` distinct device copies
-    (identical contents; distinct memory so that no step finds its weights in L2)."""
-    from q27b200 import configs, shard, weights
-    from q27b200.linear import Fp4Linear
-
-    x = configs.make_x(cfg)
-    in_scale = configs.input_scale_of(x)
-    w = configs.make_w(cfg.N, cfg.K, 1000 + cfg.index, cfg.w_std).cuda()
-    codes, sfb, g = weights.quantize_weight_rtn(w)
-    del w
-    if cfg.glu:
-        codes, sfb = weights.interleave_gate_up(codes), weights.interleave_gate_up(sfb)
-    b, e = shard.shard_rows(cfg.N, world, rank, cfg.glu)
-    codes, sfs = codes[b:e].contiguous(), weights.swizzle_scales(sfb[b:e])
-    n_out = (e - b) // 2 if cfg.glu else e - b
-    per = codes.numel() + sfs.numel()
-    nbuf = max(2, -(-nbuf_min_bytes // per))
-    ws = torch.zeros(48 << 20, dtype=torch.uint8, device="cuda")  # zeroed once, as the contract asks
-    layers = [Fp4Linear(codes if i == 0 else codes.clone(), sfs if i == 0 else sfs.clone(), g, in_scale, n_out, cfg.K,
-                        cfg.glu, ws) for i in range(nbuf)]
-    return x, in_scale, layers, n_out
+        if not rows:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "samples": 0}
+        # "under load" = the samples in the upper half of the power readings seen (the sampler also sees idle time)
+        power = sorted(p for _, p in rows)
+        busy = [c for c, p in rows if p >= power[len(power) // 2]]
+        return {"sm_mhz": float(np.median(busy)), "sm_max_mhz": mx, "reasons": sorted(reasons), "samples": len(rows),
+                "power_w_max": power[-1]}
 
 
 def sync_all(world):
@@ -144,19 +146,18 @@ def max_over_ranks(ms, world):
     return float(t.item())
 
 
-def timed(fn, steps, warmup, world, graph=False, after=None, before=None, graph_cap=None):
-    """`steps` calls of fn(i) bracketed by a barrier + synchronize, timed with CUDA events on the current stream
-    (the stream every launch of the library goes to); max over ranks, in ms. graph=True: the steps are captured
-    once into a CUDA graph and the timed region is its replay, so that the host's launch cost (two ctypes calls
-    and two tensor-map encodings per step from Python) does not sit between the kernels - the way the reference
-    engine runs its decode step (engine/src/model.cc:1388-1461) and times its GEMMs (engine/src/capi.cc:57-92)."""
+def timed(fn, steps, warmup, world, graph=True, graph_cap=None, busy_ms=0.0):
+    """Exactly `steps` calls of fn(i), bracketed by a barrier + synchronize, timed with CUDA events on the current
+    stream (the stream every launch of the library goes to); max over ranks, in ms. graph=True: `per` steps are
+    captured once into a CUDA graph and the timed region is steps / per replays of it, so that the host's launch cost
+    (ctypes calls and tensor-map encodings from Python) does not sit between the kernels - the way the reference engine
+    runs its decode step (engine/src/model.cc:1388-1461) and times its GEMMs (engine/src/capi.cc:57-92). busy_ms: the
+    graph is replayed untimed for about that long first (a clock sampler then sees the GPU under this load)."""
     for i in range(warmup):
         fn(i)
     sync_all(world)
     run = None
     if graph:
-        # the graph holds `per` steps and is replayed steps / per times (per = steps unless a cap is given: a step
-        # of hundreds of launches makes a graph of all the steps needlessly large)
         per = steps
         if graph_cap:
             per = max(d for d in range(1, min(graph_cap, steps) + 1) if steps % d == 0)
@@ -164,16 +165,19 @@ def timed(fn, steps, warmup, world, graph=False, after=None, before=None, graph_
         side = torch.cuda.Stream()
         side.wait_stream(torch.cuda.current_stream())
         with torch.cuda.stream(side):
-            if before:
-                before()
             with torch.cuda.graph(g, stream=side):
                 for i in range(per):
                     fn(warmup + i)
-                if after:
-                    after()  # other streams the steps used rejoin the captured stream
         torch.cuda.current_stream().wait_stream(side)
         g.replay()  # once untimed
         sync_all(world)
+        if busy_ms > 0:
+            t0 = time.perf_counter()
+            while (time.perf_counter() - t0) * 1e3 < busy_ms:
+                for _ in range(4):
+                    g.replay()
+                torch.cuda.synchronize()
+            sync_all(world)
 
         def run():
             for _ in range(steps // per):
@@ -185,64 +189,41 @@ def timed(fn, steps, warmup, world, graph=False, after=None, before=None, graph_
     else:
         for i in range(steps):
             fn(warmup + i)
-    if after and not run:
-        after()  # make the timed stream wait for work the steps put on another stream
     e1.record()
     sync_all(world)
     return max_over_ranks(e0.elapsed_time(e1), world)
 
 
-def cpu_reference(cfg, steps, warmup, frac_rows=4):
-    """The reference's CPU path (fake-quantise the activation, fp32 matmul against the once-dequantised weight,
-    SiLU*mul) restated by the oracle, on a bounded sample: the first 1/frac_rows of the output channels. Returns
-    (GB/s of algorithmic bytes, seconds per step, cores, description)."""
-    from oracle import nvfp4_oracle as O
-    from q27b200 import configs
+class serial_launches:
+    """Context: programmatic dependent launch off, for the one-kernel-at-a-time runs the timed results are checked
+    against (the caller synchronises the device between the launches)."""
 
-    cores = os.cpu_count() or 1
-    torch.set_num_threads(cores)
-    x = configs.make_x(cfg).float().numpy()
-    s = configs.input_scale_of(configs.make_x(cfg))
-    n_out = cfg.n_out // frac_rows // 64 * 64
-    w_full = configs.make_w(cfg.N, cfg.K, 1000 + cfg.index, cfg.w_std)
-    rows = np.concatenate([np.arange(n_out), cfg.N // 2 + np.arange(n_out)]) if cfg.glu else np.arange(n_out)
-    g = O.weight_global_scale(w_full.numpy())
-    codes, sfb, _ = O.quant_weight_rtn(w_full.numpy()[rows], g)
-    del w_full
-    wdq = torch.from_numpy(O.dequant_nvfp4(codes, sfb, g))  # dequantised once, outside the timed loop
+    def __enter__(self):
+        self.old = os.environ.get("Q27_NO_PDL")
+        os.environ["Q27_NO_PDL"] = "1"
 
-    def step():
-        xq = torch.from_numpy(O.quant_act_nvfp4(x, s))
-        y = xq @ wdq.T  # fp32, all host threads
-        if cfg.glu:
-            y = torch.nn.functional.silu(y[:, :n_out]) * y[:, n_out:]
-        return y.to(torch.bfloat16)
-
-    for _ in range(warmup):
-        step()
-    t0 = time.perf_counter()
-    for _ in range(steps):
-        step()
-    dt = (time.perf_counter() - t0) / steps
-    n_rows = len(rows)
-    sample_bytes = n_rows * cfg.K // 2 + n_rows * cfg.K // 16 + 2 * cfg.M * cfg.K + 2 * cfg.M * n_out
-    desc = (f"{cfg.name}: output channels 0..{n_out - 1} of {cfg.n_out} ({n_rows} of {cfg.N} weight rows), "
-            f"{steps} steps; weight dequantised once outside the timed loop")
-    return sample_bytes / dt / 1e9, dt, cores, desc
+    def __exit__(self, *a):
+        if self.old is None:
+            os.environ.pop("Q27_NO_PDL", None)
+        else:
+            os.environ["Q27_NO_PDL"] = self.old
 
 
-def sweep_main(args, rank, world, local_rank):
-    """Configuration 3: the whole-model decode weight sweep. 64 layers x {q, k, v, o, gate_up, down}, every
-    projection in its own device memory (11.9 GB in total, far beyond L2; the contents of one quantised layer are
-    repeated), N-sharded over the ranks; per layer the kernels a model step would launch: quantise the hidden
-    state, q / k / v on it, quantise, o, quantise, gate | up with SiLU*mul, quantise, down. One "step" = the sweep
-    at one M; timed as a CUDA-graph replay; value = algorithmic bytes of the sweep / time."""
+# ------------------------------------------------------------------------------------------- the decode weight sweep
+
+
+class QuantJob(ctypes.Structure):  # q27b_quant_job (include/q27b200/capi.h)
+    _fields_ = [("x", ctypes.c_void_p), ("q", ctypes.c_void_p), ("sf", ctypes.c_void_p), ("M", ctypes.c_int),
+                ("K", ctypes.c_int), ("input_scale", ctypes.c_float), ("bf16", ctypes.c_int)]
+
+
+def build_model(layers_n, rank, world):
+    """The rank's shard of every projection of every layer: contents of one quantised layer repeated, every copy in
+    device memory of its own (so that no launch finds its weights in L2)."""
     from q27b200 import configs, shard, weights
-    from q27b200.linear import ActQuant, Fp4Linear
-    from q27b200.q27lib import device_status
+    from q27b200.linear import Fp4Linear
 
-    layers_n = args.layers
-    ws = torch.zeros(48 << 20, dtype=torch.uint8, device="cuda")
+    ws = torch.zeros(48 << 20, dtype=torch.uint8, device="cuda")  # per-GEMM workspace, zeroed once
     protos = {}
     for pi, (name, N, K, glu) in enumerate(configs.LAYER_PROJECTIONS):
         w = configs.make_w(N, K, 1000 + pi, 0.02).cuda()
@@ -250,85 +231,382 @@ def sweep_main(args, rank, world, local_rank):
         del w
         if glu:
             codes, sfb = weights.interleave_gate_up(codes), weights.interleave_gate_up(sfb)
+        shard.check_even_shards(N, world)
         b, e = shard.shard_rows(N, world, rank, glu)
         protos[name] = (codes[b:e].contiguous(), weights.swizzle_scales(sfb[b:e]), g, (e - b) // 2 if glu else e - b, K, glu)
     model = []
     for _ in range(layers_n):
-        layer = {}
-        for name, (codes, sfs, g, n_out, K, glu) in protos.items():
-            layer[name] = Fp4Linear(codes.clone(), sfs.clone(), g, 1.0, n_out, K, glu, ws)
-        if args.fuse_qkv:
-            layer["qkv"] = Fp4Linear.fused([layer.pop("q"), layer.pop("k"), layer.pop("v")])
-        model.append(layer)
-    del protos
-    results = {}
-    ms_list = list(configs.SWEEP_M) if args.m == 0 else [args.m]
-    for M in ms_list:
+        layer = {name: Fp4Linear(c.clone(), s.clone(), g, 1.0, n_out, K, glu, ws) for name, (c, s, g, n_out, K, glu) in protos.items()}
+        # q, k and v read the same activation: one stacked weight with one alpha per part, as the engine stacks
+        # projections that share an input (engine/src/weights.cc:254-267)
+        layer["qkv"] = Fp4Linear.fused([layer.pop("q"), layer.pop("k"), layer.pop("v")])
+        model.append({n: layer[n] for n in ("qkv", "o", "gate_up", "down")})
+    return model
+
+
+class Sweep:
+    """One token count of the sweep: inputs, per-layer quantised activations and outputs, and the launch sequences."""
+
+    NAMES = ("qkv", "o", "gate_up", "down")
+
+    def __init__(self, model, M, world):
+        from q27b200 import configs
+        from q27b200.linear import ActQuant
+
+        self.model, self.M, self.world, self.L = model, M, world, len(model)
         gx = torch.Generator().manual_seed(3)
-        xh = torch.randn(M, configs.HIDDEN, generator=gx).to(torch.bfloat16).cuda()
-        xo = torch.randn(M, configs.HIDDEN, generator=gx).to(torch.bfloat16).cuda()
-        xd = torch.randn(M, configs.INTER, generator=gx).to(torch.bfloat16).cuda()
-        s_h, s_o, s_d = (configs.input_scale_of(t) for t in (xh, xo, xd))
-        act_h, act_d = ActQuant(max(M, 128), configs.HIDDEN), ActQuant(max(M, 128), configs.INTER)
-        outs = {name: torch.empty(M, model[0][name].out, dtype=torch.bfloat16, device="cuda") for name in model[0]}
+        self.x_host = {"h": torch.randn(M, configs.HIDDEN, generator=gx).to(torch.bfloat16).pin_memory(),
+                       "o": torch.randn(M, configs.HIDDEN, generator=gx).to(torch.bfloat16).pin_memory(),
+                       "d": torch.randn(M, configs.INTER, generator=gx).to(torch.bfloat16).pin_memory()}
+        self.x = {k: v.cuda() for k, v in self.x_host.items()}
+        self.scale = {k: configs.input_scale_of(v) for k, v in self.x.items()}
+        self.src = {"qkv": "h", "o": "o", "gate_up": "h", "down": "d"}  # which activation a projection reads
+        # every layer has quantised activations of its own (a model's layers see different values), and its own outputs
+        self.act = [{k: ActQuant(max(M, 128), v.shape[1]) for k, v in self.x.items()} for _ in range(self.L)]
+        widths = [model[0][n].out for n in self.NAMES]
+        self.width = sum(widths)
+        self.out_all = torch.zeros(self.L, M * self.width, dtype=torch.bfloat16, device="cuda")
+        self.outs = []
+        for l in range(self.L):
+            o, off = {}, 0
+            for n, wd in zip(self.NAMES, widths):
+                o[n] = self.out_all[l, off:off + M * wd].view(M, wd)
+                off += M * wd
+            self.outs.append(o)
         for layer in model:
-            for name, lin in layer.items():
-                lin.set_in_scale(s_d if name == "down" else s_o if name == "o" else s_h)
+            for n, lin in layer.items():
+                lin.set_in_scale(self.scale[self.src[n]])
+        self.gathered = torch.empty(world, self.out_all.numel(), dtype=torch.bfloat16, device="cuda") if world > 1 else None
+        self._groups = {}
+        self._jobs = {}
 
-        def sweep(_i):
-            for layer in model:
-                q, sf = act_h.quantize(xh, s_h)
-                for name in (("qkv",) if args.fuse_qkv else ("q", "k", "v")):
-                    layer[name].gemm(M, q, sf, outs[name])
-                q, sf = act_h.quantize(xo, s_o)
-                layer["o"].gemm(M, q, sf, outs["o"])
-                q, sf = act_h.quantize(xh, s_h)
-                layer["gate_up"].gemm(M, q, sf, outs["gate_up"])
-                q, sf = act_d.quantize(xd, s_d)
-                layer["down"].gemm(M, q, sf, outs["down"])
+    # -- launch sequences --------------------------------------------------------------------------------------------
 
-        ms = timed(sweep, args.steps, min(args.warmup, 3), world, not args.no_graph, graph_cap=10)
-        per_sweep_s = ms / args.steps / 1e3
-        nbytes = configs.sweep_algorithmic_bytes(M, layers_n)
-        results[M] = {"gbs": nbytes / per_sweep_s / 1e9, "ms_per_sweep": per_sweep_s * 1e3}
+    def _quant_jobs(self, l0, l1):
+        key = (l0, l1)
+        if key not in self._jobs:
+            n = 3 * (l1 - l0)
+            jobs = (QuantJob * n)()
+            i = 0
+            for l in range(l0, l1):
+                for k in ("h", "o", "d"):
+                    a, j = self.act[l][k], jobs[i]
+                    j.x, j.q, j.sf, j.M, j.K = self.x[k].data_ptr(), a.q.data_ptr(), a.sf.data_ptr(), self.M, self.x[k].shape[1]
+                    j.input_scale, j.bf16 = self.scale[k], 1
+                    i += 1
+            table = torch.frombuffer(bytearray(bytes(jobs)), dtype=torch.uint8).cuda() if n > 4 else None
+            self._jobs[key] = (jobs, table, n)
+        return self._jobs[key]
+
+    def quantise(self, l0, l1):
+        from q27b200.q27lib import call
+
+        jobs, table, n = self._quant_jobs(l0, l1)
+        call("q27b_quant_fp4_batch", jobs, table, n, torch.cuda.current_stream().cuda_stream)
+
+    def group(self, l0, l1):
+        from q27b200.group import Fp4Group, problem_of
+
+        key = (l0, l1)
+        if key not in self._groups:
+            probs = []
+            for l in range(l0, l1):
+                for n in self.NAMES:
+                    a = self.act[l][self.src[n]]
+                    probs.append(problem_of(self.model[l][n], a.q, a.sf, self.outs[l][n]))
+            self._groups[key] = Fp4Group(self.M, probs)
+        return self._groups[key]
+
+    def drop_groups(self):
+        self._groups.clear()
+
+    def step_grouped(self, G):
+        for l0 in range(0, self.L, G):
+            l1 = min(l0 + G, self.L)
+            self.quantise(l0, l1)
+            self.group(l0, l1).launch()
+        self.gather()
+
+    def step_per_gemm(self):
+        for l in range(self.L):
+            self.quantise(l, l + 1)
+            for n in self.NAMES:
+                a = self.act[l][self.src[n]]
+                self.model[l][n].gemm(self.M, a.q, a.sf, self.outs[l][n])
+        self.gather()
+
+    def gather(self):
+        if self.world > 1:  # the one collective of the path: every rank's block of output columns, all layers at once
+            torch.distributed.all_gather_into_tensor(self.gathered.view(-1), self.out_all.view(-1))
+
+    def launches_per_step(self, G):
+        # per GEMM: the quantiser, four GEMMs and, above 8 tokens, the fix-up kernel of the three weights that are cut along K
+        n = self.L * (1 + len(self.NAMES) + (3 if self.M > 8 else 0)) if G == 0 else 2 * math.ceil(self.L / G)
+        return n + (1 if self.world > 1 else 0)
+
+    # -- checking ----------------------------------------------------------------------------------------------------
+
+    def verify(self):
+        """The outputs the last timed step left behind, against the same step run one kernel at a time."""
+        got = self.out_all.clone()
+        gathered = self.gathered.clone() if self.gathered is not None else None
+        self.out_all.zero_()
+        with serial_launches():
+            for l in range(self.L):
+                for n in self.NAMES:
+                    a = self.act[l][self.src[n]]
+                    k = self.src[n]
+                    a.quantize(self.x[k], self.scale[k])
+                    torch.cuda.synchronize()
+                    self.model[l][n].gemm(self.M, a.q, a.sf, self.outs[l][n])
+                    torch.cuda.synchronize()
+        ok = bool(torch.equal(got, self.out_all)) and bool(torch.isfinite(got.float()).all()) and bool(got.any())
+        if gathered is not None:
+            r = torch.distributed.get_rank()
+            ok = ok and bool(torch.equal(gathered[r], self.out_all.view(-1)))
+            flag = torch.tensor([int(ok)], device="cuda")
+            torch.distributed.all_reduce(flag, op=torch.distributed.ReduceOp.MIN)
+            ok = bool(flag.item())
+        return ok
+
+
+def run_sweep(args, model, rank, world, local_rank, peaks):
+    from q27b200 import configs
+    from q27b200.q27lib import device_status
+
+    L = len(model)
+    G = min(args.group_layers, L)
+    ms_list = list(configs.SWEEP_M) if args.m == 0 else [args.m]
+    head_m = 16 if 16 in ms_list else ms_list[0]
+    sweep, modes, verified, head = {}, {}, True, None
+    for M in ms_list:
+        sw = Sweep(model, M, world)
+        nbytes = configs.sweep_algorithmic_bytes(M, L)
+        if M == head_m:
+            with ClockSampler(local_rank) as clk:
+                ms = timed(lambda i: sw.step_grouped(G), args.steps, args.warmup, world, graph_cap=5, busy_ms=400.0)
+            clocks = clk.summary()
+        else:
+            ms = timed(lambda i: sw.step_grouped(G), args.steps, args.warmup, world, graph_cap=5)
+        ok = sw.verify()
+        verified = verified and ok
+        per = ms / args.steps
+        sweep[str(M)] = {"gbs": nbytes / per / 1e6, "ms_per_sweep": per, "frac": nbytes / per / 1e6 / world / peaks["hbm_gbs"],
+                         "verified": ok}
+        log(f"sweep M={M}: {sweep[str(M)]}")
+        if M == head_m:
+            head = dict(sweep[str(M)], clocks=clocks, bytes=nbytes)
+            # the same sweep in the other launch forms
+            for name, g in (("per_gemm", 0), ("group_1_layer", 1), ("group_8_layers", 8), ("group_64_layers", 64)):
+                if g > L or (g == G):
+                    continue
+                sw.drop_groups()
+                fn = (lambda i: sw.step_per_gemm()) if g == 0 else (lambda i, g=g: sw.step_grouped(g))
+                ms_mode = timed(fn, args.steps, args.warmup, world, graph_cap=5)
+                ok = sw.verify()
+                verified = verified and ok
+                modes[name] = {"gbs": nbytes / (ms_mode / args.steps) / 1e6, "ms_per_sweep": ms_mode / args.steps,
+                               "launches_per_sweep": sw.launches_per_step(g), "verified": ok}
+                log(f"mode {name}: {modes[name]}")
+            modes[f"group_{G}_layer{'s' if G > 1 else ''}"] = {"gbs": head["gbs"], "ms_per_sweep": head["ms_per_sweep"],
+                                                                 "launches_per_sweep": sw.launches_per_step(G), "verified": head["verified"]}
+            sw.drop_groups()
+            # end to end from host buffers: activations in from pinned host memory, the last layer's outputs back out
+            y_host = torch.empty(M * sw.width, dtype=torch.bfloat16).pin_memory()
+
+            def step_e2e(i):
+                for k in ("h", "o", "d"):
+                    sw.x[k].copy_(sw.x_host[k], non_blocking=True)
+                sw.step_grouped(G)
+                src = sw.gathered[0][-M * sw.width:] if world > 1 else sw.out_all[L - 1]
+                y_host.copy_(src, non_blocking=True)
+
+            ms_e2e = timed(step_e2e, args.steps, args.warmup, world, graph_cap=5)
+            ok = sw.verify() and bool(torch.equal(y_host.cuda(), (sw.gathered[0][-M * sw.width:] if world > 1 else sw.out_all[L - 1])))
+            verified = verified and ok
+            head["e2e"] = {"value": nbytes / (ms_e2e / args.steps) / 1e6, "unit": "GB/s",
+                           "h2d_bytes_per_step": sum(v.numel() * 2 for v in sw.x_host.values()),
+                           "d2h_bytes_per_step": y_host.numel() * 2, "ms_per_step": ms_e2e / args.steps, "verified": ok,
+                           "how": "per step: the three bf16 activations pinned host -> device, the sweep (quantisers + grouped "
+                                  "GEMM" + (" + all-gather" if world > 1 else "") + "), the last layer's outputs device -> pinned "
+                                  "host; all on the launching stream, replayed from a CUDA graph"}
+            head["launches"] = sw.launches_per_step(G)
+        del sw
+        torch.cuda.empty_cache()
     assert device_status() == 0, "a bounded wait inside a kernel ran out"
-    if rank != 0:
-        return
-    peak, peak_src = peaks()
-    head = 16 if 16 in results else ms_list[0]
-    r = results[head]
-    emit(json.dumps({
-        "metric": "nvfp4_gemm_hbm_gbs", "value": r["gbs"], "unit": "GB/s", "n_gpus": world, "steps": args.steps,
-        "warmup": min(args.warmup, 3), "ms_per_step": r["ms_per_sweep"], "higher_is_better": True, "scaling": "strong",
-        "vs_baseline": None, "dtype": "nvfp4 (e2m1 x e2m1, ue4m3 scale per 16, fp32 accumulate)", "data": "synthetic",
-        "config": {"workload": f"cfg3 decode weight sweep, {layers_n} layers x (q,k,v,o,gate_up,down), M={head}",
-                   "l2": "every projection of every layer in its own device memory (11.9 GB at 64 layers)",
-                   "step": ("per layer: quant, q|k|v (one stacked weight), quant, o, quant, gate_up(SiLU*mul), quant, down; "
-                            "8 launches") if args.fuse_qkv else
-                           "per layer: quant, q, k, v, quant, o, quant, gate_up(SiLU*mul), quant, down; 10 launches",
-                   "timing": "CUDA-graph replay" if not args.no_graph else "eager launches",
-                   "sharding": f"N-sharded {world} way(s)"},
-        "roofline": {"bound": "hbm", "achieved": r["gbs"] / world, "peak": peak, "unit": "GB/s", "frac": r["gbs"] / world / peak,
-                     "traffic": None, "peak_source": peak_src, "kernel": "umma_gemm_kernel (weight streaming), whole sweep"},
-        "gpu_launches": args.steps * layers_n * (8 if args.fuse_qkv else 10),
-        "sweep": {str(m): v for m, v in results.items()}}))
+    return {"head_m": head_m, "G": G, "sweep": sweep, "modes": modes, "verified": verified, "head": head}
+
+
+# ------------------------------------------------------------------------------------------- single-GEMM configurations
+
+
+def run_single(cfg, args, rank, world, local_rank, peaks):
+    """One of cfg0 / cfg1 / cfg2 / cfg4: step = quantise the bf16 activation + the GEMM with its epilogue, weights
+    rotating through more than L2-size of distinct copies, replayed from a CUDA graph until the region is long enough."""
+    from q27b200 import configs, shard, weights
+    from q27b200.linear import ActQuant, Fp4Linear
+    from q27b200.q27lib import device_status
+
+    x = configs.make_x(cfg)
+    in_scale = configs.input_scale_of(x)
+    w = configs.make_w(cfg.N, cfg.K, 1000 + cfg.index, cfg.w_std).cuda()
+    codes, sfb, g = weights.quantize_weight_rtn(w)
+    del w
+    if cfg.glu:
+        codes, sfb = weights.interleave_gate_up(codes), weights.interleave_gate_up(sfb)
+    shard.check_even_shards(cfg.N, world)
+    b, e = shard.shard_rows(cfg.N, world, rank, cfg.glu)
+    codes, sfs = codes[b:e].contiguous(), weights.swizzle_scales(sfb[b:e])
+    n_local = (e - b) // 2 if cfg.glu else e - b
+    nbuf = max(2, -(-4 * L2_BYTES // (codes.numel() + sfs.numel())))
+    ws = torch.zeros(48 << 20, dtype=torch.uint8, device="cuda")
+    layers = [Fp4Linear(codes if i == 0 else codes.clone(), sfs if i == 0 else sfs.clone(), g, in_scale, n_local, cfg.K, cfg.glu, ws)
+              for i in range(nbuf)]
+    M = cfg.M
+    xd = x.cuda()
+    outs = [torch.zeros(M, n_local, dtype=torch.bfloat16, device="cuda") for _ in range(2)]
+    act = ActQuant(max(M, 128), cfg.K)
+    gathered = torch.empty(world, M, n_local, dtype=torch.bfloat16, device="cuda") if world > 1 else None
+
+    def step(i):
+        q, sf = act.quantize(xd, in_scale)
+        layers[i % nbuf].gemm(M, q, sf, outs[i & 1])
+        if world > 1:
+            torch.distributed.all_gather_into_tensor(gathered.view(-1), outs[i & 1].view(-1))
+
+    q0, sf0 = act.quantize(xd, in_scale)
+
+    def gemm_only(i):
+        layers[i % nbuf].gemm(M, q0, sf0, outs[i & 1])
+
+    # how many steps make a region of MIN_REGION_MS: from a short graph-replayed run
+    est = timed(step, 40, 5, world, graph_cap=40) / 40
+    per = int(min(200, max(10, MIN_REGION_MS / max(est, 1e-4) / 4)))
+    steps = per * max(1, math.ceil(MIN_REGION_MS / max(est, 1e-4) / per))
+    with ClockSampler(local_rank) as clk:
+        ms = timed(step, steps, args.warmup, world, graph_cap=per, busy_ms=300.0)
+    clocks = clk.summary()
+    last = args.warmup + per - 1  # the last step of the replayed graph
+    got = outs[last & 1].clone()
+    want = torch.zeros_like(got)
+    with serial_launches():
+        q, sf = act.quantize(xd, in_scale)
+        torch.cuda.synchronize()
+        layers[last % nbuf].gemm(M, q, sf, want)
+        torch.cuda.synchronize()
+    ok = bool(torch.equal(got, want)) and bool(got.any())
+    if world > 1:
+        ok = ok and bool(torch.equal(gathered[rank], want))
+        flag = torch.tensor([int(ok)], device="cuda")
+        torch.distributed.all_reduce(flag, op=torch.distributed.ReduceOp.MIN)
+        ok = bool(flag.item())
+    ms_gemm = timed(gemm_only, steps, args.warmup, world, graph_cap=per)
+    assert device_status() == 0, "a bounded wait inside a kernel ran out"
+    per_step_s, gemm_s = ms / steps / 1e3, ms_gemm / steps / 1e3
+    total_bytes, flops = cfg.algorithmic_bytes(), cfg.flops()
+    tensor_bound = M > 128
+    n_rows_local = e - b
+    launch_bytes = n_rows_local * cfg.K // 2 + n_rows_local * cfg.K // 16 + 2 * M * cfg.K + 2 * M * n_local
+    if not tensor_bound:
+        achieved = launch_bytes / gemm_s / 1e9
+        roof = {"bound": "hbm", "achieved": achieved, "peak": peaks["hbm_gbs"], "unit": "GB/s", "frac": achieved / peaks["hbm_gbs"],
+                "traffic": ncu_traffic().get(f"cfg{cfg.index}") if world == 1 else None,
+                "traffic_source": "ncu capture recorded in profiles/ncu_traffic.json (not measured by this run)",
+                "algorithmic_bytes": launch_bytes, "kernel": "umma_gemm_kernel (weight streaming)", "us_per_launch": gemm_s * 1e6,
+                "peak_source": peaks["source"] + ": copy bandwidth"}
+        value, unit, metric = total_bytes / per_step_s / 1e9, "GB/s", "nvfp4_gemm_hbm_gbs"
+    else:
+        # No FP4 figure is measured on this pool: the denominator is 4 x the measured dense bf16 cuBLAS burst
+        # (block-scaled FP4 runs at 4 x the bf16 rate; nominal dense FP4 is 9000 TFLOP/s).
+        tpeak = 4.0 * peaks["bf16_tflops"]
+        launch_flops = 2 * M * n_rows_local * cfg.K
+        achieved = launch_flops / gemm_s / 1e12
+        roof = {"bound": "tensor", "achieved": achieved, "peak": tpeak, "unit": "TFLOP/s", "frac": achieved / tpeak,
+                "traffic": None, "algorithmic_flops": launch_flops, "kernel": "umma_gemm2_kernel (many rows, CTA pairs)",
+                "us_per_launch": gemm_s * 1e6, "peak_sustained": 4.0 * peaks["bf16_tflops_sustained"],
+                "frac_of_sustained": achieved / (4.0 * peaks["bf16_tflops_sustained"]),
+                "peak_source": "4 x bf16_tflops (burst) of " + peaks["source"] + "; no FP4 peak is measured on this pool, nominal dense FP4 is 9000"}
+        value, unit, metric = flops / per_step_s / 1e12, "TFLOP/s", "nvfp4_gemm_tflops"
+    res = {"workload": cfg.name, "metric": metric, "value": value, "unit": unit, "ms_per_step": ms / steps, "steps": steps,
+           "timed_region_ms": ms, "step": "quant_fp4_bf16 + " + ("skinny_fp4" if M <= 128 else "gemm_fp4") + ("_glu_bf16" if cfg.glu else "_bf16")
+           + (" + all-gather (NCCL, in the graph)" if world > 1 else ""),
+           "l2": f"weights rotate through {nbuf} distinct copies ({nbuf * layers[0].weight_bytes() / 2**20:.0f} MiB per GPU > 126 MiB L2)",
+           "roofline": roof, "clocks": clocks, "verified": ok}
+    log(f"{cfg.name}: {value:.1f} {unit}, GEMM {gemm_s * 1e6:.2f} us, frac {roof['frac']:.3f}, verified {ok}")
+    del layers, codes, sfs
+    torch.cuda.empty_cache()
+    return res
+
+
+# ------------------------------------------------------------------------------------------- the CPU arm
+
+
+def cpu_sweep_sample(M, steps, warmup, frac_rows=8):
+    """The reference's CPU path (fake-quantise the activation, fp32 matmul against the once-dequantised weight,
+    SiLU*mul; reference/qwen27b/quant.py:79-97 restated by the oracle) on a bounded sample of the sweep: ONE layer, the
+    first 1/frac_rows of the output channels of each of its four projections, M tokens; all host threads. Returns
+    (GB/s of the sample's algorithmic bytes, seconds per step, cores, description)."""
+    from oracle import nvfp4_oracle as O
+    from q27b200 import configs
+
+    cores = os.cpu_count() or 1
+    torch.set_num_threads(cores)
+    gx = torch.Generator().manual_seed(3)
+    xs = {"h": torch.randn(M, configs.HIDDEN, generator=gx).to(torch.bfloat16).float().numpy(),
+          "o": torch.randn(M, configs.HIDDEN, generator=gx).to(torch.bfloat16).float().numpy(),
+          "d": torch.randn(M, configs.INTER, generator=gx).to(torch.bfloat16).float().numpy()}
+    scales = {k: float(np.abs(v).max() / np.float32(6.0 * 448.0)) for k, v in xs.items()}
+    parts, nbytes = [], 0
+    for pi, (name, N, K, glu) in enumerate(configs.LAYER_PROJECTIONS):
+        w = configs.make_w(N, K, 1000 + pi, 0.02).numpy()
+        g = O.weight_global_scale(w)
+        n_out = (N // 2 if glu else N) // frac_rows // 64 * 64
+        rows = np.concatenate([np.arange(n_out), N // 2 + np.arange(n_out)]) if glu else np.arange(n_out)
+        codes, sfb, _ = O.quant_weight_rtn(w[rows], g)
+        del w
+        wdq = torch.from_numpy(O.dequant_nvfp4(codes, sfb, g))  # dequantised once, outside the timed loop
+        src = "d" if name == "down" else "o" if name == "o" else "h"
+        parts.append((src, wdq, glu, n_out))
+        nbytes += len(rows) * K // 2 + len(rows) * K // 16 + 2 * M * K + 2 * M * n_out
+
+    def step():
+        xq = {k: torch.from_numpy(O.quant_act_nvfp4(v, scales[k])) for k, v in xs.items()}
+        outs = []
+        for src, wdq, glu, n_out in parts:
+            y = xq[src] @ wdq.T  # fp32, all host threads
+            if glu:
+                y = torch.nn.functional.silu(y[:, :n_out]) * y[:, n_out:]
+            outs.append(y.to(torch.bfloat16))
+        return outs
+
+    for _ in range(warmup):
+        step()
+    t0 = time.perf_counter()
+    for _ in range(steps):
+        step()
+    dt = (time.perf_counter() - t0) / steps
+    desc = (f"one layer of the sweep at M={M}: the first 1/{frac_rows} of the output channels of q, k, v, o, gate|up and down "
+            f"({nbytes / 1e6:.1f} MB of the layer's {configs.sweep_algorithmic_bytes(M, 1) / 1e6:.1f} MB), {steps} steps; the whole "
+            "sweep is 64 such layers, so GB/s carries over; weights dequantised once outside the timed loop")
+    return nbytes / dt / 1e9, dt, cores, desc
+
+
+def workload_name(layers, M):
+    return f"cfg3 decode weight sweep, {layers} layers x (q|k|v, o, gate_up, down), M={M}"
 
 
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=200)
-    ap.add_argument("--warmup", type=int, default=20)
+    ap.add_argument("--steps", type=int, default=25)
+    ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--config", type=int, default=1, choices=[0, 1, 2, 3, 4])
-    ap.add_argument("--m", type=int, default=0, help="configuration 3: the M to sweep at (0: all of 1..128)")
-    ap.add_argument("--layers", type=int, default=64, help="configuration 3: layers in the sweep")
-    ap.add_argument("--separate-qkv", dest="fuse_qkv", action="store_false",
-                    help="configuration 3: q, k and v as three launches instead of one stacked weight with three "
-                         "alpha segments (the engine stacks projections that share an input, engine/src/weights.cc:254-267)")
+    ap.add_argument("--only", default="", help="comma-separated subset of sweep,cfg0,cfg1,cfg2,cfg4 (default: all that apply)")
+    ap.add_argument("--m", type=int, default=0, help="the sweep at this token count only (0: all of 1..128)")
+    ap.add_argument("--layers", type=int, default=64, help="layers in the sweep")
+    ap.add_argument("--group-layers", type=int, default=64, help="layers per grouped launch in the headline mode")
     ap.add_argument("--cpu-steps", type=int, default=20)
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg (profiling runs)")
-    ap.add_argument("--no-graph", action="store_true", help="time eager launches instead of a CUDA-graph replay")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)
 
@@ -342,197 +620,82 @@ def main():
     _json_out = os.fdopen(os.dup(1), "w")
     os.dup2(2, 1)
     local_rank = int(os.environ.get("LOCAL_RANK", 0))
-    if args.config == 3:
-        assert args.impl == "ours", "the CPU arm times single GEMM configurations"
-        torch.cuda.set_device(local_rank)
-        if world > 1:
-            torch.distributed.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
-        sweep_main(args, rank, world, local_rank)
-        if world > 1:
-            torch.distributed.destroy_process_group()
-        return
-    cfg = configs.CONFIGS[args.config]
-    metric = "nvfp4_gemm_tflops" if cfg.M > 128 else "nvfp4_gemm_hbm_gbs"
-    unit = "TFLOP/s" if cfg.M > 128 else "GB/s"
+    head_m = args.m or 16
 
     if args.impl == "reference":
         if rank != 0:
             return
-        gbs, dt, cores, desc = cpu_reference(cfg, max(1, min(args.steps, 50)), min(args.warmup, 3))
-        val = gbs if unit == "GB/s" else cfg.flops() / cfg.algorithmic_bytes() * gbs / 1e3
+        gbs, dt, cores, desc = cpu_sweep_sample(head_m, max(1, args.steps), args.warmup)
         emit(json.dumps({
-            "impl": "reference", "metric": metric, "value": val, "unit": unit, "n_gpus": args.gpus,
-            "steps": max(1, min(args.steps, 50)), "warmup": min(args.warmup, 3), "ms_per_step": dt * 1e3,
-            "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "f32 (host matmul of fake-quantised operands)",
-            "data": "synthetic", "config": {"workload": cfg.name, "sample": desc},
-            "cpu_baseline": {"value": val, "unit": unit, "cores": cores, "kind": "port", "sample": desc},
-            "e2e": {"value": val, "unit": unit, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}))
+            "impl": "reference", "metric": "nvfp4_gemm_hbm_gbs", "value": gbs, "unit": "GB/s", "n_gpus": args.gpus,
+            "steps": max(1, args.steps), "warmup": args.warmup, "ms_per_step": dt * 1e3, "higher_is_better": True,
+            "scaling": "strong", "vs_baseline": None, "dtype": "f32 (host matmul of fake-quantised operands)", "data": "synthetic",
+            "config": {"workload": workload_name(args.layers, head_m)},
+            "cpu_baseline": {"value": gbs, "unit": "GB/s", "cores": cores, "kind": "port", "sample": desc},
+            "e2e": {"value": gbs, "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}))
         return
 
     assert torch.cuda.is_available(), "bench.py needs a GPU (there is no CPU fallback)"
     torch.cuda.set_device(local_rank)
     if world > 1:
         torch.distributed.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
-    from q27b200 import shard
-    from q27b200.linear import ActQuant
-    from q27b200.q27lib import device_status
+    peaks = measured_peaks()
+    only = [s for s in args.only.split(",") if s]
+    want = lambda name: not only or name in only  # noqa: E731
 
-    x, in_scale, layers, n_local = build_layers(cfg, rank, world, 4 * L2_BYTES // 1 if world == 1 else 3 * L2_BYTES)
-    nbuf, M = len(layers), cfg.M
-    xd = x.cuda()
-    outs = [torch.empty(M, n_local, dtype=torch.bfloat16, device="cuda") for _ in range(2)]
-    act = ActQuant(max(M, 128), cfg.K)
-    for l in layers:
-        l._act = act  # one activation scratch for every copy, as one engine would have
-
-    def step(i):  # device-resident step: quantise + GEMM (+ fix-up)
-        layers[i % nbuf](xd, out=outs[i & 1])
-
-    q, sf = act.quantize(xd, in_scale)
-
-    def gemm_only(i):
-        layers[i % nbuf].gemm(M, q, sf, outs[i & 1])
-
-    # host-facing step: pinned host activation in, result back to pinned host memory
-    xh = x.pin_memory()
-    yh = [torch.empty(M, n_local, dtype=torch.bfloat16).pin_memory() for _ in range(2)]
-    xdev = [torch.empty_like(xd) for _ in range(2)]
-    up_stream, down_stream = torch.cuda.Stream(), torch.cuda.Stream()
-    uploaded = [torch.cuda.Event() for _ in range(2)]
-    computed = [torch.cuda.Event() for _ in range(2)]
-    copied = [torch.cuda.Event() for _ in range(2)]
-
-    def step_e2e_sync(i):  # latency form: the caller waits for every result before the next step
-        xdev[0].copy_(xh, non_blocking=True)
-        layers[i % nbuf](xdev[0], out=outs[0])
-        yh[0].copy_(outs[0], non_blocking=True)
-        torch.cuda.current_stream().synchronize()
-
-    fresh = [0]  # steps whose buffers nothing has used yet (the first two of a graph capture)
-
-    def step_e2e(i):
-        # throughput form: every step copies its input in, computes, and copies its result out; the two copies run
-        # on streams of their own so that they overlap the neighbouring steps' kernels (two buffers of everything);
-        # nothing waits on the host
-        b = i & 1
-        main = torch.cuda.current_stream()
-        first = fresh[0] > 0
-        if first:
-            if fresh[0] == 2:  # the copy streams branch off the stream the steps are issued (or captured) on
-                fork = torch.cuda.Event()
-                fork.record(main)
-                up_stream.wait_event(fork)
-                down_stream.wait_event(fork)
-            fresh[0] -= 1
-        else:
-            up_stream.wait_event(computed[b])  # step i - 2 has consumed this input buffer
-        with torch.cuda.stream(up_stream):
-            xdev[b].copy_(xh, non_blocking=True)
-            uploaded[b].record(up_stream)
-        main.wait_event(uploaded[b])
-        if not first:
-            main.wait_event(copied[b])  # the result buffer of step i - 2 has been read out
-        layers[i % nbuf](xdev[b], out=outs[b])
-        computed[b].record(main)
-        down_stream.wait_event(computed[b])
-        with torch.cuda.stream(down_stream):
-            yh[b].copy_(outs[b], non_blocking=True)
-            copied[b].record(down_stream)
-
-    gathered = torch.empty(world, M, n_local, dtype=torch.bfloat16, device="cuda") if world > 1 else None
-
-    def step_gather(i):
-        step(i)
-        torch.distributed.all_gather_into_tensor(gathered, outs[i & 1])
-
-    graph = not args.no_graph
-    with ClockSampler(local_rank) as clk:
-        ms = timed(step, args.steps, args.warmup, world, graph)
-        if graph:  # keep the GPU busy long enough for the clock sampler to see it under load
-            for _ in range(20):
-                timed(step, args.steps, 0, world, False)
-    ms_gemm = timed(gemm_only, args.steps, args.warmup, world, graph)
-    ms_eager = timed(step, args.steps, args.warmup, world, False)
-
-    def e2e_join():  # the timed region ends when the last results have reached the host buffers
-        for ev in copied:
-            torch.cuda.current_stream().wait_event(ev)
-
-    fresh[0] = 2
-    ms_e2e_eager = timed(step_e2e, args.steps, args.warmup, world, after=e2e_join)
-    ms_e2e = ms_e2e_eager
-    if graph:  # the same steps, copies included, replayed from one CUDA graph: the host's launch cost drops out
-        fresh[0] = 2
-        ms_e2e = timed(step_e2e, args.steps, args.warmup, world, graph=True, after=e2e_join, before=lambda: fresh.__setitem__(0, 2))
-    ms_e2e_sync = timed(step_e2e_sync, args.steps, args.warmup, world)
-    ms_gather = timed(step_gather, args.steps, args.warmup, world) if world > 1 else None
-    assert device_status() == 0, "a bounded wait inside a kernel ran out"
-    clocks = clk.summary()
-
-    if rank != 0:
-        torch.distributed.destroy_process_group()
-        return
-
-    total_bytes = cfg.algorithmic_bytes()  # whole job: all ranks' weight shards + activation in + output
-    flops = cfg.flops()
-    per_step_s, gemm_s, e2e_s = ms / args.steps / 1e3, ms_gemm / args.steps / 1e3, ms_e2e / args.steps / 1e3
-
-    def val(seconds):
-        return total_bytes / seconds / 1e9 if unit == "GB/s" else flops / seconds / 1e12
-
-    peak, peak_src = peaks()
-    # per-GPU roofline of the dominant kernel: the rank's share of the weight bytes + the whole activation + its
-    # output block, over the average duration of one GEMM launch (launch gap included)
-    n_rows_local = layers[0].rows()
-    launch_bytes = n_rows_local * cfg.K // 2 + n_rows_local * cfg.K // 16 + 2 * M * cfg.K + 2 * M * n_local
-    if M <= 128:
-        achieved = launch_bytes / gemm_s / 1e9
-        roof = {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
-                "traffic": NCU_TRAFFIC_BYTES.get(cfg.index) if world == 1 else None, "algorithmic_bytes": launch_bytes,
-                "kernel": "umma_gemm_kernel (weight streaming)", "us_per_launch": gemm_s * 1e6, "peak_source": peak_src}
-    else:
-        # No FP4 figure is measured on this pool: the denominator is 4 x the measured dense bf16 cuBLAS burst
-        # (block-scaled FP4 runs at 4 x the bf16 rate; nominal dense FP4 is 9000 TFLOP/s).
-        pk = json.load(open(os.path.join(ROOT, "MEASURED_PEAKS.json"))) if os.path.exists(os.path.join(ROOT, "MEASURED_PEAKS.json")) else {}
-        tpeak = 4.0 * float(pk.get("bf16_tflops", 1590.0))
-        tpeak_sustained = 4.0 * float(pk.get("bf16_tflops_sustained", 1400.0))
-        launch_flops = 2 * M * n_rows_local * cfg.K
-        achieved = launch_flops / gemm_s / 1e12
-        roof = {"bound": "tensor", "achieved": achieved, "peak": tpeak, "unit": "TFLOP/s", "frac": achieved / tpeak,
-                "traffic": None, "algorithmic_flops": launch_flops, "kernel": "umma_gemm_kernel (many rows)",
-                "us_per_launch": gemm_s * 1e6,
-                # the timed region is a long run of back-to-back GEMMs under the power cap: the sustained cuBLAS
-                # figure (seconds-long loop, clocks settled) is the like-for-like denominator; the burst one is kept
-                # as `peak`
-                "peak_sustained": tpeak_sustained, "frac_of_sustained": achieved / tpeak_sustained,
-                "peak_source": "4 x bf16_tflops of MEASURED_PEAKS.json (no measured FP4 peak; nominal dense FP4 9000)"
-                if pk else "4 x fallback bf16 1590 (no measured FP4 peak; nominal dense FP4 9000)"}
-    line = {
-        "metric": metric, "value": val(per_step_s), "unit": unit, "n_gpus": world, "steps": args.steps,
-        "warmup": args.warmup, "ms_per_step": ms / args.steps, "higher_is_better": True, "scaling": "strong",
-        "vs_baseline": None, "dtype": "nvfp4 (e2m1 x e2m1, ue4m3 scale per 16, fp32 accumulate)", "data": "synthetic",
-        "config": {"workload": cfg.name, "M": M, "N": cfg.N, "K": cfg.K, "epilogue": "silu*mul->bf16" if cfg.glu else "bf16",
-                   "sharding": f"N-sharded {world} way(s), no reduction", "l2": f"weights rotate through {nbuf} distinct copies "
-                   f"({nbuf * layers[0].weight_bytes() / 2**20:.0f} MiB per GPU > 126 MiB L2)",
-                   "step": "quant_fp4_bf16 + skinny_fp4_glu_bf16" if M <= 128 else "quant_fp4_bf16 + gemm_fp4_glu_bf16",
-                   "timing": "CUDA-graph replay of the timed steps" if graph else "eager launches", "eager_ms_per_step": ms_eager / args.steps},
-        "e2e": {"value": val(e2e_s), "unit": unit, "h2d_bytes_per_step": x.numel() * 2, "d2h_bytes_per_step": M * n_local * 2,
-                "ms_per_step": ms_e2e / args.steps, "ms_per_step_host_waits_each_result": ms_e2e_sync / args.steps,
-                "ms_per_step_eager_launches": ms_e2e_eager / args.steps,
-                "how": "per step: pinned host activation -> device, quantise + GEMM through Fp4Linear, result -> pinned "
-                       "host; the two copies on streams of their own, overlapping the neighbouring steps; " +
-                       ("the steps with their copies replayed from one CUDA graph" if graph else "eager launches")},
-        "gpu_launches": args.steps * 2,  # quantiser + GEMM
-        "roofline": roof,
-        "clocks": clocks,
-    }
-    if ms_gather is not None:
-        line["with_allgather"] = {"value": val(ms_gather / args.steps / 1e3), "unit": unit, "ms_per_step": ms_gather / args.steps}
-    if world == 1 and not args.no_cpu:
-        gbs, dt, cores, desc = cpu_reference(cfg, args.cpu_steps, 2)
-        line["cpu_baseline"] = {"value": gbs if unit == "GB/s" else flops / total_bytes * gbs / 1e3, "unit": unit, "cores": cores,
-                                "kind": "port", "sample": desc, "ms_per_step_sample": dt * 1e3}
-    emit(json.dumps(line))
+    t_start = time.perf_counter()
+    line = {"metric": "nvfp4_gemm_hbm_gbs", "unit": "GB/s", "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
+            "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": DTYPE, "data": "synthetic"}
+    verified = True
+    if want("sweep"):
+        model = build_model(args.layers, rank, world)
+        log(f"model built in {time.perf_counter() - t_start:.1f} s")
+        r = run_sweep(args, model, rank, world, local_rank, peaks)
+        del model
+        torch.cuda.empty_cache()
+        h, G = r["head"], r["G"]
+        verified = verified and r["verified"]
+        line.update({
+            "value": h["gbs"], "ms_per_step": h["ms_per_sweep"],
+            "config": {"workload": workload_name(args.layers, r["head_m"]),
+                       "l2": f"every projection of every layer in its own device memory ({configs.layer_weight_bytes() * args.layers / 1e9:.1f} GB), far beyond the 126 MB L2",
+                       "step": f"per group of {G} layer(s): one launch quantising the layers' bf16 activations (q27b_quant_fp4_batch), "
+                               f"one grouped weight-streaming GEMM over their projections (q27b_skinny_fp4_group)"
+                               + ("; then one NCCL all-gather of all outputs, inside the timed graph" if world > 1 else ""),
+                       "timing": "CUDA-graph replay, CUDA events on the launching stream",
+                       "sharding": f"weight rows N-sharded {world} way(s), no reduction"},
+            "roofline": {"bound": "hbm", "achieved": h["gbs"] / world, "peak": peaks["hbm_gbs"], "unit": "GB/s",
+                         "frac": h["gbs"] / world / peaks["hbm_gbs"], "traffic": ncu_traffic().get("cfg3_group") if world == 1 else None,
+                         "traffic_source": "ncu capture recorded in profiles/ncu_traffic.json (not measured by this run)",
+                         "algorithmic_bytes": h["bytes"] // world, "kernel": "skinny_group_kernel (grouped weight streaming), whole sweep, per GPU",
+                         "us_per_launch": h["ms_per_sweep"] * 1e3 / math.ceil(args.layers / G),
+                         "peak_source": peaks["source"] + ": copy bandwidth"},
+            "clocks": h["clocks"], "e2e": h["e2e"], "gpu_launches": args.steps * h["launches"],
+            "sweep": r["sweep"], "modes": r["modes"]})
+    subs = {}
+    for idx in (0, 1, 2, 4):
+        if not want(f"cfg{idx}"):
+            continue
+        if world > 1 and idx != 4:
+            continue  # only the sweep and the prefill GEMM are sharded
+        subs[f"cfg{idx}"] = run_single(configs.CONFIGS[idx], args, rank, world, local_rank, peaks)
+        verified = verified and subs[f"cfg{idx}"]["verified"]
+    line["configs"] = subs
+    line["verified"] = verified
+    if "value" not in line and subs:  # a run restricted to single configurations: the first one is the headline
+        first = next(iter(subs.values()))
+        line.update({"metric": first["metric"], "unit": first["unit"], "value": first["value"], "ms_per_step": first["ms_per_step"],
+                     "steps": first["steps"], "config": {"workload": first["workload"], "step": first["step"], "l2": first["l2"]},
+                     "roofline": first["roofline"], "clocks": first["clocks"], "gpu_launches": first["steps"] * 2})
+    if rank == 0 and world == 1 and not args.no_cpu:
+        gbs, dt, cores, desc = cpu_sweep_sample(head_m, args.cpu_steps, 2)
+        line["cpu_baseline"] = {"value": gbs, "unit": "GB/s", "cores": cores, "kind": "port", "sample": desc, "ms_per_step_sample": dt * 1e3}
+    line["bench_wall_s"] = time.perf_counter() - t_start
+    if world > 1:
+        torch.distributed.barrier()
+    assert verified, "a timed region left outputs that differ from the one-kernel-at-a-time run"
+    if rank == 0:
+        emit(json.dumps(line))
     if world > 1:
         torch.distributed.destroy_process_group()
 

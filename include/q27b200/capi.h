@@ -66,6 +66,26 @@ int q27b_quant_fp4(const float* x, int M, int K, float input_scale, uint8_t* q, 
 /* The same for bf16 input (bf16 -> fp32 is exact, so the result equals quantising the widened values). New entry
  * point (the benchmark's activations are bf16); the reference quantises bf16 only inside silu_mul_quant_fp4. */
 int q27b_quant_fp4_bf16(const void* x, int M, int K, float input_scale, uint8_t* q, uint8_t* sf, void* stream);
+/* Several activations quantised by ONE launch (a decode layer quantises three small activations, and a launch
+ * costs more than the work). jobs_host: HOST array of n jobs, read for validation and for the grid size; jobs_dev:
+ * the same array in device memory, read by the kernel, or NULL for n <= 4 (the jobs then travel in the launch
+ * parameters). No counterpart in the reference, which fuses its quantisers into the producing kernels instead. */
+typedef struct q27b_quant_job {
+  const void* x;     /* fp32 or bf16 [M][K], 16-byte aligned */
+  uint8_t* q;        /* codes [M][K/2], 8-byte aligned */
+  uint8_t* sf;       /* swizzled scales, 4-byte aligned */
+  int M, K;          /* K a multiple of 64 */
+  float input_scale;
+  int bf16;          /* non-zero: x is bf16 */
+} q27b_quant_job;
+int q27b_quant_fp4_batch(const q27b_quant_job* jobs_host, const q27b_quant_job* jobs_dev, int n, void* stream);
+/* RMSNorm over D (a multiple of 512, at most 16384) with zero-centred weights, x / rms(x) * (1 + w), per token, fused
+ * with the quantiser: writes the fp32 result to out (may be null) and, when q is not null, its NVFP4 quantisation
+ * (exactly quant_fp4 of the fp32 result). cap (optional): a bf16 copy of the input rows, cap_ld elements apart;
+ * rstd (optional): 1 / rms per token. Replaces rmsnorm_quant for QuantOut::kFp4 / kNone (engine/src/kernels.h:131-136,
+ * engine/src/kernels.cu:211-262,718-726); the FP8 kinds are not part of this path. */
+int q27b_rmsnorm_quant_fp4(const float* x, const void* w_bf16, int T, int D, float eps, float* out, float input_scale,
+                           uint8_t* q, uint8_t* sf, void* cap_bf16, int cap_ld, float* rstd, void* stream);
 /* Dynamic per-token quantisation: as quant_fp4 with each row's own tensor scale ascale[m] = amax(row) / (6 * 448)
  * (1 for an all-zero row), which the call writes. The rule of the reference's draft model (engine/src/draft.cu:70-111,
  * where it is fused into the producing kernels); feeds q27b_skinny_fp4_scaled. */
@@ -221,6 +241,9 @@ float q27t_last_us(void); /* per-launch time of the last Q27T_REPEAT graph repla
 int64_t q27t_sf_bytes(int64_t rows, int64_t kblocks);                                  /* capi.cc:565 */
 int q27t_quant_fp4(const float* x, int M, int K, float input_scale, uint8_t* q, uint8_t* sf); /* capi.cc:498-500 */
 int q27t_quant_fp4_bf16(const void* x, int M, int K, float input_scale, uint8_t* q, uint8_t* sf);
+/* hidden size 5120; kind 0: fp32 output only, 2: + NVFP4 (the reference's QuantOut kinds; capi.cc:519-522) */
+int q27t_rmsnorm_quant(const float* x, const void* w_bf16, int T, float eps, float* out, int kind, float in_scale,
+                       uint8_t* q, uint8_t* sf);
 int q27t_quant_fp4_weight(const void* w, int M, int K, float global, uint8_t* q, uint8_t* sf); /* (new wrapper) */
 int q27t_quant_fp4_dynamic(const float* x, int M, int K, uint8_t* q, uint8_t* sf, float* ascale); /* (new wrapper) */
 int q27t_skinny_fp4_scaled(int M, int N, int K, const uint8_t* a, const uint8_t* a_sf, const float* ascale,

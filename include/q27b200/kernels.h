@@ -32,6 +32,18 @@ void quant_fp4(const bf16* x, int M, int K, float input_scale, uint8_t* q, uint8
 // Dynamic per-token quantisation (the draft model's rule, engine/src/draft.cu:70-111): writes ascale[m].
 void quant_fp4_dynamic(const float* x, int M, int K, uint8_t* q, uint8_t* sf, float* ascale, cudaStream_t s);
 void quant_fp4_dynamic(const bf16* x, int M, int K, uint8_t* q, uint8_t* sf, float* ascale, cudaStream_t s);
+// engine/src/kernels.h:104-114,131-136: the quantised copy an op writes for the next GEMM, and RMSNorm(1 + w) over the
+// hidden size (5120) fused with it. Of the reference's kinds this path has kNone and kFp4; the FP8 kinds throw.
+struct QuantOut {
+  enum Kind : int { kNone = 0, kFp8 = 1, kFp4 = 2, kFp8Row = 3 };
+  Kind kind = kNone;
+  float in_scale = 1.f;
+  uint8_t* q = nullptr;    // packed e2m1 [T][D/2]
+  uint8_t* sf = nullptr;   // swizzled scale factors
+  float* scale = nullptr;  // (kFp8Row only)
+};
+void rmsnorm_quant(const float* x, const bf16* w, int T, float eps, float* out, QuantOut q, cudaStream_t s,
+                   bf16* cap = nullptr, int cap_ld = 0, float* rstd = nullptr);
 // engine/src/kernels.h:130: the load-time weight quantiser (block scales searched for the smallest squared error)
 void quant_fp4_weight(const bf16* w, int M, int K, float global, uint8_t* q, uint8_t* sf, cudaStream_t s);
 void silu_mul_quant_fp4(const float* gate, const float* up, int64_t ld, int T, int I, float input_scale, uint8_t* q,

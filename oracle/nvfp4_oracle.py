@@ -24,6 +24,13 @@ What each function follows (paths inside the reference project):
   sf_offset/sf_bytes engine/src/kernels.h:192-199       (python twin engine/tests/test_elementwise.py:14-23)
   glu_row            engine/src/kernels.h:186           (python twin engine/tests/test_gemm.py:53-56)
   silu_mul           reference/qwen27b/model.py:182-185 (F.silu(gate) * up)
+  rms_norm           reference/qwen27b/model.py:60-63   (zero-centred RMSNorm in fp32; golden vectors from the
+                     reference's own function: tests/golden/make_golden_rmsnorm.py)
+  rms_norm_fixed_order  the same quantity with the summation order and the separate IEEE operations of this
+                     repository's fused kernel (one lane per 16 elements, a butterfly over 32 lanes, the warps in
+                     order, IEEE sqrt and divisions), so that the kernel can be compared bit for bit; the reference's
+                     kernel (engine/src/kernels.cu:211-262) uses an approximate rsqrt and its tests allow 1e-5
+                     (engine/tests/test_elementwise.py:94-115), which is how rms_norm pins this function
 """
 
 from __future__ import annotations
@@ -321,6 +328,36 @@ def qlinear(x, w_codes, w_sf, scale_2, input_scale, dtype=np.float64) -> np.ndar
 def silu_mul(gate: np.ndarray, up: np.ndarray) -> np.ndarray:
     gate = np.asarray(gate, dtype=np.float64)
     return gate / (1.0 + np.exp(-gate)) * np.asarray(up, dtype=np.float64)
+
+
+def rms_norm(x: np.ndarray, w: np.ndarray, eps: float) -> np.ndarray:
+    """x / rms(x) * (1 + w) over the last axis, evaluated in fp64 (the reference evaluates it in fp32)."""
+    x64 = np.asarray(x, dtype=np.float64)
+    r = 1.0 / np.sqrt((x64 * x64).mean(-1, keepdims=True) + eps)
+    return x64 * r * (1.0 + np.asarray(w, dtype=np.float64))
+
+
+def rms_norm_fixed_order(x: np.ndarray, w: np.ndarray, eps: float):
+    """fp32 [T][D] (D a multiple of 512), w fp32 [D] -> (fp32 [T][D], 1 / rms [T]) with every operation a separate
+    fp32 operation in the order of the fused kernel."""
+    x = np.asarray(x, dtype=np.float32)
+    w = np.asarray(w, dtype=np.float32)
+    T, D = x.shape
+    assert D % 512 == 0
+    lanes = x.reshape(T, D // 16, 16)
+    ss = np.zeros((T, D // 16), dtype=np.float32)
+    for j in range(16):  # each lane: its 16 squares in order
+        ss = (ss + (lanes[:, :, j] * lanes[:, :, j]).astype(np.float32)).astype(np.float32)
+    ss = ss.reshape(T, D // 512, 32)
+    lane = np.arange(32)
+    for o in (16, 8, 4, 2, 1):  # butterfly over the 32 lanes of a warp
+        ss = (ss + ss[:, :, lane ^ o]).astype(np.float32)
+    total = np.zeros(T, dtype=np.float32)
+    for i in range(D // 512):  # the warps' sums in order
+        total = (total + ss[:, i, 0]).astype(np.float32)
+    r = (f32(1.0) / np.sqrt(((total / f32(D)).astype(np.float32) + f32(eps)).astype(np.float32)).astype(np.float32)).astype(np.float32)
+    y = ((x * r[:, None]).astype(np.float32) * (f32(1.0) + w).astype(np.float32)[None, :]).astype(np.float32)
+    return y, r
 
 
 def bf16_round(x: np.ndarray) -> np.ndarray:

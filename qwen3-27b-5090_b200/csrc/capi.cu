@@ -109,6 +109,14 @@ int q27t_quant_fp4_weight(const void* w, int M, int K, float global, uint8_t* q,
 int q27t_quant_fp4_bf16(const void* x, int M, int K, float input_scale, uint8_t* q, uint8_t* sf) {
   return kernel([&] { return q27b_quant_fp4_bf16(x, M, K, input_scale, q, sf, test_stream()); });
 }
+int q27t_rmsnorm_quant(const float* x, const void* w, int T, float eps, float* out, int kind, float in_scale, uint8_t* q,
+                       uint8_t* sf) {
+  Q27B_REQUIRE(kind == 0 || kind == 2, "rmsnorm_quant: only the plain (0) and NVFP4 (2) outputs are part of this path");
+  return kernel([&] {
+    return q27b_rmsnorm_quant_fp4(x, w, T, 5120, eps, out, in_scale, kind == 2 ? q : nullptr, sf, nullptr, 0, nullptr,
+                                  test_stream());
+  });
+}
 int q27t_silu_mul_quant_fp4(const float* g, const float* u, int64_t ld, int T, int I, float in_scale, uint8_t* q,
                             uint8_t* sf) {
   return kernel([&] { return q27b_silu_mul_quant_fp4(g, u, ld, T, I, in_scale, q, sf, test_stream()); });

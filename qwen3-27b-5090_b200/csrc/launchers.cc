@@ -22,6 +22,13 @@ void quant_fp4(const float* x, int M, int K, float input_scale, uint8_t* q, uint
 void quant_fp4(const bf16* x, int M, int K, float input_scale, uint8_t* q, uint8_t* sf, cudaStream_t s) {
   check(q27b_quant_fp4_bf16(x, M, K, input_scale, q, sf, s));
 }
+void rmsnorm_quant(const float* x, const bf16* w, int T, float eps, float* out, QuantOut q, cudaStream_t s, bf16* cap,
+                   int cap_ld, float* rstd) {
+  if (q.kind != QuantOut::kNone && q.kind != QuantOut::kFp4)
+    throw std::runtime_error("check failed: rmsnorm_quant: only QuantOut::kNone and kFp4 are part of the NVFP4 path");
+  check(q27b_rmsnorm_quant_fp4(x, w, T, 5120, eps, out, q.in_scale, q.kind == QuantOut::kFp4 ? q.q : nullptr, q.sf, cap,
+                               cap_ld, rstd, s));
+}
 void quant_fp4_dynamic(const float* x, int M, int K, uint8_t* q, uint8_t* sf, float* ascale, cudaStream_t s) {
   check(q27b_quant_fp4_dynamic(x, M, K, q, sf, ascale, s));
 }

@@ -23,6 +23,8 @@ SIGNATURES = {
     "q27b_swizzle_sf": ([P, I, I, P, I, P], I),
     "q27b_quant_fp4": ([P, I, I, F, P, P, P], I),
     "q27b_quant_fp4_bf16": ([P, I, I, F, P, P, P], I),
+    "q27b_quant_fp4_batch": ([P, P, I, P], I),
+    "q27b_rmsnorm_quant_fp4": ([P, P, I, I, F, P, F, P, P, P, I, P, P], I),
     "q27b_trace_set": ([P], I),
     "q27b_probe_wait_timeout": ([I, P], I),
     "q27b_quant_fp4_weight": ([P, I, I, F, P, P, P], I),
@@ -50,6 +52,7 @@ SIGNATURES = {
     "q27t_sf_bytes": ([I64, I64], I64),
     "q27t_quant_fp4": ([P, I, I, F, P, P], I),
     "q27t_quant_fp4_bf16": ([P, I, I, F, P, P], I),
+    "q27t_rmsnorm_quant": ([P, P, I, F, P, I, F, P, P], I),
     "q27t_quant_fp4_weight": ([P, I, I, F, P, P], I),
     "q27t_quant_fp4_dynamic": ([P, I, I, P, P, P], I),
     "q27t_skinny_fp4_scaled": ([I, I, I, P, P, P, P, P, P, P, P, SZ], I),

@@ -21,6 +21,16 @@ def shard_rows(n_rows: int, world: int, rank: int, glu: bool = False) -> tuple[i
     return begin * 128, (begin + base + (1 if rank < extra else 0)) * 128
 
 
+def check_even_shards(n_rows: int, world: int) -> None:
+    """The gather of the outputs is one collective with equal contributions: every rank must hold the same number of
+    128-row tiles. Raises before anything is launched when they do not divide (a collective with mismatched sizes can
+    hang the ranks)."""
+    assert n_rows % 128 == 0, "weight rows must be a multiple of 128"
+    if (n_rows // 128) % world != 0:
+        raise ValueError(f"{n_rows} weight rows are {n_rows // 128} tiles of 128, which {world} ranks cannot share equally; "
+                         "use a rank count that divides the tile count (or pad the weight)")
+
+
 def output_columns(n_rows: int, world: int, rank: int, glu: bool = False) -> tuple[int, int]:
     b, e = shard_rows(n_rows, world, rank, glu)
     return (b // 2, e // 2) if glu else (b, e)
@@ -40,6 +50,11 @@ def all_gather_output(local: torch.Tensor, group=None) -> torch.Tensor:
     if world == 1:
         return local
     M, n_local = local.shape
+    # equal widths on every rank, checked on the host before the collective (mismatched sizes can hang it)
+    widths = [None] * world
+    dist.all_gather_object(widths, (M, n_local), group=group)
+    if any(w != (M, n_local) for w in widths):
+        raise ValueError(f"all_gather_output needs equal local shapes on every rank, got {widths}")
     # rank blocks concatenated along dim 0 (the form every backend accepts), viewed as [world][M][n_local]
     buf = torch.empty(world * M, n_local, dtype=local.dtype, device=local.device)
     dist.all_gather_into_tensor(buf, local.contiguous(), group=group)

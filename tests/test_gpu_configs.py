@@ -128,7 +128,7 @@ def test_cfg2_batched_verify_down():
     assert torch.equal(y, lin(x.to(DEV), out_dtype=torch.float32).bfloat16())
 
 
-@pytest.mark.parametrize("M", [1, 16, 128])
+@pytest.mark.parametrize("M", configs.SWEEP_M)
 def test_cfg3_one_layer_and_n_sharding(M, gate_up):
     """One layer of the decode sweep (q, k, v, o, gate_up, down) at M tokens, each projection against the oracle,
     and N-sharded 8 ways on one device: the concatenated shards reproduce the unsharded output."""

@@ -14,8 +14,11 @@ from q27b200.q27lib import call, lib
 pytestmark = pytest.mark.gpu
 
 
-@pytest.mark.parametrize("M", [1, 5, 128, 300, 2048])
-@pytest.mark.parametrize("N,K", [(5120, 17408), (17408, 5120), (384, 5120), (128, 128)])
+CASES = [(M, N, K) for N, K in [(5120, 17408), (17408, 5120), (384, 5120), (128, 128)] for M in [1, 5, 128, 300, 2048]]
+CASES += [(M, N, K) for N, K in [(1024, 5120), (128, 5120), (34816, 5120)] for M in [300, 4096]]
+
+
+@pytest.mark.parametrize("M,N,K", CASES)
 def test_gemm_fp4(M, N, K):
     rng = np.random.RandomState(M + N + K)
     a, asf, adq = fp4_operand(M, K, rng)

@@ -1,0 +1,161 @@
+"""The grouped weight-streaming GEMM (q27b_skinny_fp4_group): a list of skinny GEMMs run as one persistent launch
+must reproduce, BIT FOR BIT, the results of the per-GEMM entry points called one by one - for a whole layer of the
+model (q|k|v stacked with three alpha segments, o with a residual, gate | up with the SiLU*mul epilogue, down in
+bf16) at every token count of the decode sweep, on a workspace left behind by the previous launch, for several layers
+in one launch, and for small odd shapes."""
+
+import ctypes
+
+import numpy as np
+import pytest
+import torch
+
+from helpers import DEV, dev, fp4_operand, rel_err, swizzled_dev, workspace
+from q27b200.group import EPI_BF16, EPI_F32, EPI_GLU_BF16, Fp4Group, GroupProblem
+from q27b200.q27lib import call
+
+pytestmark = pytest.mark.gpu
+WS = 48 << 20
+
+_ops = {}
+
+
+def operand(rows, K, seed):
+    if (rows, K, seed) not in _ops:
+        c, sf, dq = fp4_operand(rows, K, np.random.RandomState(seed))
+        _ops[(rows, K, seed)] = (dev(c), swizzled_dev(sf), dq)
+    return _ops[(rows, K, seed)]
+
+
+def problem(N, K, epi, a, a_sf, w, w_sf, d, alphas=(1.0,), begins=(0,), alpha_up=1.0, c=None):
+    p = GroupProblem()
+    p.N, p.K, p.epilogue, p.alpha_count = N, K, epi, len(alphas)
+    for i, (b, al) in enumerate(zip(begins, alphas)):
+        p.alpha_begin[i], p.alpha[i] = b, al
+    p.alpha_up, p.beta = alpha_up, 1.0 if c is not None else 0.0
+    p.a, p.a_sf, p.w, p.w_sf = a.data_ptr(), a_sf.data_ptr(), w.data_ptr(), w_sf.data_ptr()
+    p.c = c.data_ptr() if c is not None else None
+    p.d = d.data_ptr()
+    return p
+
+
+QKV_BEGIN, QKV_ALPHA = (0, 5120, 6144), (0.37, 0.11, 0.23)
+
+
+def layer_by_single_calls(M, ws, res):
+    """The four projections of one layer through the per-GEMM entry points; returns their outputs."""
+    a5, a5sf, _ = operand(128, 5120, 11)
+    a17, a17sf, _ = operand(128, 17408, 12)
+    out = {}
+    w, wsf, _ = operand(7168, 5120, 21)
+    out["qkv"] = torch.empty(M, 7168, device=DEV)
+    call("q27t_skinny_fp4_segments", M, 7168, 5120, a5, a5sf, w, wsf, 3, (ctypes.c_int * 3)(*QKV_BEGIN),
+         (ctypes.c_float * 3)(*QKV_ALPHA), None, 0.0, out["qkv"], ws, ws.numel())
+    w, wsf, _ = operand(5120, 5120, 22)
+    out["o"] = torch.empty(M, 5120, device=DEV)
+    call("q27t_skinny_fp4", M, 5120, 5120, a5, a5sf, w, wsf, 0.5, res[:M], 1.0, out["o"], ws, ws.numel())
+    w, wsf, _ = operand(34816, 5120, 23)
+    out["gate_up"] = torch.empty(M, 17408, dtype=torch.bfloat16, device=DEV)
+    call("q27t_skinny_fp4_glu_bf16", M, 17408, 5120, a5, a5sf, w, wsf, 0.013, 0.021, out["gate_up"], ws, ws.numel())
+    w, wsf, _ = operand(5120, 17408, 24)
+    out["down"] = torch.empty(M, 5120, dtype=torch.bfloat16, device=DEV)
+    call("q27t_skinny_fp4_bf16", M, 5120, 17408, a17, a17sf, w, wsf, 0.7, out["down"], ws, ws.numel())
+    return out
+
+
+def layer_problems(M, res, outs):
+    a5, a5sf, _ = operand(128, 5120, 11)
+    a17, a17sf, _ = operand(128, 17408, 12)
+    ps = []
+    w, wsf, _ = operand(7168, 5120, 21)
+    ps.append(problem(7168, 5120, EPI_F32, a5, a5sf, w, wsf, outs["qkv"], QKV_ALPHA, QKV_BEGIN))
+    w, wsf, _ = operand(5120, 5120, 22)
+    ps.append(problem(5120, 5120, EPI_F32, a5, a5sf, w, wsf, outs["o"], (0.5,), c=res))
+    w, wsf, _ = operand(34816, 5120, 23)
+    ps.append(problem(34816, 5120, EPI_GLU_BF16, a5, a5sf, w, wsf, outs["gate_up"], (0.013,), alpha_up=0.021))
+    w, wsf, _ = operand(5120, 17408, 24)
+    ps.append(problem(5120, 17408, EPI_BF16, a17, a17sf, w, wsf, outs["down"], (0.7,)))
+    return ps
+
+
+def fresh_outputs(M):
+    return {"qkv": torch.full((M, 7168), float("nan"), device=DEV), "o": torch.full((M, 5120), float("nan"), device=DEV),
+            "gate_up": torch.zeros(M, 17408, dtype=torch.bfloat16, device=DEV),
+            "down": torch.zeros(M, 5120, dtype=torch.bfloat16, device=DEV)}
+
+
+@pytest.mark.parametrize("M", [1, 2, 4, 8, 16, 32, 64, 128])
+def test_group_of_a_layer_equals_single_calls(M):
+    res = torch.randn(128, 5120, device=DEV)
+    want = layer_by_single_calls(M, workspace(WS), res)
+    # sanity of the reference side against the fp64 product (one projection; the others have tests of their own)
+    _, _, adq = operand(128, 5120, 11)
+    _, _, wdq = operand(5120, 5120, 22)
+    assert rel_err(want["o"].cpu().numpy(), 0.5 * (adq[:M] @ wdq.T) + res[:M].cpu().numpy().astype(np.float64)) < 1e-5
+    got = fresh_outputs(M)
+    grp = Fp4Group(M, layer_problems(M, res[:M].contiguous(), got))
+    grp.ws.view(torch.uint8)[256 * ((136 * 4 + 255) // 256):] = 0xFF  # partial tiles poisoned with NaN bit patterns
+    for _ in range(2):  # the second launch runs on the counters and partial tiles the first one left behind
+        for t in got.values():
+            t.fill_(float("nan")) if t.dtype == torch.float32 else t.zero_()
+        grp.run_sync()
+        for name in want:
+            assert torch.equal(got[name], want[name]), f"{name} differs at M={M}"
+
+
+def test_group_of_three_layers_in_place_residual():
+    """Several layers in one launch (the same weights, separate outputs), o with its residual in place."""
+    M = 16
+    res = torch.randn(128, 5120, device=DEV)
+    want = layer_by_single_calls(M, workspace(WS), res)
+    probs, outs = [], []
+    for _ in range(3):
+        got = fresh_outputs(M)
+        got["o"] = res[:M].clone()
+        ps = layer_problems(M, got["o"], got)  # c aliases d
+        probs += ps
+        outs.append(got)
+    grp = Fp4Group(M, probs)
+    grp.run_sync()
+    for got in outs:
+        for name in want:
+            assert torch.equal(got[name], want[name]), name
+
+
+@pytest.mark.parametrize("M", [3, 16, 77])
+def test_group_of_small_and_odd_shapes(M):
+    """K not a multiple of 256, a single tile, a tile count below the CTA count, and the contiguous-range split of a
+    very wide weight in one group."""
+    shapes = [(384, 448), (128, 5120), (1024, 5120), (128, 64), (44032, 5120)]
+    ws = workspace(WS)
+    probs, got, want = [], [], []
+    for i, (N, K) in enumerate(shapes):
+        a, asf, _ = operand(128, K, 100 + i)
+        w, wsf, _ = operand(N, K, 200 + i)
+        d = torch.empty(M, N, device=DEV)
+        call("q27t_skinny_fp4", M, N, K, a, asf, w, wsf, 0.37, None, 0.0, d, ws, ws.numel())
+        want.append(d)
+        g = torch.full((M, N), float("nan"), device=DEV)
+        got.append(g)
+        probs.append(problem(N, K, EPI_F32, a, asf, w, wsf, g, (0.37,)))
+    grp = Fp4Group(M, probs)
+    for _ in range(2):
+        grp.run_sync()
+        for (N, K), g, w_ in zip(shapes, got, want):
+            assert torch.equal(g, w_), (N, K)
+
+
+def test_group_rejects_bad_arguments():
+    a, asf, _ = operand(128, 5120, 11)
+    w, wsf, _ = operand(5120, 5120, 22)
+    d = torch.empty(4, 5120, device=DEV)
+    with pytest.raises(RuntimeError, match="M must be 1..128"):
+        Fp4Group(129, [problem(5120, 5120, EPI_F32, a, asf, w, wsf, d)])
+    with pytest.raises(RuntimeError, match="multiple of 128"):
+        Fp4Group(4, [problem(5000, 5120, EPI_F32, a, asf, w, wsf, d)])
+    with pytest.raises(RuntimeError, match="residual needs the fp32 epilogue"):
+        Fp4Group(4, [problem(5120, 5120, EPI_BF16, a, asf, w, wsf, d, c=d)])
+    grp = Fp4Group(4, [problem(5120, 5120, EPI_F32, a, asf, w, wsf, d)])
+    small = torch.zeros(64, dtype=torch.uint8, device=DEV)
+    with pytest.raises(RuntimeError, match="workspace too small"):
+        call("q27t_skinny_fp4_group", grp.table_host, grp.table_dev, small, small.numel())

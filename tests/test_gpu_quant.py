@@ -188,3 +188,97 @@ def test_quant_fp4_dynamic_against_oracle():
     c3, s3, r3 = O.quant_act_dynamic(xb.float().numpy())
     assert np.array_equal(q2.cpu().numpy(), c3) and np.array_equal(asc2.cpu().numpy(), r3)
     assert np.array_equal(layouts.unswizzle(sf2.cpu().numpy(), M, K // 16), s3)
+
+
+def test_quant_fp4_batch_equals_single_calls():
+    """Several activations quantised by one launch (jobs in the launch parameters up to four, in device memory
+    above) give the bytes of one call each."""
+    import ctypes
+
+    class Job(ctypes.Structure):  # q27b_quant_job
+        _fields_ = [("x", ctypes.c_void_p), ("q", ctypes.c_void_p), ("sf", ctypes.c_void_p), ("M", ctypes.c_int),
+                    ("K", ctypes.c_int), ("input_scale", ctypes.c_float), ("bf16", ctypes.c_int)]
+
+    rng = np.random.RandomState(11)
+    shapes = [(16, 5120, torch.bfloat16), (3, 17408, torch.float32), (128, 5120, torch.bfloat16), (1, 64, torch.float32),
+              (7, 5120, torch.float32), (16, 17408, torch.bfloat16)]
+    for n in (3, 6):
+        xs, outs, want, jobs = [], [], [], (Job * n)()
+        for i, (M, K, dt) in enumerate(shapes[:n]):
+            x = torch.from_numpy((rng.standard_normal((M, K)) * (i + 1)).astype(np.float32)).to(dt).to(DEV)
+            s = 0.01 * (i + 1)
+            want.append(run_quant(x, M, K, s))
+            q = torch.full((M, K // 2), 0xAA, dtype=torch.uint8, device=DEV)
+            sf = torch.zeros(lib().q27t_sf_bytes(M, K // 16), dtype=torch.uint8, device=DEV)
+            xs.append(x), outs.append((q, sf))
+            jobs[i].x, jobs[i].q, jobs[i].sf = x.data_ptr(), q.data_ptr(), sf.data_ptr()
+            jobs[i].M, jobs[i].K, jobs[i].input_scale, jobs[i].bf16 = M, K, s, int(dt == torch.bfloat16)
+        table = None
+        if n > 4:
+            table = torch.frombuffer(bytearray(bytes(jobs)), dtype=torch.uint8).to(DEV)
+        torch.cuda.synchronize()
+        call("q27b_quant_fp4_batch", jobs, table, n, torch.cuda.current_stream().cuda_stream)
+        torch.cuda.synchronize()
+        for (q, sf), (wq, wsf) in zip(outs, want):
+            assert np.array_equal(q.cpu().numpy(), wq) and np.array_equal(sf.cpu().numpy(), wsf)
+    with pytest.raises(RuntimeError, match="more than four jobs"):
+        call("q27b_quant_fp4_batch", jobs, None, 6, 0)
+
+
+@pytest.mark.parametrize("T", [1, 5, 16])
+def test_rmsnorm_quant(T):
+    """RMSNorm(1 + w) fused with the quantiser (protocol of engine/tests/test_elementwise.py:94-115): the fp32 result
+    against the reference's definition within 1e-5, and - stronger - bit for bit against the fixed-order fp32
+    restatement; the quantised copy exactly the quantisation of the fp32 result (codes and scale bytes)."""
+    D = 5120
+    rng = np.random.RandomState(T)
+    x = (rng.standard_normal((T, D)) * 3).astype(np.float32)
+    x[0, 64:80] = 0
+    if T > 2:
+        x[2] *= 1e-3
+    w = torch.from_numpy((rng.standard_normal(D) * 0.1).astype(np.float32)).bfloat16()
+    s = 0.0123
+    out = torch.full((T, D), float("nan"), device=DEV)
+    q = torch.full((T, D // 2), 0xAA, dtype=torch.uint8, device=DEV)
+    sf = torch.zeros(lib().q27t_sf_bytes(T, D // 16), dtype=torch.uint8, device=DEV)
+    call("q27t_rmsnorm_quant", dev(x), w.to(DEV), T, 1e-6, out, 2, s, q, sf)
+    y = out.cpu().numpy()
+    ref = O.rms_norm(x, w.float().numpy(), 1e-6)
+    assert (np.abs(y - ref) <= 1e-5 + 1e-5 * np.abs(ref)).all()
+    y32, _ = O.rms_norm_fixed_order(x, w.float().numpy(), 1e-6)
+    assert np.array_equal(y, y32)
+    check_against_oracle(y, q.cpu().numpy(), sf.cpu().numpy(), s)
+    # the plain form writes the same fp32 result and leaves q alone
+    out2 = torch.empty_like(out)
+    q2 = torch.full_like(q, 0x55)
+    call("q27t_rmsnorm_quant", dev(x), w.to(DEV), T, 1e-6, out2, 0, s, q2, sf)
+    assert torch.equal(out2, out) and (q2 == 0x55).all()
+
+
+def test_rmsnorm_quant_golden_and_options():
+    """On the golden vectors made by the reference's own functions; with the bf16 copy of the input and 1 / rms."""
+    import os
+
+    g = dict(np.load(os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden", "nvfp4_rmsnorm_golden.npz")))
+    x, w, eps, s = g["x"], g["w"], float(g["eps"]), float(g["in_scale"])
+    T, D = x.shape
+    out = torch.empty(T, D, device=DEV)
+    q = torch.zeros(T, D // 2, dtype=torch.uint8, device=DEV)
+    sf = torch.zeros(lib().q27t_sf_bytes(T, D // 16), dtype=torch.uint8, device=DEV)
+    cap = torch.zeros(T, D + 64, dtype=torch.bfloat16, device=DEV)
+    rstd = torch.zeros(T, device=DEV)
+    wd = torch.from_numpy(w).bfloat16().to(DEV)
+    torch.cuda.synchronize()
+    call("q27b_rmsnorm_quant_fp4", dev(x), wd, T, D, eps, out, s, q, sf, cap, D + 64, rstd, torch.cuda.current_stream().cuda_stream)
+    torch.cuda.synchronize()
+    y = out.cpu().numpy()
+    assert (np.abs(y - g["y"]) <= 1e-5 + 1e-5 * np.abs(g["y"])).all()
+    gs = np.float32(1.0) / np.float32(s)
+    deq = (O.unpack_e2m1(q.cpu().numpy()) * np.repeat(O.e4m3_decode(layouts.unswizzle(sf.cpu().numpy(), T, D // 16)), 16, -1)).astype(np.float32) / gs
+    assert np.array_equal(deq, O.quant_act_nvfp4(y, s))
+    assert (deq != g["y_quant"]).mean() < 1e-3  # the reference's fp32 result differs in the last bit here and there
+    assert torch.equal(cap[:, :D].cpu(), torch.from_numpy(x).bfloat16()) and not cap[:, D:].any()
+    _, r = O.rms_norm_fixed_order(x, w, eps)
+    assert np.array_equal(rstd.cpu().numpy(), r)
+    with pytest.raises(RuntimeError, match="multiple of 512"):
+        call("q27b_rmsnorm_quant_fp4", dev(x), wd, T, 5000, eps, out, s, q, sf, None, 0, None, 0)

@@ -38,7 +38,7 @@ def expected(adq, bdq32, alpha):
     return alpha * (torch.from_numpy(adq) @ torch.from_numpy(bdq32).double().T).numpy()
 
 
-SHAPES = [(5120, 17408), (17408, 5120), (34816, 5120), (128, 5120), (1024, 5120), (384, 448)]
+SHAPES = [(5120, 5120), (5120, 17408), (17408, 5120), (34816, 5120), (128, 5120), (1024, 5120), (384, 448)]
 
 
 @pytest.mark.parametrize("M", [1, 2, 3, 4, 8, 13, 16, 29, 32, 64, 77, 128])

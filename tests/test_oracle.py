@@ -1,6 +1,8 @@
 """Pins the CPU oracle: the reference's own known-answer tests (reference/tests/test_quant.py, restated as
 literal vectors) and golden vectors recorded from the reference's Python modules (tests/golden)."""
 
+import os
+
 import numpy as np
 import pytest
 import torch
@@ -216,3 +218,21 @@ def test_dynamic_per_token_quantiser_properties():
         assert s.max() == 0x7E  # the largest block reaches the top of the E4M3 range: 448
     c2, s2, r2 = O.quant_act_dynamic(x * np.float32(8))
     assert np.array_equal(c2, codes) and np.array_equal(s2, sfs) and np.array_equal(r2[[0, 1, 3, 4, 5]], rs[[0, 1, 3, 4, 5]] * 8)
+
+
+def test_rms_norm_against_the_references_function():
+    """The oracle's RMSNorm and the fixed-order fp32 restatement of this repository's fused kernel against golden
+    vectors made by the reference's own rms_norm and quant_act_nvfp4 (tests/golden/make_golden_rmsnorm.py), within the
+    tolerance the reference's kernel test allows (engine/tests/test_elementwise.py:94-115: rtol = atol = 1e-5)."""
+    g = dict(np.load(os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden", "nvfp4_rmsnorm_golden.npz")))
+    x, w, eps, s = g["x"], g["w"], float(g["eps"]), float(g["in_scale"])
+    y64 = O.rms_norm(x, w, eps)
+    assert np.abs(y64 - g["y"]).max() < 2e-6
+    y32, r = O.rms_norm_fixed_order(x, w, eps)
+    assert y32.dtype == np.float32 and (np.abs(y32 - g["y"]) <= 1e-5 + 1e-5 * np.abs(g["y"])).all()
+    assert np.allclose(r, 1.0 / np.sqrt((x.astype(np.float64) ** 2).mean(-1) + eps), rtol=1e-6)
+    # the quantised copy is defined as the quantisation of the fp32 result
+    assert np.array_equal(O.quant_act_nvfp4(g["y"], s), g["y_quant"])
+    # an all-zero row stays zero (1 / sqrt(eps) is finite)
+    z, rz = O.rms_norm_fixed_order(np.zeros((1, 512), np.float32), np.zeros(512, np.float32), 1e-6)
+    assert not z.any() and np.isfinite(rz).all()

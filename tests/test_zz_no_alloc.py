@@ -35,13 +35,21 @@ def test_static_scratch_matches_workspace_entry_point(M, N, K):
     c = torch.randn(M, N, device=DEV)
     want_res = c.clone()
     call("q27t_skinny_fp4", M, N, K, ad, asw, bd, bsw, alpha, want_res, 1.0, want_res, ws, ws.numel())
+    got = torch.empty(M, N, device=DEV)
+    got_res = torch.empty(M, N, device=DEV)
+    call("q27t_skinny_fp4_static", M, N, K, ad, asw, bd, bsw, alpha, None, 0.0, got)  # (first use on this device)
+    torch.equal(got, want)  # (torch's comparison takes its scratch from the caching allocator once, before the reading)
+    torch.cuda.synchronize()
+    free_before = torch.cuda.mem_get_info()[0]
     for _ in range(2):  # the second call runs on the scratch array exactly as the first one left it
-        got = torch.full((M, N), float("nan"), device=DEV)
+        got.fill_(float("nan"))
         call("q27t_skinny_fp4_static", M, N, K, ad, asw, bd, bsw, alpha, None, 0.0, got)
         assert torch.equal(got, want)  # same kernel, same split: the tolerance is zero
-        got_res = c.clone()
+        got_res.copy_(c)
         call("q27t_skinny_fp4_static", M, N, K, ad, asw, bd, bsw, alpha, got_res, 1.0, got_res)
         assert torch.equal(got_res, want_res)
+    # what the entry point is for: the calls took no device memory (every tensor above existed before them)
+    assert torch.cuda.mem_get_info()[0] == free_before
 
 
 def test_static_scratch_rejects_sizes_beyond_its_limit():

@@ -392,7 +392,21 @@ def run_sweep(args, model, rank, world, local_rank, peaks):
         verified = verified and ok
         per = ms / args.steps
         sweep[str(M)] = {"gbs": nbytes / per / 1e6, "ms_per_sweep": per, "frac": nbytes / per / 1e6 / world / peaks["hbm_gbs"],
-                         "verified": ok}
+                         "mode": f"grouped, {G} layer(s) per launch", "verified": ok}
+        if M > 16:
+            # many tokens: a cut tile is summed by the one CTA that delivers its last piece, which costs the grouped
+            # launch more than its saved launch boundaries; the per-GEMM form (fix-up kernel over the whole GPU) is
+            # timed as well and the faster of the two is reported, by name
+            sw.drop_groups()
+            ms2 = timed(lambda i: sw.step_per_gemm(), args.steps, args.warmup, world, graph_cap=5)
+            ok2 = sw.verify()
+            verified = verified and ok2
+            sweep[str(M)]["grouped_gbs"] = sweep[str(M)]["gbs"]
+            sweep[str(M)]["per_gemm_gbs"] = nbytes / (ms2 / args.steps) / 1e6
+            if ms2 < ms:
+                per = ms2 / args.steps
+                sweep[str(M)].update({"gbs": nbytes / per / 1e6, "ms_per_sweep": per, "frac": nbytes / per / 1e6 / world / peaks["hbm_gbs"],
+                                      "mode": "per GEMM (one launch per projection, programmatic dependent launch)", "verified": ok2})
         log(f"sweep M={M}: {sweep[str(M)]}")
         if M == head_m:
             head = dict(sweep[str(M)], clocks=clocks, bytes=nbytes)

@@ -5,8 +5,11 @@
 // Each problem keeps exactly the K split its stand-alone launch would use (choose_skinny_plan, layout.h): the
 // pieces {tile, chunk range} and the order in which the pieces of a cut tile are summed are the same, which makes
 // the grouped results bit-identical to per-GEMM calls. What changes is only WHO streams a piece: the pieces of
-// all problems are dealt to the CTAs longest first onto the least loaded CTA, and every CTA then walks its pieces
-// in problem order.
+// all problems are dealt to the CTAs longest first onto the least loaded CTA, and every CTA walks its pieces in
+// problem order: the pieces of one tile are then streamed at about the same time by their CTAs, so the CTA that
+// sums the tile (fixed by the plan: piece tile % pieces) finds the other pieces there soon after its own.
+// (`rotate`: every CTA starts at a different point of its list instead; kept for experiments only - it spreads the
+// pieces of a tile over the whole run of the kernel.)
 //
 // Host-only code (no CUDA): shared by the launcher and the CPU tests.
 #pragma once
@@ -32,7 +35,8 @@ struct GroupItem {
   const uint8_t* w_sf_tile;  // scale atoms of this tile's 128 weight rows (device pointer)
   const uint8_t* a_sf;       // scale atoms of the problem's activation (device pointer)
   int counter;               // index of the tile's arrival counter in the workspace
-  int pad[3];
+  int sums;                  // 1: the CTA that streams this piece also sums the tile (one piece per cut tile)
+  int pad[2];
 };
 static_assert(sizeof(GroupItem) == 64, "GroupItem is read as four 16-byte words");
 
@@ -76,6 +80,8 @@ inline void problem_pieces(int prob, const GroupShape& s, int cta_slots, int64_t
       pieces[k].slot0 = n > 1 ? int(next_slot) : -1;
       pieces[k].slot = n > 1 ? int(next_slot + int64_t(k - i)) : -1;
       pieces[k].counter = n > 1 ? next_counter : -1;
+      // which piece's CTA sums the tile: dealt round the pieces so that the sums spread over the CTAs
+      pieces[k].sums = n > 1 && int(k - i) == pieces[i].tile % n;
     }
     if (n > 1) next_slot += n, next_counter++;
     i = j;
@@ -84,7 +90,7 @@ inline void problem_pieces(int prob, const GroupShape& s, int cta_slots, int64_t
 }
 
 // Deals the pieces of all problems to at most `cta_slots` CTAs (the CTAs that can be resident at once).
-inline GroupSchedule schedule_group(const GroupShape* shapes, int n, int cta_slots) {
+inline GroupSchedule schedule_group(const GroupShape* shapes, int n, int cta_slots, bool rotate = false) {
   GroupSchedule sch;
   std::vector<GroupItem> all;
   int64_t next_slot = 0;
@@ -113,6 +119,7 @@ inline GroupSchedule schedule_group(const GroupShape* shapes, int n, int cta_slo
   sch.cta_first.assign(ctas + 1, 0);
   for (int g = 0; g < ctas; g++) {
     std::sort(mine[g].begin(), mine[g].end());  // problem order, then tile, then K
+    if (rotate && !mine[g].empty()) std::rotate(mine[g].begin(), mine[g].begin() + g % int(mine[g].size()), mine[g].end());
     for (int i : mine[g]) sch.items.push_back(all[i]);
     sch.cta_first[g + 1] = int(sch.items.size());
   }

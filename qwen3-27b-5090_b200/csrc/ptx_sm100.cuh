@@ -18,6 +18,7 @@ enum : uint32_t {
   kStatusAccumFreeTimeout = 4,   // MMA issuer never saw an accumulator buffer drained
   kStatusDrainTimeout = 5,       // a copy in flight did not land during unwinding
   kStatusProbeTimeout = 6,       // the self-test's wait on a barrier nothing arrives at ran out, as it must
+  kStatusTileWaitTimeout = 7,    // grouped launch: the pieces of a cut tile never all arrived
 };
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) {

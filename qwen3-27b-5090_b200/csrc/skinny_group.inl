@@ -7,9 +7,9 @@
 // problem p + 1 are already in flight while the last stages of problem p are multiplied, its cut tiles summed and
 // its epilogue stored. Ring fill and tail are paid once per group.
 //
-// Each problem keeps the K split of its stand-alone launch and a cut tile is summed in ascending K order by
-// whichever CTA delivers its last piece (arrival counter, nobody waits for anybody), so the results are
-// bit-identical to q27b_skinny_fp4 / _bf16 / _glu_bf16 called problem by problem, for every M.
+// Each problem keeps the K split of its stand-alone launch and a cut tile is summed in ascending K order whatever
+// the order in which its pieces arrive, so the results are bit-identical to q27b_skinny_fp4 / _bf16 / _glu_bf16
+// called problem by problem, for every M. Which CTA sums a tile is fixed by the plan (see the epilogue).
 //
 // The table (header, problems with their two tensor maps, per-CTA piece lists) is built once on the host
 // (q27b_skinny_group_build) and lives in device memory the caller owns; a launch only passes pointers, so it can
@@ -43,9 +43,52 @@ struct GroupLaunch {
   int M;
   int* counters;         // one per cut tile, zero between launches
   float* partials;       // [slots][M][128]
+#ifdef Q27B_TRACE
+  unsigned long long* trace;  // [cta][16]: per-role busy / waiting times in ns (null: off)
+#endif
 };
 
+#ifdef Q27B_TRACE
+#define GTRACE_DECL(name) unsigned long long name = 0
+#define GTRACE_T0(t) const unsigned long long t = gtime()
+#define GTRACE_ADD(acc, t) acc += gtime() - t
+#define GTRACE_INC(acc) acc += 1
+#define GTRACE_PUT(slot, v)                                                     \
+  do {                                                                          \
+    if (g.trace) g.trace[size_t(blockIdx.x) * 16 + (slot)] = (v);               \
+  } while (0)
+#else
+#define GTRACE_DECL(name)
+#define GTRACE_T0(t)
+#define GTRACE_ADD(acc, t)
+#define GTRACE_INC(acc)
+#define GTRACE_PUT(slot, v)
+#endif
+
 __device__ __forceinline__ int4 ldg16(const void* p) { return __ldg(reinterpret_cast<const int4*>(p)); }
+__device__ __forceinline__ int ld_acquire_gpu(const int* p) {
+  int v;
+  asm volatile("ld.acquire.gpu.global.s32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+constexpr int kSumBatch = 4;  // partial tiles whose loads are in flight together when a cut tile is summed
+
+// Tile configuration of the grouped kernel: the stage layout of the stand-alone weight-streaming kernel, but as
+// many accumulator buffers as tensor memory holds beside the scale columns (8 at 16 tokens, 4 at 32, 2 at 64, 1 at
+// 128). A piece of a cut tile is only 2-4 stages long while its epilogue (partial tile out, arrival counted, now and
+// then the sum of a whole tile) takes as long as streaming it: with many buffers the MMAs run several pieces ahead
+// and the epilogue catches up during the long uncut tiles instead of stalling the stream.
+template <int NB, int STAGES>
+struct GroupCfg {
+  using C = Cfg<NB, STAGES, 2, true>;
+  static constexpr int kAccBufs = (C::kTmemCols - C::kSfCols * STAGES) / NB < 8 ? (C::kTmemCols - C::kSfCols * STAGES) / NB : 8;
+  static constexpr int kSfCol0 = kAccBufs * NB;
+  static constexpr int kXchgBytes = 8 * 64 * 4 + 16 * 16;      // SiLU*mul exchange between the gate and the up warps + the queue of tiles to sum
+  static constexpr int kNumBars = 3 * STAGES + 2 * kAccBufs;
+  static constexpr int kSmemBytes = STAGES * C::kStageBytes + kXchgBytes + kNumBars * 8 + 16 + 1024;
+  static_assert(kAccBufs >= 1 && kSfCol0 + C::kSfCols * STAGES <= C::kTmemCols, "tensor memory budget");
+  static_assert(2 * (kSmemBytes + 1024) <= 228 * 1024, "shared memory budget");
+};
 
 // The stages (units of 128 weight rows x 256 K-elements) of this CTA in the order it streams them. The record of
 // the next piece is requested while the current one is being streamed, so that moving on never waits for memory.
@@ -90,14 +133,15 @@ struct GroupUnits {
 template <int NB, int STAGES>
 __global__ void __launch_bounds__((Cfg<NB, STAGES, 2, true>::kThreads), 2) skinny_group_kernel(const __grid_constant__ GroupLaunch g) {
   using C = Cfg<NB, STAGES, 2, true>;
+  using G = GroupCfg<NB, STAGES>;
   static_assert(C::kQAtoms == 1, "the tokens of a group fit one 128-row block");
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   float* xchg = reinterpret_cast<float*>(smem + STAGES * C::kStageBytes);
-  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + STAGES * C::kStageBytes + C::kXchgBytes);
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + STAGES * C::kStageBytes + G::kXchgBytes);
   const uint32_t full0 = smem_u32(bars), empty0 = full0 + 8 * STAGES, sfr0 = empty0 + 8 * STAGES,
-                 afull0 = sfr0 + 8 * STAGES, aempty0 = afull0 + 16;
-  uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(bars + C::kNumBars);
+                 afull0 = sfr0 + 8 * STAGES, aempty0 = afull0 + 8 * G::kAccBufs;
+  uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(bars + G::kNumBars);
   volatile uint32_t* abort_flag = tmem_holder + 1;
   volatile uint32_t* last_flag = tmem_holder + 2;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -120,7 +164,7 @@ __global__ void __launch_bounds__((Cfg<NB, STAGES, 2, true>::kThreads), 2) skinn
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < STAGES; s++) mbar_init(full0 + 8 * s, 1), mbar_init(empty0 + 8 * s, 1), mbar_init(sfr0 + 8 * s, 4);
-    for (int b = 0; b < 2; b++) mbar_init(afull0 + 8 * b, 1), mbar_init(aempty0 + 8 * b, C::kEpiWarps);
+    for (int b = 0; b < G::kAccBufs; b++) mbar_init(afull0 + 8 * b, 1), mbar_init(aempty0 + 8 * b, C::kEpiWarps);
     *abort_flag = 0;
     mbar_init_fence();
     // The stream starts at once: the ring is filled with weights (which no kernel of this stream produces) while the
@@ -151,22 +195,28 @@ __global__ void __launch_bounds__((Cfg<NB, STAGES, 2, true>::kThreads), 2) skinn
       uint32_t phase = npre == STAGES ? 1 : 0;
       bool ok = true;
       int cur_prob = -1;
+      GTRACE_DECL(t_wait_empty);
+      GTRACE_PUT(0, gtime());
       for (; k.valid; k.advance()) {
         if (k.prob != cur_prob) {  // descriptors of a problem this CTA has not touched yet
           cur_prob = k.prob;
           prefetch_tensormap(&g.probs[cur_prob].tmap_w);
           prefetch_tensormap(&g.probs[cur_prob].tmap_a);
         }
+        GTRACE_T0(t0);
         if (!mbar_wait_bounded(empty0 + 8 * stage, phase ^ 1, abort_flag, &g_status, kStatusEmptyWaitTimeout)) {
           ok = false;
           break;
         }
+        GTRACE_ADD(t_wait_empty, t0);
         mbar_arrive_expect_tx(full0 + 8 * stage, stage_bytes(k));
         last_parity = (last_parity & ~(1u << stage)) | (phase << stage);
         load_w(k, stage);
         load_a(k, stage);
         if (++stage == STAGES) stage = 0, phase ^= 1;
       }
+      GTRACE_PUT(1, gtime());
+      GTRACE_PUT(2, t_wait_empty);
       pdl_trigger();  // everything this CTA reads from HBM has been requested
       if (!ok) {
         for (int s = 0; s < STAGES; s++)
@@ -188,24 +238,30 @@ __global__ void __launch_bounds__((Cfg<NB, STAGES, 2, true>::kThreads), 2) skinn
       int stage = 0, nseg = 0;
       uint32_t phase = 0;
       bool ok = true;
+      GTRACE_DECL(t_wait_acc);
+      GTRACE_DECL(t_wait_stage);
       for (int i = i0; ok && i < i1; i++) {
         const int4 w0 = ldg16(g.items + i), w1 = ldg16(reinterpret_cast<const int4*>(g.items + i) + 1);
         const int c0 = w0.z, c1 = w0.w, ksteps = w1.w, n = i - i0;
-        const int buf = n % C::kAccBufs, use = n / C::kAccBufs;
+        const int buf = n % G::kAccBufs, use = n / G::kAccBufs;
+        GTRACE_T0(ta);
         if (!mbar_wait_bounded(aempty0 + 8 * buf, (use & 1) ^ 1, abort_flag, &g_status, kStatusAccumFreeTimeout)) break;
+        GTRACE_ADD(t_wait_acc, ta);
         tc_fence_after_sync();
         const uint32_t d_tmem = tmem_base + buf * NB;
         uint32_t accumulate = 0;
         for (int c = c0; c < c1; c++) {
+          GTRACE_T0(ts);
           if (!mbar_wait_bounded(sfr0 + 8 * stage, phase, abort_flag, &g_status, kStatusFullWaitTimeout)) {
             ok = false;
             break;
           }
+          GTRACE_ADD(t_wait_stage, ts);
           tc_fence_after_sync();
           const int nsteps = min(4, ksteps - 4 * c);
           const uint32_t sbase = smem_base + stage * C::kStageBytes;
           const uint64_t desc_p = umma_desc_k_sw128(sbase), desc_q = umma_desc_k_sw128(sbase + C::kOffQ);
-          const uint32_t sf_col = tmem_base + C::kSfCol0 + C::kSfCols * stage;
+          const uint32_t sf_col = tmem_base + G::kSfCol0 + C::kSfCols * stage;
           for (int ks = 0; ks < nsteps; ks++) {
             umma_nvfp4(d_tmem, desc_p + 2 * ks, desc_q + 2 * ks, idesc, sf_col + 4 * ks, sf_col + 16 + 4 * ks, accumulate);
             accumulate = 1;
@@ -216,8 +272,11 @@ __global__ void __launch_bounds__((Cfg<NB, STAGES, 2, true>::kThreads), 2) skinn
         if (ok) umma_commit(afull0 + 8 * buf);
         nseg = n + 1;
       }
-      for (int j = nseg - 1; ok && j >= 0 && j >= nseg - C::kAccBufs; j--)
-        ok = mbar_wait_bounded(aempty0 + 8 * (j % C::kAccBufs), (j / C::kAccBufs) & 1, abort_flag, &g_status,
+      GTRACE_PUT(3, t_wait_acc);
+      GTRACE_PUT(4, t_wait_stage);
+      GTRACE_PUT(5, gtime());
+      for (int j = nseg - 1; ok && j >= 0 && j >= nseg - G::kAccBufs; j--)
+        ok = mbar_wait_bounded(aempty0 + 8 * (j % G::kAccBufs), (j / G::kAccBufs) & 1, abort_flag, &g_status,
                                kStatusAccumFreeTimeout, 64);
     }
   } else if (warp >= C::kFeederWarp0) {
@@ -231,7 +290,7 @@ __global__ void __launch_bounds__((Cfg<NB, STAGES, 2, true>::kThreads), 2) skinn
       const uint8_t* sb = smem + stage * C::kStageBytes;
       const uint4* sfp = reinterpret_cast<const uint4*>(sb + C::kOffSfP) + lane;
       const uint4* sfq = reinterpret_cast<const uint4*>(sb + C::kOffSfQ) + lane;
-      const uint32_t taddr = tmem_base + lane_base + C::kSfCol0 + C::kSfCols * stage;
+      const uint32_t taddr = tmem_base + lane_base + G::kSfCol0 + C::kSfCols * stage;
       uint4 a[4];
 #pragma unroll
       for (int ks = 0; ks < 4; ks++) a[ks] = sfp[32 * ks];
@@ -247,64 +306,68 @@ __global__ void __launch_bounds__((Cfg<NB, STAGES, 2, true>::kThreads), 2) skinn
     }
   } else {
     // ------------------------------------------------------------------------------------------ epilogue
+    // A piece that is a whole tile is finished here. A piece of a CUT tile leaves its partial sums in the workspace and
+    // counts its arrival (fire and forget). One piece of every cut tile is marked by the planner: its CTA sums the tile,
+    // in ascending K order whatever the order of arrival. It does not wait for the other pieces: the tile goes into a
+    // short queue, and before each later piece the CTA looks once whether the oldest queued tile is complete; what is
+    // still queued when the CTA has no pieces left is waited for (bounded). The sums are thus dealt out by the plan,
+    // evenly - with "whoever arrives last sums" the CTAs that fall behind collect the sums and fall further behind.
     const int quarter = warp & 3;
     const int row = quarter * 32 + lane;  // weight row of the tile = output channel
-    GemmParams p = {};                    // the epilogue's view of the current problem
-    p.M = g.M;
-    int cur_prob = -1, epi = 0;
-    for (int i = i0; i < i1; i++) {
-      const int4 w0 = ldg16(g.items + i), w1 = ldg16(reinterpret_cast<const int4*>(g.items + i) + 1);
-      const int tile = w0.y, slot = w1.x, nparts = w1.y, slot0 = w1.z;
-      const int counter = __ldg(&g.items[i].counter);
-      if (w0.x != cur_prob) {
-        cur_prob = w0.x;
-        const GroupProblemDev* q = g.probs + cur_prob;
-        p.d = q->d, p.c = q->c, p.alpha = q->alpha, p.alpha_up = q->alpha_up, p.beta = q->beta, p.N = q->N, epi = q->epi;
-      }
-      auto store = [&](const float(&v)[8], int m0) {
-        if (epi == kEpiGluBf16) store_swapped<kEpiGluBf16>(p, v, m0, tile, row, xchg);
-        else if (epi == kEpiBf16) store_swapped<kEpiBf16>(p, v, m0, tile, row, xchg);
-        else store_swapped<kEpiF32>(p, v, m0, tile, row, xchg);
-      };
-      const int n = i - i0, buf = n % C::kAccBufs;
-      if (!warp_wait(afull0 + 8 * buf, (n / C::kAccBufs) & 1, abort_flag, &g_status, kStatusAccumWaitTimeout, 128)) break;
-      tc_fence_after_sync();
-      const uint32_t taddr = tmem_base + (uint32_t(quarter * 32) << 16) + buf * NB;
-      if (slot < 0) {
-        for (int m0 = 0; m0 < p.M; m0 += 8) {
-          float v[8];
-          tmem_ld8(taddr + m0, v);
-          tmem_ld_wait();
-          store(v, m0);
-        }
-        tc_fence_before_sync();
-        __syncwarp();
-        if (lane == 0) mbar_arrive(aempty0 + 8 * buf);
-        continue;
-      }
-      // A piece of a cut tile: leave the partial sums, count the arrival; whoever delivers the last piece sums all of
-      // them in ascending K order (whatever the order of arrival) and finishes the tile.
-      for (int m0 = 0; m0 < p.M; m0 += 8) {
-        float v[8];
-        tmem_ld8(taddr + m0, v);
-        tmem_ld_wait();
-        float* part = g.partials + (int64_t(slot) * p.M + m0) * 128 + row;
-#pragma unroll
-        for (int j = 0; j < 8; j++)
-          if (m0 + j < p.M) __stcg(part + j * 128, v[j]);
-      }
-      tc_fence_before_sync();
-      __syncwarp();
-      if (lane == 0) mbar_arrive(aempty0 + 8 * buf);
-      epi_bar();  // every partial sum of this CTA is written ...
+    const int M = g.M;
+    constexpr int kQueue = 16;
+    int4* queue = reinterpret_cast<int4*>(xchg + 8 * 64);  // {first slot, pieces | problem << 16, counter, tile}
+    int head = 0, queued = 0, polls = 0;
+    bool ok = true;
+    GTRACE_DECL(t_wait_mma);
+    GTRACE_DECL(t_reduce);
+    GTRACE_DECL(n_reduce);
+    // The epilogue's view of a problem, read when a tile is finished (once per whole tile or summed tile; the
+    // record sits in L1 / L2) rather than carried in registers across pieces.
+    auto load_problem = [&](int prob, GemmParams& dst, int& e) {
+      const GroupProblemDev* q = g.probs + prob;
+      dst.M = M, dst.d = q->d, dst.c = q->c, dst.alpha = q->alpha, dst.alpha_up = q->alpha_up, dst.beta = q->beta, dst.N = q->N;
+      dst.wscale = nullptr, e = q->epi;
+    };
+    auto store = [&](const GemmParams& q, int e, const float(&v)[8], int m0, int tile) {
+      if (e == kEpiGluBf16) store_swapped<kEpiGluBf16>(q, v, m0, tile, row, xchg);
+      else if (e == kEpiBf16) store_swapped<kEpiBf16>(q, v, m0, tile, row, xchg);
+      else store_swapped<kEpiF32>(q, v, m0, tile, row, xchg);
+    };
+    // Has every piece of the oldest queued tile arrived? One thread reads the counter; `wait`: keep reading (bounded).
+    auto oldest_complete = [&](bool wait) -> bool {
+      volatile uint32_t* flag = last_flag + (polls++ & 1);
       if (threadIdx.x == 64) {
-        __threadfence();  // ... and published device-wide before the arrival is counted
-        *last_flag = atomicAdd(g.counters + counter, 1) == nparts - 1;
+        const int4 e = queue[head % kQueue];
+        const int want = e.y & 0xffff;
+        bool done = ld_acquire_gpu(g.counters + e.z) == want;
+        if (!done && wait) {
+          const long long t0 = clock64();
+          for (uint32_t it = 0; !done && it < kMaxPolls; it++) {
+            __nanosleep(200);
+            done = ld_acquire_gpu(g.counters + e.z) == want;
+            if ((it & 63u) == 63u && (*abort_flag || clock64() - t0 > kMaxWaitCycles)) break;
+          }
+          if (!done) {
+            *abort_flag = 1u;
+            atomicCAS(&g_status, 0u, uint32_t(kStatusTileWaitTimeout));
+          }
+        }
+        *flag = done;
       }
       epi_bar();
-      if (!*last_flag) continue;
-      __threadfence();
-      if (p.M <= 2) {
+      return *flag != 0;
+    };
+    // Sums the pieces of the oldest queued tile in ascending K order and finishes the tile.
+    auto sum_oldest = [&]() {
+      const int4 e = queue[head % kQueue];
+      head++, queued--;
+      const int slot0 = e.x, nparts = e.y & 0xffff, prob = e.y >> 16, counter = e.z, tile = e.w;
+      GemmParams pr;
+      int sum_epi;
+      load_problem(prob, pr, sum_epi);
+      GTRACE_T0(tr);
+      if (pr.M <= 2) {
         // one or two tokens (plain decode): up to eight pieces in flight, one round trip
         float v[8] = {};
         for (int q0 = 0; q0 < nparts; q0 += 8) {
@@ -312,9 +375,9 @@ __global__ void __launch_bounds__((Cfg<NB, STAGES, 2, true>::kThreads), 2) skinn
 #pragma unroll
           for (int q = 0; q < 8; q++) {
             if (q0 + q < nparts) {
-              const float* part = g.partials + int64_t(slot0 + q0 + q) * p.M * 128 + row;
+              const float* part = g.partials + int64_t(slot0 + q0 + q) * pr.M * 128 + row;
               x[q][0] = __ldcg(part);
-              x[q][1] = p.M > 1 ? __ldcg(part + 128) : 0.f;
+              x[q][1] = pr.M > 1 ? __ldcg(part + 128) : 0.f;
             }
           }
 #pragma unroll
@@ -325,32 +388,107 @@ __global__ void __launch_bounds__((Cfg<NB, STAGES, 2, true>::kThreads), 2) skinn
             }
           }
         }
-        store(v, 0);
+        store(pr, sum_epi, v, 0, tile);
       } else {
-        for (int m0 = 0; m0 < p.M; m0 += 8) {
+        for (int m0 = 0; m0 < pr.M; m0 += 8) {
           float v[8];
-          for (int q0 = 0; q0 < nparts; q0 += 4) {  // four pieces in flight at a time
-            float x[4][8];
+          for (int q0 = 0; q0 < nparts; q0 += kSumBatch) {  // kSumBatch pieces in flight at a time
+            float x[kSumBatch][8];
 #pragma unroll
-            for (int q = 0; q < 4; q++) {
+            for (int q = 0; q < kSumBatch; q++) {
               if (q0 + q < nparts) {
-                const float* part = g.partials + (int64_t(slot0 + q0 + q) * p.M + m0) * 128 + row;
+                const float* part = g.partials + (int64_t(slot0 + q0 + q) * pr.M + m0) * 128 + row;
 #pragma unroll
-                for (int j = 0; j < 8; j++) x[q][j] = m0 + j < p.M ? __ldcg(part + j * 128) : 0.f;
+                for (int j = 0; j < 8; j++) x[q][j] = m0 + j < pr.M ? __ldcg(part + j * 128) : 0.f;
               }
             }
 #pragma unroll
-            for (int q = 0; q < 4; q++) {
+            for (int q = 0; q < kSumBatch; q++) {
               if (q0 + q < nparts) {
 #pragma unroll
                 for (int j = 0; j < 8; j++) v[j] = (q0 + q == 0) ? x[q][j] : __fadd_rn(v[j], x[q][j]);
               }
             }
           }
-          store(v, m0);
+          store(pr, sum_epi, v, m0, tile);
         }
       }
       if (threadIdx.x == 64) g.counters[counter] = 0;  // the counters are zero again when the kernel ends
+      GTRACE_ADD(t_reduce, tr);
+      GTRACE_INC(n_reduce);
+    };
+
+    for (int i = i0; ok && i < i1; i++) {
+      const int4 w0 = ldg16(g.items + i), w1 = ldg16(reinterpret_cast<const int4*>(g.items + i) + 1),
+                 w3 = ldg16(reinterpret_cast<const int4*>(g.items + i) + 3);
+      const int prob = w0.x, tile = w0.y, slot = w1.x, nparts = w1.y, slot0 = w1.z, counter = w3.x, sums = w3.y;
+      if (queued > 0) {  // one look per piece; the queue only blocks when it is full
+        if (oldest_complete(queued == kQueue)) sum_oldest();
+        else if (queued == kQueue) break;  // (timed out: the status word says so)
+      }
+      const int n = i - i0, buf = n % G::kAccBufs;
+      GTRACE_T0(tw);
+      if (!warp_wait(afull0 + 8 * buf, (n / G::kAccBufs) & 1, abort_flag, &g_status, kStatusAccumWaitTimeout, 128)) {
+        ok = false;
+        break;
+      }
+      GTRACE_ADD(t_wait_mma, tw);
+      tc_fence_after_sync();
+      const uint32_t taddr = tmem_base + (uint32_t(quarter * 32) << 16) + buf * NB;
+      if (slot < 0) {
+        GemmParams p;
+        int epi;
+        load_problem(prob, p, epi);
+        for (int m0 = 0; m0 < M; m0 += 8) {
+          float v[8];
+          tmem_ld8(taddr + m0, v);
+          tmem_ld_wait();
+          store(p, epi, v, m0, tile);
+        }
+        tc_fence_before_sync();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(aempty0 + 8 * buf);
+        continue;
+      }
+      for (int m0 = 0; m0 < M; m0 += 16) {
+        float* part = g.partials + (int64_t(slot) * M + m0) * 128 + row;
+        if (M - m0 > 8) {
+          float v[16];
+          tmem_ld16(taddr + m0, v);
+          tmem_ld_wait();
+#pragma unroll
+          for (int j = 0; j < 16; j++)
+            if (m0 + j < M) __stcg(part + j * 128, v[j]);
+        } else {
+          float v[8];
+          tmem_ld8(taddr + m0, v);
+          tmem_ld_wait();
+#pragma unroll
+          for (int j = 0; j < 8; j++)
+            if (m0 + j < M) __stcg(part + j * 128, v[j]);
+        }
+      }
+      tc_fence_before_sync();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(aempty0 + 8 * buf);
+      epi_bar();  // every partial sum of this CTA is written ...
+      if (threadIdx.x == 64) {
+        __threadfence();  // ... and published device-wide before the arrival is counted
+        atomicAdd(g.counters + counter, 1);
+        if (sums) queue[(head + queued) % kQueue] = make_int4(slot0, nparts | (prob << 16), counter, tile);
+      }
+      if (sums) queued++;
+    }
+    while (ok && queued > 0) {  // what is still queued: wait for the other pieces (bounded)
+      if (!oldest_complete(true)) break;
+      sum_oldest();
+    }
+    if (threadIdx.x == 64) {
+      GTRACE_PUT(6, t_wait_mma);
+      GTRACE_PUT(7, t_reduce);
+      GTRACE_PUT(8, n_reduce);
+      GTRACE_PUT(9, gtime());
+      GTRACE_PUT(10, (unsigned long long)(i1 - i0));
     }
   }
 
@@ -389,11 +527,11 @@ int launch_group(const GroupLaunch& gl, int ctas, cudaStream_t s) {
   int dev = 0;
   Q27B_CUDA(cudaGetDevice(&dev));
   if (!(dev < 64 && done[dev])) {
-    Q27B_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, C::kSmemBytes));
+    Q27B_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, GroupCfg<NB, STAGES>::kSmemBytes));
     if (dev < 64) done[dev] = true;
   }
   cudaLaunchConfig_t cfg = {};
-  cfg.gridDim = dim3(ctas), cfg.blockDim = dim3(C::kThreads), cfg.dynamicSmemBytes = C::kSmemBytes, cfg.stream = s;
+  cfg.gridDim = dim3(ctas), cfg.blockDim = dim3(C::kThreads), cfg.dynamicSmemBytes = GroupCfg<NB, STAGES>::kSmemBytes, cfg.stream = s;
   cudaLaunchAttribute attr[1];
   attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
   attr[0].val.programmaticStreamSerializationAllowed = 1;

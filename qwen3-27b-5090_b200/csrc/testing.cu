@@ -88,7 +88,7 @@ int q27b_skinny_tile_parts(int N, int K, int slots, int tile, int* slot, int cap
   return t.n;
 }
 
-int q27b_skinny_group_plan(int n, const int* N, const int* K, int slots, int* pieces, int cap, int* ctas_out,
+int q27b_skinny_group_plan(int n, const int* N, const int* K, int slots, int rotate, int* pieces, int cap, int* ctas_out,
                            int64_t* slots_out, int* counters_out) {
   if (n <= 0 || !N || !K || slots <= 0) return fail("skinny_group_plan: bad arguments");
   std::vector<GroupShape> shapes(n);
@@ -96,7 +96,7 @@ int q27b_skinny_group_plan(int n, const int* N, const int* K, int slots, int* pi
     if (N[i] <= 0 || N[i] % 128 || K[i] <= 0 || K[i] % 64) return fail("skinny_group_plan: bad shape");
     shapes[i] = {N[i], K[i]};
   }
-  const GroupSchedule sch = schedule_group(shapes.data(), n, slots);
+  const GroupSchedule sch = schedule_group(shapes.data(), n, slots, rotate != 0);
   if (ctas_out) *ctas_out = int(sch.cta_units.size());
   if (slots_out) *slots_out = sch.slots;
   if (counters_out) *counters_out = sch.counters;
@@ -104,8 +104,8 @@ int q27b_skinny_group_plan(int n, const int* N, const int* K, int slots, int* pi
     for (int i = sch.cta_first[g]; i < sch.cta_first[g + 1]; i++) {
       if (!pieces || i >= cap) continue;
       const GroupItem& it = sch.items[i];
-      const int v[8] = {int(g), it.prob, it.tile, it.c0, it.c1, it.slot, it.nparts, it.slot0};
-      for (int j = 0; j < 8; j++) pieces[8 * i + j] = v[j];
+      const int v[9] = {int(g), it.prob, it.tile, it.c0, it.c1, it.slot, it.nparts, it.slot0, it.sums};
+      for (int j = 0; j < 9; j++) pieces[9 * i + j] = v[j];
     }
   return int(sch.items.size());
 }

@@ -1380,6 +1380,9 @@ int q27b_skinny_fp4_group(const void* table_host, const void* table_dev, void* w
   gl.M = h.M;
   gl.counters = static_cast<int*>(ws);
   gl.partials = reinterpret_cast<float*>(static_cast<uint8_t*>(ws) + align_up(int64_t(h.counters) * 4, 256));
+#ifdef Q27B_TRACE
+  gl.trace = g_trace;
+#endif
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   switch (h.nb) {
     case 16: return launch_group<16, 4>(gl, h.n_ctas, s);

@@ -8,6 +8,7 @@ taken out, bit-identical to calling the projections one by one.
 from __future__ import annotations
 
 import ctypes
+import struct
 
 import torch
 
@@ -58,6 +59,9 @@ class Fp4Group:
         self.table_host = (ctypes.c_uint8 * tb.value)()
         call("q27b_skinny_group_build", M, self.n, arr, self.table_host, tb.value, ctypes.byref(tb), ctypes.byref(wb))
         self.table_bytes, self.ws_bytes = tb.value, max(wb.value, 256)
+        # header of the table (GroupHeader, csrc/skinny_group.inl): what was planned
+        (_, _, self.tokens_tile, _, self.ctas, self.pieces, self.counters, self.sms, self.slots) = struct.unpack_from("<I7iq", self.table_host)
+        self.partials_offset = (self.counters * 4 + 255) // 256 * 256  # arrival counters first, then the partial tiles
         host = torch.frombuffer(self.table_host, dtype=torch.uint8)
         self.table_dev = host.to(device)  # torch's device allocations are at least 256-byte aligned
         if workspace is None:

@@ -94,7 +94,8 @@ def test_group_of_a_layer_equals_single_calls(M):
     assert rel_err(want["o"].cpu().numpy(), 0.5 * (adq[:M] @ wdq.T) + res[:M].cpu().numpy().astype(np.float64)) < 1e-5
     got = fresh_outputs(M)
     grp = Fp4Group(M, layer_problems(M, res[:M].contiguous(), got))
-    grp.ws.view(torch.uint8)[256 * ((136 * 4 + 255) // 256):] = 0xFF  # partial tiles poisoned with NaN bit patterns
+    assert grp.ctas == 2 * torch.cuda.get_device_properties(0).multi_processor_count and grp.counters == 136
+    grp.ws[grp.partials_offset:] = 0xFF  # partial tiles poisoned with NaN bit patterns
     for _ in range(2):  # the second launch runs on the counters and partial tiles the first one left behind
         for t in got.values():
             t.fill_(float("nan")) if t.dtype == torch.float32 else t.zero_()

@@ -117,15 +117,15 @@ def test_skinny_plan_choices():
     assert plan(248320, 5120, 296)[2] == 0     # lm_head: contiguous ranges (no wave quantisation)
 
 
-def group_plan(shapes, slots):
+def group_plan(shapes, slots, rotate=0):
     n = len(shapes)
     Ns, Ks = (ctypes.c_int * n)(*[s[0] for s in shapes]), (ctypes.c_int * n)(*[s[1] for s in shapes])
     ctas, nslots, counters = ctypes.c_int(), ctypes.c_int64(), ctypes.c_int()
     l = scaffold_lib()
-    count = l.q27b_skinny_group_plan(n, Ns, Ks, slots, None, 0, ctypes.byref(ctas), ctypes.byref(nslots), ctypes.byref(counters))
-    buf = (ctypes.c_int * (8 * count))()
-    assert l.q27b_skinny_group_plan(n, Ns, Ks, slots, buf, count, None, None, None) == count
-    pieces = [tuple(buf[8 * i:8 * i + 8]) for i in range(count)]
+    count = l.q27b_skinny_group_plan(n, Ns, Ks, slots, rotate, None, 0, ctypes.byref(ctas), ctypes.byref(nslots), ctypes.byref(counters))
+    buf = (ctypes.c_int * (9 * count))()
+    assert l.q27b_skinny_group_plan(n, Ns, Ks, slots, rotate, buf, count, None, None, None) == count
+    pieces = [tuple(buf[9 * i:9 * i + 9]) for i in range(count)]
     return ctas.value, nslots.value, counters.value, pieces
 
 
@@ -143,9 +143,9 @@ def test_group_schedule_keeps_each_problems_own_split(shapes, slots):
     by_problem = {}
     loads = np.zeros(ctas, dtype=np.int64)
     last_key = {}
-    for cta, prob, tile, c0, c1, slot, nparts, slot0 in pieces:
+    for cta, prob, tile, c0, c1, slot, nparts, slot0, sums in pieces:
         assert 0 <= cta < ctas
-        by_problem.setdefault(prob, []).append((tile, c0, c1, slot, nparts, slot0))
+        by_problem.setdefault(prob, []).append((tile, c0, c1, slot, nparts, slot0, sums))
         loads[cta] += c1 - c0
         assert last_key.get(cta, (-1, -1, -1)) < (prob, tile, c0)  # a CTA walks its pieces in problem order
         last_key[cta] = (prob, tile, c0)
@@ -158,11 +158,13 @@ def test_group_schedule_keeps_each_problems_own_split(shapes, slots):
         assert [g[:3] for g in got] == want  # the same pieces as the stand-alone launch
         chunks = (K + 255) // 256
         tiles = {}
-        for t, c0, c1, slot, nparts, slot0 in got:
-            tiles.setdefault(t, []).append((c0, c1, slot, nparts, slot0))
+        for t, c0, c1, slot, nparts, slot0, sums in got:
+            tiles.setdefault(t, []).append((c0, c1, slot, nparts, slot0, sums))
         for t, parts in tiles.items():
             assert all(p[3] == len(parts) for p in parts)
             assert parts[0][0] == 0 and parts[-1][1] == chunks and all(a[1] == b[0] for a, b in zip(parts, parts[1:]))
+            # exactly one piece of a cut tile is marked: its CTA sums the tile (dealt round the pieces by tile index)
+            assert [p[5] for p in parts] == [int(len(parts) > 1 and k == t % len(parts)) for k in range(len(parts))]
             if len(parts) == 1:
                 assert parts[0][2] == -1
             else:
@@ -174,8 +176,20 @@ def test_group_schedule_keeps_each_problems_own_split(shapes, slots):
     assert used_slots == set(range(nslots)) and counters == cut_tiles
     total = sum(N // 128 * ((K + 255) // 256) for N, K in shapes)
     assert loads.sum() == total
-    biggest = max(c1 - c0 for _, _, _, c0, c1, _, _, _ in pieces)
+    biggest = max(p[4] - p[3] for p in pieces)
     assert loads.max() - loads.min() <= biggest  # longest-first dealing: no CTA is more than one piece ahead
+    # the experimental order: the same pieces on the same CTAs, each CTA's list rotated to a start of its own
+    _, _, _, rotated = group_plan(shapes, slots, rotate=1)
+    assert sorted(rotated) == sorted(pieces)
+    per_cta = {}
+    for p in pieces:
+        per_cta.setdefault(p[0], []).append(p)
+    rot_cta = {}
+    for p in rotated:
+        rot_cta.setdefault(p[0], []).append(p)
+    for g, lst in per_cta.items():
+        k = g % len(lst)
+        assert rot_cta[g] == lst[k:] + lst[:k]
 
 
 def test_group_schedule_balance_on_a_layer():

@@ -39,43 +39,59 @@ cudaStream_t test_stream() {
   return s;
 }
 
-// Runs f (which launches on test_stream()) the way the reference's test wrappers do, then checks that no bounded
-// wait inside a kernel ran out.
-template <class F>
-int kernel(F&& f) {
-  Q27B_CUDA(cudaDeviceSynchronize());
-  if (int rc = f()) return rc;
-  Q27B_CUDA(cudaStreamSynchronize(test_stream()));
-  const char* e = getenv("Q27T_REPEAT");
-  const int rep = e ? atoi(e) : 0;
-  if (rep > 0) {
-    cudaGraph_t g;
-    cudaGraphExec_t ge;
-    Q27B_CUDA(cudaStreamBeginCapture(test_stream(), cudaStreamCaptureModeThreadLocal));
-    int rc = 0;
-    for (int i = 0; i < rep && !rc; i++) rc = f();
-    Q27B_CUDA(cudaStreamEndCapture(test_stream(), &g));
-    if (rc) return rc;
-    Q27B_CUDA(cudaGraphInstantiate(&ge, g, 0));
-    cudaEvent_t e0, e1;
-    Q27B_CUDA(cudaEventCreate(&e0));
-    Q27B_CUDA(cudaEventCreate(&e1));
-    Q27B_CUDA(cudaGraphLaunch(ge, test_stream()));  // warm-up
-    Q27B_CUDA(cudaEventRecord(e0, test_stream()));
-    Q27B_CUDA(cudaGraphLaunch(ge, test_stream()));
-    Q27B_CUDA(cudaEventRecord(e1, test_stream()));
-    Q27B_CUDA(cudaEventSynchronize(e1));
-    float ms = 0.f;
-    Q27B_CUDA(cudaEventElapsedTime(&ms, e0, e1));
-    g_last_us = 1000.f * ms / rep;
-    cudaEventDestroy(e0);
-    cudaEventDestroy(e1);
-    cudaGraphExecDestroy(ge);
-    cudaGraphDestroy(g);
+// What the synchronous wrappers do around one launcher call `launch` (a callable returning the library's status
+// code, launching on test_stream()):
+//   1. drain the device, so that the call starts from a quiet GPU and earlier failures are not blamed on it;
+//   2. launch once and wait for the private stream;
+//   3. when the environment asks for timing (Q27T_REPEAT=n, the reference's switch, engine/src/capi.cc:57-92): time n
+//      more launches, replayed from a CUDA graph so that host launch cost stays out, into q27t_last_us();
+//   4. fail if a kernel gave up on a bounded wait (device status word).
+struct ReplayTimer {  // the graph of `n` launches and the two events; everything is released on scope exit
+  cudaGraph_t graph = nullptr;
+  cudaGraphExec_t exec = nullptr;
+  cudaEvent_t begin = nullptr, end = nullptr;
+  ~ReplayTimer() {
+    if (begin) cudaEventDestroy(begin);
+    if (end) cudaEventDestroy(end);
+    if (exec) cudaGraphExecDestroy(exec);
+    if (graph) cudaGraphDestroy(graph);
   }
-  uint32_t status = 0;
-  if (int rc = q27b_device_status(&status)) return rc;
-  Q27B_REQUIRE(status == 0, "a bounded wait inside a kernel ran out (device status %u)", status);
+};
+
+template <class Launch>
+int time_replays(Launch& launch, int n) {
+  ReplayTimer t;
+  cudaStream_t s = test_stream();
+  Q27B_CUDA(cudaStreamBeginCapture(s, cudaStreamCaptureModeThreadLocal));
+  int status = 0;
+  for (int i = 0; i < n && status == 0; i++) status = launch();
+  Q27B_CUDA(cudaStreamEndCapture(s, &t.graph));  // (always ended, also after a failed launch)
+  if (status != 0) return status;
+  Q27B_CUDA(cudaGraphInstantiate(&t.exec, t.graph, 0));
+  Q27B_CUDA(cudaEventCreate(&t.begin));
+  Q27B_CUDA(cudaEventCreate(&t.end));
+  Q27B_CUDA(cudaGraphLaunch(t.exec, s));  // one untimed replay first
+  Q27B_CUDA(cudaEventRecord(t.begin, s));
+  Q27B_CUDA(cudaGraphLaunch(t.exec, s));
+  Q27B_CUDA(cudaEventRecord(t.end, s));
+  Q27B_CUDA(cudaEventSynchronize(t.end));
+  float ms = 0.f;
+  Q27B_CUDA(cudaEventElapsedTime(&ms, t.begin, t.end));
+  g_last_us = ms * 1000.f / float(n);
+  return 0;
+}
+
+template <class Launch>
+int kernel(Launch&& launch) {
+  Q27B_CUDA(cudaDeviceSynchronize());
+  if (int status = launch()) return status;
+  Q27B_CUDA(cudaStreamSynchronize(test_stream()));
+  const char* repeat = getenv("Q27T_REPEAT");
+  if (repeat && atoi(repeat) > 0)
+    if (int status = time_replays(launch, atoi(repeat))) return status;
+  uint32_t waited_out = 0;
+  if (int status = q27b_device_status(&waited_out)) return status;
+  Q27B_REQUIRE(waited_out == 0, "a bounded wait inside a kernel ran out (device status %u)", waited_out);
   return 0;
 }
 

@@ -8,6 +8,8 @@ torch's current stream; torch only owns the device memory.
 from __future__ import annotations
 
 import ctypes
+import os
+import sys
 
 import torch
 
@@ -124,8 +126,24 @@ class Fp4Linear:
         return out
 
     def gemm(self, M, q, sf, out, residual=None):
+        """The dispatch of Model::gemm_q (engine/src/model.cc:869-888) with its two debugging switches, read at every
+        call like the reference's: Q27_NO_SKINNY=1 sends every token count to the many-row kernel; Q27_SKINNY_CHECK=1
+        runs the many-row kernel beside the weight-streaming one and reports a relative difference above 1e-4 on
+        stderr (engine/src/model.cc:773-805). The check synchronises; it is a debugging aid, not a product path."""
         N, K, s = self.rows(), self.inp, _stream()
-        skinny = M <= SKINNY_MAX_M
+        skinny = M <= SKINNY_MAX_M and os.environ.get("Q27_NO_SKINNY", "0") in ("", "0")
+        if skinny and os.environ.get("Q27_SKINNY_CHECK", "0") not in ("", "0") and self._nseg == 1 and residual is None and N % 128 == 0 and K % 128 == 0:
+            self._dispatch(M, q, sf, out, residual, True, N, K, s)
+            other = torch.empty_like(out)
+            self._dispatch(M, q, sf, other, residual, False, N, K, s)
+            a, b = out.float(), other.float()
+            rel = float((a - b).norm() / b.norm().clamp_min(1e-30))
+            if rel > 1e-4:
+                print(f"Q27_SKINNY_CHECK: M={M} N={N} K={K}: weight-streaming vs many-row GEMM differ by {rel:.3e}", file=sys.stderr)
+            return
+        self._dispatch(M, q, sf, out, residual, skinny, N, K, s)
+
+    def _dispatch(self, M, q, sf, out, residual, skinny, N, K, s):
         if self.glu:
             assert out.dtype == torch.bfloat16 and residual is None
             if skinny:

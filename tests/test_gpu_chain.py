@@ -240,3 +240,23 @@ def test_ext_reduce_switch_keeps_the_bits():
             os.environ.pop("Q27_SKINNY_EXT_REDUCE_M", None)
     assert rel_err(outs[0].cpu().numpy(), 0.5 * (adq @ bdq.T)) < 1e-5
     assert torch.equal(outs[0], outs[1]) and torch.equal(outs[0], outs[2])
+
+
+def test_dispatch_switches(capsys):
+    """Q27_NO_SKINNY sends few tokens to the many-row kernel as well; Q27_SKINNY_CHECK runs both and stays silent
+    when they agree (they compute the same products in the same order per tile)."""
+    layers, H, I = small_layer(1)
+    lin = layers[0]["o"]
+    x = torch.randn(5, H, generator=torch.Generator().manual_seed(3)).bfloat16().to(DEV)
+    lin.set_in_scale(configs.input_scale_of(x))
+    y = lin(x)
+    for name in ("Q27_NO_SKINNY", "Q27_SKINNY_CHECK"):
+        os.environ[name] = "1"
+        try:
+            y2 = lin(x)
+        finally:
+            del os.environ[name]
+        torch.cuda.synchronize()
+        assert rel_err(y2.float().cpu().numpy(), y.float().cpu().numpy()) < 2e-3
+    assert "differ" not in capsys.readouterr().err
+    assert device_status() == 0

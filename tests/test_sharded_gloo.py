@@ -45,6 +45,19 @@ CHILD = textwrap.dedent("""
         assert got.shape == want.shape, (got.shape, want.shape)
         assert np.allclose(got, want, rtol=1e-5, atol=1e-6), np.abs(got - want).max()
         assert np.array_equal(got[:, c0:c1], local.astype(np.float32))
+    # unequal contributions never reach the collective: the host check raises on every rank first
+    try:
+        shard.check_even_shards(640, 2)  # 5 tiles of 128 rows on 2 ranks
+        raise SystemExit("uneven shards were accepted")
+    except ValueError:
+        pass
+    shard.check_even_shards(512, 2)
+    ragged = torch.zeros(M, 128 + 128 * rank)
+    try:
+        shard.all_gather_output(ragged)
+        raise SystemExit("a ragged gather was attempted")
+    except ValueError:
+        pass
     dist.barrier()
     dist.destroy_process_group()
     print("rank", rank, "ok")

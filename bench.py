@@ -304,6 +304,11 @@ class Sweep:
         jobs, table, n = self._quant_jobs(l0, l1)
         call("q27b_quant_fp4_batch", jobs, table, n, torch.cuda.current_stream().cuda_stream)
 
+    def whole_tiles(self, layers):
+        """Groups of several layers run without the K split (whole tiles fill the GPU evenly by themselves); a single
+        layer keeps the split of the stand-alone launches."""
+        return layers >= 8
+
     def group(self, l0, l1):
         from q27b200.group import Fp4Group, problem_of
 
@@ -314,7 +319,7 @@ class Sweep:
                 for n in self.NAMES:
                     a = self.act[l][self.src[n]]
                     probs.append(problem_of(self.model[l][n], a.q, a.sf, self.outs[l][n]))
-            self._groups[key] = Fp4Group(self.M, probs)
+            self._groups[key] = Fp4Group(self.M, probs, whole_tiles=self.whole_tiles(l1 - l0))
         return self._groups[key]
 
     def drop_groups(self):
@@ -346,11 +351,30 @@ class Sweep:
 
     # -- checking ----------------------------------------------------------------------------------------------------
 
-    def verify(self):
-        """The outputs the last timed step left behind, against the same step run one kernel at a time."""
+    def _many_row(self, lin, a, out):
+        """One projection through the many-row GEMM entry points (no K split): per alpha segment of a stacked weight."""
+        from q27b200.q27lib import call
+
+        s, K, M = torch.cuda.current_stream().cuda_stream, lin.inp, self.M
+        if lin.glu:
+            call("q27b_gemm_fp4_glu_bf16", M, lin.out, K, a.q, a.sf, lin.w, lin.sf, lin.alpha, lin.alpha, out, s)
+            return
+        begins = [lin._zero[i] for i in range(lin._nseg)] + [lin.rows()]
+        for i in range(lin._nseg):
+            b, e = begins[i], begins[i + 1]
+            part = out if lin._nseg == 1 else torch.empty(M, e - b, dtype=out.dtype, device=out.device)
+            call("q27b_gemm_fp4_bf16", M, e - b, K, a.q, a.sf, lin.w[b:e], lin.sf[b // 128 * (K // 64) * 512:], lin._alpha[i], part, s)
+            if lin._nseg > 1:
+                out[:, b:e] = part
+
+    def verify(self, G):
+        """The outputs the last timed step left behind, against the same step run one kernel at a time through the
+        per-GEMM entry points: the weight-streaming launch, or - for groups planned without the K split, whose sums
+        run over all of K in one chain - the many-row GEMM."""
         got = self.out_all.clone()
         gathered = self.gathered.clone() if self.gathered is not None else None
         self.out_all.zero_()
+        whole = G > 0 and self.whole_tiles(min(G, self.L))
         with serial_launches():
             for l in range(self.L):
                 for n in self.NAMES:
@@ -358,7 +382,10 @@ class Sweep:
                     k = self.src[n]
                     a.quantize(self.x[k], self.scale[k])
                     torch.cuda.synchronize()
-                    self.model[l][n].gemm(self.M, a.q, a.sf, self.outs[l][n])
+                    if whole:
+                        self._many_row(self.model[l][n], a, self.outs[l][n])
+                    else:
+                        self.model[l][n].gemm(self.M, a.q, a.sf, self.outs[l][n])
                     torch.cuda.synchronize()
         ok = bool(torch.equal(got, self.out_all)) and bool(torch.isfinite(got.float()).all()) and bool(got.any())
         if gathered is not None:
@@ -388,18 +415,18 @@ def run_sweep(args, model, rank, world, local_rank, peaks):
             clocks = clk.summary()
         else:
             ms = timed(lambda i: sw.step_grouped(G), args.steps, args.warmup, world, graph_cap=5)
-        ok = sw.verify()
+        ok = sw.verify(G)
         verified = verified and ok
         per = ms / args.steps
         sweep[str(M)] = {"gbs": nbytes / per / 1e6, "ms_per_sweep": per, "frac": nbytes / per / 1e6 / world / peaks["hbm_gbs"],
-                         "mode": f"grouped, {G} layer(s) per launch", "verified": ok}
+                         "mode": f"grouped, {G} layer(s) per launch" + (", whole tiles" if sw.whole_tiles(G) else ""), "verified": ok}
         if M > 16:
             # many tokens: a cut tile is summed by the one CTA that delivers its last piece, which costs the grouped
             # launch more than its saved launch boundaries; the per-GEMM form (fix-up kernel over the whole GPU) is
             # timed as well and the faster of the two is reported, by name
             sw.drop_groups()
             ms2 = timed(lambda i: sw.step_per_gemm(), args.steps, args.warmup, world, graph_cap=5)
-            ok2 = sw.verify()
+            ok2 = sw.verify(0)
             verified = verified and ok2
             sweep[str(M)]["grouped_gbs"] = sweep[str(M)]["gbs"]
             sweep[str(M)]["per_gemm_gbs"] = nbytes / (ms2 / args.steps) / 1e6
@@ -411,19 +438,26 @@ def run_sweep(args, model, rank, world, local_rank, peaks):
         if M == head_m:
             head = dict(sweep[str(M)], clocks=clocks, bytes=nbytes)
             # the same sweep in the other launch forms
-            for name, g in (("per_gemm", 0), ("group_1_layer", 1), ("group_8_layers", 8), ("group_64_layers", 64)):
+            for name, g in (("per_gemm", 0), ("group_1_layer", 1), ("group_4_layers", 4), ("group_8_layers", 8), ("group_64_layers", 64)):
                 if g > L or (g == G):
                     continue
                 sw.drop_groups()
                 fn = (lambda i: sw.step_per_gemm()) if g == 0 else (lambda i, g=g: sw.step_grouped(g))
                 ms_mode = timed(fn, args.steps, args.warmup, world, graph_cap=5)
-                ok = sw.verify()
+                ok = sw.verify(g)
                 verified = verified and ok
                 modes[name] = {"gbs": nbytes / (ms_mode / args.steps) / 1e6, "ms_per_sweep": ms_mode / args.steps,
                                "launches_per_sweep": sw.launches_per_step(g), "verified": ok}
                 log(f"mode {name}: {modes[name]}")
             modes[f"group_{G}_layer{'s' if G > 1 else ''}"] = {"gbs": head["gbs"], "ms_per_sweep": head["ms_per_sweep"],
                                                                  "launches_per_sweep": sw.launches_per_step(G), "verified": head["verified"]}
+            if world > 1:  # the same steps without the collective, for the cost of the gather
+                def step_no_gather(i):
+                    for l0 in range(0, L, G):
+                        sw.quantise(l0, min(l0 + G, L))
+                        sw.group(l0, min(l0 + G, L)).launch()
+                ms_ng = timed(step_no_gather, args.steps, args.warmup, world, graph_cap=5)
+                head["without_allgather"] = {"gbs": nbytes / (ms_ng / args.steps) / 1e6, "ms_per_sweep": ms_ng / args.steps}
             # the same K steps after 0.4 s of uninterrupted replays: streaming at this rate runs into the board's power cap
             # (sw_power_cap, SM clock down to 1.5-1.7 GHz), which a long-running decode loop would see
             with ClockSampler(local_rank) as clk:
@@ -443,7 +477,7 @@ def run_sweep(args, model, rank, world, local_rank, peaks):
                 y_host.copy_(src, non_blocking=True)
 
             ms_e2e = timed(step_e2e, args.steps, args.warmup, world, graph_cap=5)
-            ok = sw.verify() and bool(torch.equal(y_host.cuda(), (sw.gathered[0][-M * sw.width:] if world > 1 else sw.out_all[L - 1])))
+            ok = sw.verify(G) and bool(torch.equal(y_host.cuda(), (sw.gathered[0][-M * sw.width:] if world > 1 else sw.out_all[L - 1])))
             verified = verified and ok
             head["e2e"] = {"value": nbytes / (ms_e2e / args.steps) / 1e6, "unit": "GB/s",
                            "h2d_bytes_per_step": sum(v.numel() * 2 for v in sw.x_host.values()),
@@ -681,7 +715,8 @@ def main():
             "config": {"workload": workload_name(args.layers, r["head_m"]),
                        "l2": f"every projection of every layer in its own device memory ({configs.layer_weight_bytes() * args.layers / 1e9:.1f} GB), far beyond the 126 MB L2",
                        "step": f"per group of {G} layer(s): one launch quantising the layers' bf16 activations (q27b_quant_fp4_batch), "
-                               f"one grouped weight-streaming GEMM over their projections (q27b_skinny_fp4_group)"
+                               f"one grouped weight-streaming GEMM over their projections (q27b_skinny_fp4_group"
+                               + (", planned without the K split: whole tiles)" if G >= 8 else ")")
                                + ("; then one NCCL all-gather of all outputs, inside the timed graph" if world > 1 else ""),
                        "timing": "CUDA-graph replay, CUDA events on the launching stream",
                        "sharding": f"weight rows N-sharded {world} way(s), no reduction"},
@@ -692,6 +727,7 @@ def main():
                          "us_per_launch": h["ms_per_sweep"] * 1e3 / math.ceil(args.layers / G),
                          "peak_source": peaks["source"] + ": copy bandwidth"},
             "clocks": h["clocks"], "sustained": h["sustained"], "e2e": h["e2e"], "gpu_launches": args.steps * h["launches"],
+            **({"without_allgather": h["without_allgather"]} if "without_allgather" in h else {}),
             "sweep": r["sweep"], "modes": r["modes"]})
     subs = {}
     for idx in (0, 1, 2, 4):

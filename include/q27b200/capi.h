@@ -150,8 +150,8 @@ int q27b_skinny_fp4_static(int M, int N, int K, const uint8_t* a, const uint8_t*
  * No counterpart in the reference, which launches one kernel per projection and hides the launch boundaries with
  * CUDA graphs and programmatic dependent launch (engine/src/launch.cuh:1-8, engine/src/skinny.cu:225-237). On this
  * GPU a decode GEMM needs 2-4 us of HBM time and a launch boundary costs more than that, so here every CTA streams
- * its share of the weight tiles of ALL problems of the group back to back. Each problem keeps the K split of its
- * stand-alone launch: the results are bit-identical to q27b_skinny_fp4 / _bf16 / _glu_bf16 called one by one.
+ * its share of the weight tiles of ALL problems of the group back to back. By default each problem keeps the K split
+ * of its stand-alone launch: the results are bit-identical to q27b_skinny_fp4 / _bf16 / _glu_bf16 called one by one.
  *
  * One problem of a group; all pointers are device pointers, all problems share the token count M of the group. */
 typedef struct q27b_group_problem {
@@ -171,6 +171,12 @@ typedef struct q27b_group_problem {
   const float* c;      /* residual [M][N] (fp32 epilogue only; may alias d) or null */
   void* d;             /* output */
 } q27b_group_problem;
+/* flags of q27b_skinny_group_build. WHOLE_TILES: no tile is cut along K. A group with many tiles (several layers) fills
+ * the GPU evenly without the K split, writes no partial tiles and sums nothing - the fastest form at every M. Every
+ * output is then one accumulation chain over all of K, so the results are bit-identical to the many-row GEMM
+ * (q27b_gemm_fp4 / _bf16 / _glu_bf16) rather than to the weight-streaming launch. With few tiles (one layer) the
+ * CTAs are loaded unevenly; the table's header reports the imbalance, and the default mode is the better choice. */
+#define Q27B_GROUP_WHOLE_TILES 1
 /* Plans the group for 1 <= M <= 128 on the current device and writes its table: tensor maps of every operand, and
  * for every CTA the pieces {problem, weight tile, K range} it streams, longest piece first onto the least loaded
  * CTA, walked in problem order. HOST function, called once per (problem list, M): `problems` and `table_host` are
@@ -178,8 +184,8 @@ typedef struct q27b_group_problem {
  * table_host to 128-byte aligned device memory (a plain cudaMemcpy) and keeps both copies for the launches. ws_bytes:
  * the workspace the launches need, zeroed once by the caller (arrival counters at its head, which every launch
  * leaves at zero; after a launch that reported a timed-out wait, zero it again). */
-int q27b_skinny_group_build(int M, int n_problems, const q27b_group_problem* problems, void* table_host, size_t table_cap,
-                            size_t* table_bytes, size_t* ws_bytes);
+int q27b_skinny_group_build(int M, int n_problems, const q27b_group_problem* problems, int flags, void* table_host,
+                            size_t table_cap, size_t* table_bytes, size_t* ws_bytes);
 /* Enqueues the group on `stream`: one launch, nothing allocated or copied (capturable after one eager call per
  * token-tile size and device). Operands, weights and the table must be complete before the kernel that precedes
  * this one in the stream STARTS (see "programmatic dependent launch" above), except the activations, which may be

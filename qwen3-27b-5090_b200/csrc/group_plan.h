@@ -11,6 +11,13 @@
 // (`rotate`: every CTA starts at a different point of its list instead; kept for experiments only - it spreads the
 // pieces of a tile over the whole run of the kernel.)
 //
+// Whole-tile mode. A group with many tiles (several layers) does not need the K split at all: uncut tiles of all
+// problems fill the CTAs evenly by themselves (one layer: 408 tiles of 20 or 68 stages on 296 CTAs does not; eight
+// layers do). No partial tiles are written, nothing is summed. Every output is then one accumulation chain over all
+// of K, which is what the many-row GEMM computes: the results are bit-identical to q27b_gemm_fp4 / _bf16 / _glu_bf16
+// instead of to the weight-streaming launch (whose three K-split shapes add their parts in another order). Both
+// modes are deterministic and independent of M.
+//
 // Host-only code (no CUDA): shared by the launcher and the CPU tests.
 #pragma once
 
@@ -50,12 +57,19 @@ struct GroupSchedule {
   std::vector<int64_t> cta_units;  // units (stages) CTA g streams
   int64_t slots = 0;               // partial-tile slots the workspace must hold
   int counters = 0;                // arrival counters (one per cut tile)
+  // stages of the busiest CTA over the mean: 1 = perfectly even (whole tiles of few problems can be far from it)
+  double imbalance() const {
+    int64_t most = 0, total = 0;
+    for (int64_t u : cta_units) most = u > most ? u : most, total += u;
+    return total ? double(most) * double(cta_units.size()) / double(total) : 1.0;
+  }
 };
 
 // The pieces of one problem exactly as its stand-alone launch cuts them, in (tile, K) order.
-inline void problem_pieces(int prob, const GroupShape& s, int cta_slots, int64_t& next_slot, int& next_counter,
-                           std::vector<GroupItem>& out) {
-  const SkinnyPlan plan = choose_skinny_plan(s.N, s.K, cta_slots);
+inline void problem_pieces(int prob, const GroupShape& s, int cta_slots, bool whole_tiles, int64_t& next_slot,
+                           int& next_counter, std::vector<GroupItem>& out) {
+  SkinnyPlan plan = choose_skinny_plan(s.N, s.K, cta_slots);
+  if (whole_tiles) plan.split = 1, plan.grid = plan.tiles < cta_slots ? plan.tiles : cta_slots;  // every tile in one piece
   std::vector<GroupItem> pieces;
   for (int g = 0; g < plan.grid; g++) {
     int64_t u = -1;
@@ -90,12 +104,12 @@ inline void problem_pieces(int prob, const GroupShape& s, int cta_slots, int64_t
 }
 
 // Deals the pieces of all problems to at most `cta_slots` CTAs (the CTAs that can be resident at once).
-inline GroupSchedule schedule_group(const GroupShape* shapes, int n, int cta_slots, bool rotate = false) {
+inline GroupSchedule schedule_group(const GroupShape* shapes, int n, int cta_slots, bool whole_tiles = false, bool rotate = false) {
   GroupSchedule sch;
   std::vector<GroupItem> all;
   int64_t next_slot = 0;
   int next_counter = 0;
-  for (int p = 0; p < n; p++) problem_pieces(p, shapes[p], cta_slots, next_slot, next_counter, all);
+  for (int p = 0; p < n; p++) problem_pieces(p, shapes[p], cta_slots, whole_tiles, next_slot, next_counter, all);
   sch.slots = next_slot, sch.counters = next_counter;
   const int ctas = int(std::min<size_t>(size_t(cta_slots), all.size()));
   // longest piece first onto the CTA with the least to stream (ties: the lower index)

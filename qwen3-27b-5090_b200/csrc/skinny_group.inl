@@ -31,7 +31,9 @@ struct GroupHeader {  // the first 128 bytes of the table
   uint32_t magic;
   int M, nb, n_problems, n_ctas, n_items, counters, sms;
   int64_t slots, off_problems, off_cta_first, off_cta_units, off_items, table_bytes, ws_bytes;
-  int64_t pad[5];
+  int imbalance_permille;  // stages of the busiest CTA over the mean, in thousandths (1000 = perfectly even)
+  int pad32;
+  int64_t pad[4];
 };
 static_assert(sizeof(GroupHeader) == 128, "GroupHeader layout");
 

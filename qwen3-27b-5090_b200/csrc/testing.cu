@@ -88,7 +88,7 @@ int q27b_skinny_tile_parts(int N, int K, int slots, int tile, int* slot, int cap
   return t.n;
 }
 
-int q27b_skinny_group_plan(int n, const int* N, const int* K, int slots, int rotate, int* pieces, int cap, int* ctas_out,
+int q27b_skinny_group_plan(int n, const int* N, const int* K, int slots, int whole_tiles, int rotate, int* pieces, int cap, int* ctas_out,
                            int64_t* slots_out, int* counters_out) {
   if (n <= 0 || !N || !K || slots <= 0) return fail("skinny_group_plan: bad arguments");
   std::vector<GroupShape> shapes(n);
@@ -96,7 +96,7 @@ int q27b_skinny_group_plan(int n, const int* N, const int* K, int slots, int rot
     if (N[i] <= 0 || N[i] % 128 || K[i] <= 0 || K[i] % 64) return fail("skinny_group_plan: bad shape");
     shapes[i] = {N[i], K[i]};
   }
-  const GroupSchedule sch = schedule_group(shapes.data(), n, slots, rotate != 0);
+  const GroupSchedule sch = schedule_group(shapes.data(), n, slots, whole_tiles != 0, rotate != 0);
   if (ctas_out) *ctas_out = int(sch.cta_units.size());
   if (slots_out) *slots_out = sch.slots;
   if (counters_out) *counters_out = sch.counters;

@@ -1305,8 +1305,9 @@ int q27b_trace_set(void* buf) {
 
 // ---- the grouped weight-streaming GEMM ------------------------------------------------------------------------------
 
-int q27b_skinny_group_build(int M, int n_problems, const q27b_group_problem* problems, void* table_host, size_t table_cap,
-                            size_t* table_bytes, size_t* ws_bytes) {
+int q27b_skinny_group_build(int M, int n_problems, const q27b_group_problem* problems, int flags, void* table_host,
+                            size_t table_cap, size_t* table_bytes, size_t* ws_bytes) {
+  Q27B_REQUIRE((flags & ~Q27B_GROUP_WHOLE_TILES) == 0, "skinny_group: unknown flags 0x%x", flags);
   Q27B_REQUIRE(M >= 1 && M <= 128, "skinny_group: M must be 1..128 (M = %d)", M);
   Q27B_REQUIRE(n_problems >= 1 && n_problems <= kGroupMaxProblems && problems, "skinny_group: 1..%d problems", kGroupMaxProblems);
   const int sms = sm_count();
@@ -1316,11 +1317,12 @@ int q27b_skinny_group_build(int M, int n_problems, const q27b_group_problem* pro
     if (int rc = check_group_problem(i, problems[i])) return rc;
     shapes[i] = {problems[i].N, problems[i].K};
   }
-  const GroupSchedule sch = schedule_group(shapes.data(), n_problems, 2 * sms);
+  const GroupSchedule sch = schedule_group(shapes.data(), n_problems, 2 * sms, (flags & Q27B_GROUP_WHOLE_TILES) != 0);
   const int ctas = int(sch.cta_units.size());
   GroupHeader h = {};
   h.magic = kGroupMagic, h.M = M, h.nb = group_tokens_tile(M), h.n_problems = n_problems, h.n_ctas = ctas;
   h.n_items = int(sch.items.size()), h.counters = sch.counters, h.sms = sms, h.slots = sch.slots;
+  h.imbalance_permille = int(sch.imbalance() * 1000.0 + 0.5);
   h.off_problems = sizeof(GroupHeader);
   h.off_cta_first = h.off_problems + int64_t(n_problems) * sizeof(GroupProblemDev);
   h.off_cta_units = align_up(h.off_cta_first + int64_t(ctas + 1) * 4, 16);

@@ -15,6 +15,7 @@ import torch
 from .q27lib import call
 
 EPI_F32, EPI_BF16, EPI_GLU_BF16 = 0, 1, 2
+WHOLE_TILES = 1  # Q27B_GROUP_WHOLE_TILES
 
 
 class GroupProblem(ctypes.Structure):
@@ -51,17 +52,22 @@ class Fp4Group:
     """A planned group: the table on the host and on the device, and its workspace. `problems` is a list of
     GroupProblem; the tensors they point to must stay alive (and in place) as long as the group is used."""
 
-    def __init__(self, M: int, problems: list[GroupProblem], device="cuda", workspace: torch.Tensor | None = None):
+    def __init__(self, M: int, problems: list[GroupProblem], device="cuda", workspace: torch.Tensor | None = None,
+                 whole_tiles: bool = False):
+        """whole_tiles: no tile is cut along K (for groups of several layers: fastest, and bit-identical to the
+        many-row GEMM instead of to the weight-streaming launch)."""
         self.M, self.n = M, len(problems)
+        flags = WHOLE_TILES if whole_tiles else 0
         arr = (GroupProblem * self.n)(*problems)
         tb, wb = ctypes.c_size_t(), ctypes.c_size_t()
-        call("q27b_skinny_group_build", M, self.n, arr, None, 0, ctypes.byref(tb), ctypes.byref(wb))
+        call("q27b_skinny_group_build", M, self.n, arr, flags, None, 0, ctypes.byref(tb), ctypes.byref(wb))
         self.table_host = (ctypes.c_uint8 * tb.value)()
-        call("q27b_skinny_group_build", M, self.n, arr, self.table_host, tb.value, ctypes.byref(tb), ctypes.byref(wb))
+        call("q27b_skinny_group_build", M, self.n, arr, flags, self.table_host, tb.value, ctypes.byref(tb), ctypes.byref(wb))
         self.table_bytes, self.ws_bytes = tb.value, max(wb.value, 256)
         # header of the table (GroupHeader, csrc/skinny_group.inl): what was planned
         (_, _, self.tokens_tile, _, self.ctas, self.pieces, self.counters, self.sms, self.slots) = struct.unpack_from("<I7iq", self.table_host)
         self.partials_offset = (self.counters * 4 + 255) // 256 * 256  # arrival counters first, then the partial tiles
+        self.imbalance = struct.unpack_from("<i", self.table_host, 4 + 7 * 4 + 7 * 8)[0] / 1000.0  # busiest CTA over the mean
         host = torch.frombuffer(self.table_host, dtype=torch.uint8)
         self.table_dev = host.to(device)  # torch's device allocations are at least 256-byte aligned
         if workspace is None:

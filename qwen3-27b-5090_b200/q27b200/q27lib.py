@@ -40,7 +40,7 @@ SIGNATURES = {
     "q27b_skinny_fp4_glu_bf16": ([I, I, I, P, P, P, P, F, F, P, P, SZ, P], I),
     "q27b_skinny_fp4_static": ([I, I, I, P, P, P, P, I, P, P, P, F, P, P], I),
     "q27b_skinny_workspace_bytes": ([I, I, I], I64),
-    "q27b_skinny_group_build": ([I, I, P, P, SZ, P, P], I),
+    "q27b_skinny_group_build": ([I, I, P, I, P, SZ, P, P], I),
     "q27b_skinny_fp4_group": ([P, P, P, SZ, P], I),
     "q27t_skinny_fp4_group": ([P, P, P, SZ], I),
     "q27b_gemm_fp4": ([I, I, I, P, P, P, P, F, P, F, P, P], I),
@@ -79,7 +79,7 @@ TEST_LIB_PATH = os.path.join(HERE, "libq27b200_test.so")
 TEST_SIGNATURES = {
     "q27b_skinny_plan": ([I, I, I, I, P, I, P, P, P], I),
     "q27b_skinny_tile_parts": ([I, I, I, I, P, I], I),
-    "q27b_skinny_group_plan": ([I, P, P, I, I, P, I, P, P, P], I),
+    "q27b_skinny_group_plan": ([I, P, P, I, I, I, P, I, P, P, P], I),
     "q27t_ref_gemm_fp4": ([I, I, I, P, P, P, P, F, P], I),
     "q27t_cxx_launchers": ([P, I, I, F, P, P, I, P, P, I, P, P, P, P, SZ, I, P, P, F, F, F, P, P], I),
     "q27t_cxx_throws": ([], I),

@@ -160,3 +160,40 @@ def test_group_rejects_bad_arguments():
     small = torch.zeros(64, dtype=torch.uint8, device=DEV)
     with pytest.raises(RuntimeError, match="workspace too small"):
         call("q27t_skinny_fp4_group", grp.table_host, grp.table_dev, small, small.numel())
+
+
+@pytest.mark.parametrize("M", [1, 16, 128])
+def test_group_of_whole_tiles_equals_the_many_row_gemm(M):
+    """Whole-tile mode (no K split): every output is one accumulation chain over all of K, exactly what the many-row
+    GEMM computes - bit for bit, for every epilogue; a stacked weight with three alphas equals the many-row GEMM of
+    each part with its own alpha. Two layers in one launch."""
+    res = torch.randn(128, 5120, device=DEV)
+    a5, a5sf, _ = operand(128, 5120, 11)
+    a17, a17sf, _ = operand(128, 17408, 12)
+    want = {}
+    w, wsf, _ = operand(7168, 5120, 21)
+    want["qkv"] = torch.empty(M, 7168, device=DEV)
+    for (b, e), al in zip(((0, 5120), (5120, 6144), (6144, 7168)), QKV_ALPHA):
+        part = torch.empty(M, e - b, device=DEV)
+        # rows b..e of the stacked weight: codes and scale atoms of whole 128-row tiles
+        call("q27t_gemm_fp4", M, e - b, 5120, a5, a5sf, w[b:e], wsf[b // 128 * (5120 // 64) * 512:], al, None, 0.0, part)
+        want["qkv"][:, b:e] = part
+    w, wsf, _ = operand(5120, 5120, 22)
+    want["o"] = torch.empty(M, 5120, device=DEV)
+    call("q27t_gemm_fp4", M, 5120, 5120, a5, a5sf, w, wsf, 0.5, res[:M].contiguous(), 1.0, want["o"])
+    w, wsf, _ = operand(34816, 5120, 23)
+    want["gate_up"] = torch.empty(M, 17408, dtype=torch.bfloat16, device=DEV)
+    call("q27t_gemm_fp4_glu_bf16", M, 17408, 5120, a5, a5sf, w, wsf, 0.013, 0.021, want["gate_up"])
+    w, wsf, _ = operand(5120, 17408, 24)
+    want["down"] = torch.empty(M, 5120, dtype=torch.bfloat16, device=DEV)
+    call("q27t_gemm_fp4_bf16", M, 5120, 17408, a17, a17sf, w, wsf, 0.7, want["down"])
+    outs = [fresh_outputs(M) for _ in range(2)]
+    probs = []
+    for got in outs:
+        probs += layer_problems(M, res[:M].contiguous(), got)
+    grp = Fp4Group(M, probs, whole_tiles=True)
+    assert grp.slots == 0 and grp.counters == 0 and grp.pieces == 2 * 408
+    grp.run_sync()
+    for got in outs:
+        for name in want:
+            assert torch.equal(got[name], want[name]), f"{name} differs at M={M}"

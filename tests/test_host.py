@@ -117,14 +117,14 @@ def test_skinny_plan_choices():
     assert plan(248320, 5120, 296)[2] == 0     # lm_head: contiguous ranges (no wave quantisation)
 
 
-def group_plan(shapes, slots, rotate=0):
+def group_plan(shapes, slots, rotate=0, whole=0):
     n = len(shapes)
     Ns, Ks = (ctypes.c_int * n)(*[s[0] for s in shapes]), (ctypes.c_int * n)(*[s[1] for s in shapes])
     ctas, nslots, counters = ctypes.c_int(), ctypes.c_int64(), ctypes.c_int()
     l = scaffold_lib()
-    count = l.q27b_skinny_group_plan(n, Ns, Ks, slots, rotate, None, 0, ctypes.byref(ctas), ctypes.byref(nslots), ctypes.byref(counters))
+    count = l.q27b_skinny_group_plan(n, Ns, Ks, slots, whole, rotate, None, 0, ctypes.byref(ctas), ctypes.byref(nslots), ctypes.byref(counters))
     buf = (ctypes.c_int * (9 * count))()
-    assert l.q27b_skinny_group_plan(n, Ns, Ks, slots, rotate, buf, count, None, None, None) == count
+    assert l.q27b_skinny_group_plan(n, Ns, Ks, slots, whole, rotate, buf, count, None, None, None) == count
     pieces = [tuple(buf[9 * i:9 * i + 9]) for i in range(count)]
     return ctas.value, nslots.value, counters.value, pieces
 
@@ -285,3 +285,22 @@ def test_gathered_layout_to_row_major():
     per = n_out // world
     gathered = np.stack([full[:, r * per:(r + 1) * per] for r in range(world)])  # what all_gather yields
     assert np.array_equal(shard.gathered_to_row_major(torch.from_numpy(gathered)).numpy(), full)
+
+
+def test_group_schedule_whole_tiles():
+    """Whole-tile mode: every tile is one piece, nothing is cut, no slots or counters; eight layers fill 296 CTAs
+    evenly, one layer does not (its down-projection tiles are 68 stages long)."""
+    ctas, nslots, counters, pieces = group_plan(LAYER_SHAPES * 8, 296, whole=1)
+    assert nslots == 0 and counters == 0 and len(pieces) == 8 * 408
+    assert all(p[5] == -1 and p[6] == 1 and p[8] == 0 and p[3] == 0 for p in pieces)
+    chunks = {i: (K + 255) // 256 for i, (N, K) in enumerate(LAYER_SHAPES * 8)}
+    assert all(p[4] == chunks[p[1]] for p in pieces)
+    loads = np.zeros(ctas, dtype=np.int64)
+    for p in pieces:
+        loads[p[0]] += p[4] - p[3]
+    assert loads.sum() == 8 * 10080 and loads.max() <= 1.07 * loads.mean()  # (a piece is 20 or 68 stages: 272 +- 16)
+    ctas, _, _, pieces = group_plan(LAYER_SHAPES, 296, whole=1)
+    loads = np.zeros(ctas, dtype=np.int64)
+    for p in pieces:
+        loads[p[0]] += p[4] - p[3]
+    assert loads.max() == 68 and loads.max() > 1.9 * loads.sum() / 296

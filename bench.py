@@ -20,8 +20,11 @@ inputs resident in HBM, exactly K steps replayed from a CUDA graph and timed wit
   "verified": after every timed region the outputs left by the LAST timed step are compared bit for bit with the
              same step run one kernel at a time (device synchronised in between, programmatic launch off).
 
-With N > 1 GPUs the weight rows are sharded N ways (no reduction anywhere); the step then ends with ONE NCCL
-all-gather of all outputs of the sweep (captured in the same graph), and `value` includes it.
+With N > 1 GPUs the weight rows are sharded N ways (no reduction anywhere) and every step ends with every rank
+holding every rank's outputs: by default the grouped launch stores its outputs into all peers' memory from its
+epilogue (plain peer stores overlapping the weight stream, then a wait for the peers' signals; --gather nccl: one NCCL
+all-gather after the launch instead). Either way the gather is inside the timed graph and inside `value`; the figures
+without it and with the other way are reported beside it.
 
 --impl reference times the CPU restatement of the reference's own path (fake-quantise, fp32 matmul against the
 once-dequantised weight, SiLU*mul) on the host cores for the same workload, on a bounded sample of it.
@@ -245,15 +248,24 @@ def build_model(layers_n, rank, world):
 
 
 class Sweep:
-    """One token count of the sweep: inputs, per-layer quantised activations and outputs, and the launch sequences."""
+    """One token count of the sweep: inputs, per-layer quantised activations and outputs, and the launch sequences.
+
+    gather (several GPUs): "fused" - the grouped launch stores every output into all peers' memory as well (plain
+    peer stores from its epilogue, overlapping the weight stream) and a one-warp kernel behind it waits for the peers'
+    signals; "nccl" - one NCCL all-gather of all outputs after the launches. Either way the step ends with every rank
+    holding every rank's block of the outputs, rank-major ([rank][layer][M x columns of the rank]). With the fused
+    gather the outputs alternate between two buffers from step to step: a rank may start its next step while a peer
+    still reads the previous one's."""
 
     NAMES = ("qkv", "o", "gate_up", "down")
 
-    def __init__(self, model, M, world):
+    def __init__(self, model, M, world, gather="nccl"):
         from q27b200 import configs
         from q27b200.linear import ActQuant
 
         self.model, self.M, self.world, self.L = model, M, world, len(model)
+        self.rank = torch.distributed.get_rank() if world > 1 else 0
+        self.fused = world > 1 and gather == "fused"
         gx = torch.Generator().manual_seed(3)
         self.x_host = {"h": torch.randn(M, configs.HIDDEN, generator=gx).to(torch.bfloat16).pin_memory(),
                        "o": torch.randn(M, configs.HIDDEN, generator=gx).to(torch.bfloat16).pin_memory(),
@@ -265,18 +277,33 @@ class Sweep:
         self.act = [{k: ActQuant(max(M, 128), v.shape[1]) for k, v in self.x.items()} for _ in range(self.L)]
         widths = [model[0][n].out for n in self.NAMES]
         self.width = sum(widths)
-        self.out_all = torch.zeros(self.L, M * self.width, dtype=torch.bfloat16, device="cuda")
+        block = self.L * M * self.width  # bf16 elements one rank contributes
+        if self.fused:
+            from q27b200.peer import PeerRegion
+
+            self.region = PeerRegion(2 * world * block * 2)
+            pay = self.region.payload()[:2 * world * block * 2].view(torch.bfloat16).view(2, world, block)
+            self.gathered = [pay[0], pay[1]]
+            self.out_all = [pay[b][self.rank].view(self.L, M * self.width) for b in range(2)]
+            self.peers = self.region.peers()
+            self.wait_slots = (ctypes.c_int * (world - 1))(*self.region.peer_slots())
+        else:
+            self.out_all = [torch.zeros(self.L, M * self.width, dtype=torch.bfloat16, device="cuda")]
+            self.gathered = [torch.empty(world, block, dtype=torch.bfloat16, device="cuda")] if world > 1 else [None]
         self.outs = []
-        for l in range(self.L):
-            o, off = {}, 0
-            for n, wd in zip(self.NAMES, widths):
-                o[n] = self.out_all[l, off:off + M * wd].view(M, wd)
-                off += M * wd
-            self.outs.append(o)
+        for oa in self.out_all:
+            per_layer = []
+            for l in range(self.L):
+                o, off = {}, 0
+                for n, wd in zip(self.NAMES, widths):
+                    o[n] = oa[l, off:off + M * wd].view(M, wd)
+                    off += M * wd
+                per_layer.append(o)
+            self.outs.append(per_layer)
         for layer in model:
             for n, lin in layer.items():
                 lin.set_in_scale(self.scale[self.src[n]])
-        self.gathered = torch.empty(world, self.out_all.numel(), dtype=torch.bfloat16, device="cuda") if world > 1 else None
+        self.last_b = 0
         self._groups = {}
         self._jobs = {}
 
@@ -309,45 +336,62 @@ class Sweep:
         layer keeps the split of the stand-alone launches."""
         return layers >= 8
 
-    def group(self, l0, l1):
+    def group(self, l0, l1, b=0):
         from q27b200.group import Fp4Group, problem_of
 
-        key = (l0, l1)
+        key = (l0, l1, b)
         if key not in self._groups:
             probs = []
             for l in range(l0, l1):
                 for n in self.NAMES:
                     a = self.act[l][self.src[n]]
-                    probs.append(problem_of(self.model[l][n], a.q, a.sf, self.outs[l][n]))
+                    probs.append(problem_of(self.model[l][n], a.q, a.sf, self.outs[b][l][n]))
             self._groups[key] = Fp4Group(self.M, probs, whole_tiles=self.whole_tiles(l1 - l0))
         return self._groups[key]
 
     def drop_groups(self):
         self._groups.clear()
 
-    def step_grouped(self, G):
+    def step_grouped(self, G, i=0, gather=True):
+        from q27b200.q27lib import call
+
+        b = self.last_b = i % len(self.out_all)
+        launches = 0
         for l0 in range(0, self.L, G):
             l1 = min(l0 + G, self.L)
             self.quantise(l0, l1)
-            self.group(l0, l1).launch()
-        self.gather()
+            if self.fused and gather:
+                self.group(l0, l1, b).launch_gather(self.peers)
+            else:
+                self.group(l0, l1, b).launch()
+            launches += 1
+        if self.fused and gather:  # one wait per launch: each launch raises this rank's word in every peer once
+            for _ in range(launches):
+                call("q27b_group_gather_wait", self.region.ptrs[self.rank], self.world - 1, self.wait_slots,
+                     torch.cuda.current_stream().cuda_stream)
+        elif gather:
+            self.gather(b)
 
-    def step_per_gemm(self):
+    def step_per_gemm(self, i=0):
+        b = self.last_b = i % len(self.out_all)
         for l in range(self.L):
             self.quantise(l, l + 1)
             for n in self.NAMES:
                 a = self.act[l][self.src[n]]
-                self.model[l][n].gemm(self.M, a.q, a.sf, self.outs[l][n])
-        self.gather()
+                self.model[l][n].gemm(self.M, a.q, a.sf, self.outs[b][l][n])
+        self.gather(b)
 
-    def gather(self):
+    def gather(self, b=0):
         if self.world > 1:  # the one collective of the path: every rank's block of output columns, all layers at once
-            torch.distributed.all_gather_into_tensor(self.gathered.view(-1), self.out_all.view(-1))
+            assert not self.fused, "the NCCL gather writes into a buffer of its own"
+            torch.distributed.all_gather_into_tensor(self.gathered[b].view(-1), self.out_all[b].view(-1))
 
     def launches_per_step(self, G):
         # per GEMM: the quantiser, four GEMMs and, above 8 tokens, the fix-up kernel of the three weights that are cut along K
         n = self.L * (1 + len(self.NAMES) + (3 if self.M > 8 else 0)) if G == 0 else 2 * math.ceil(self.L / G)
-        return n + (1 if self.world > 1 else 0)
+        if self.world > 1:
+            n += math.ceil(self.L / max(G, 1)) if self.fused else 1  # the wait kernels / the collective
+        return n
 
     # -- checking ----------------------------------------------------------------------------------------------------
 
@@ -367,13 +411,22 @@ class Sweep:
             if lin._nseg > 1:
                 out[:, b:e] = part
 
-    def verify(self, G):
+    def verify(self, G, gathered=True):
         """The outputs the last timed step left behind, against the same step run one kernel at a time through the
         per-GEMM entry points: the weight-streaming launch, or - for groups planned without the K split, whose sums
-        run over all of K in one chain - the many-row GEMM."""
-        got = self.out_all.clone()
-        gathered = self.gathered.clone() if self.gathered is not None else None
-        self.out_all.zero_()
+        run over all of K in one chain - the many-row GEMM. On several GPUs every rank also checks the other ranks'
+        blocks it received against an all-gather of those one-kernel-at-a-time results."""
+        b = self.last_b
+        got = self.out_all[b].clone()
+        got_all = self.gathered[b].clone() if (self.world > 1 and gathered) else None
+        want = torch.zeros_like(got)
+        wouts, widths = [], [self.model[0][n].out for n in self.NAMES]
+        for l in range(self.L):
+            o, off = {}, 0
+            for n, wd in zip(self.NAMES, widths):
+                o[n] = want[l, off:off + self.M * wd].view(self.M, wd)
+                off += self.M * wd
+            wouts.append(o)
         whole = G > 0 and self.whole_tiles(min(G, self.L))
         with serial_launches():
             for l in range(self.L):
@@ -383,14 +436,16 @@ class Sweep:
                     a.quantize(self.x[k], self.scale[k])
                     torch.cuda.synchronize()
                     if whole:
-                        self._many_row(self.model[l][n], a, self.outs[l][n])
+                        self._many_row(self.model[l][n], a, wouts[l][n])
                     else:
-                        self.model[l][n].gemm(self.M, a.q, a.sf, self.outs[l][n])
+                        self.model[l][n].gemm(self.M, a.q, a.sf, wouts[l][n])
                     torch.cuda.synchronize()
-        ok = bool(torch.equal(got, self.out_all)) and bool(torch.isfinite(got.float()).all()) and bool(got.any())
-        if gathered is not None:
-            r = torch.distributed.get_rank()
-            ok = ok and bool(torch.equal(gathered[r], self.out_all.view(-1)))
+        ok = bool(torch.equal(got, want)) and bool(torch.isfinite(got.float()).all()) and bool(got.any())
+        if self.world > 1:
+            if got_all is not None:
+                ref_all = torch.empty_like(got_all)
+                torch.distributed.all_gather_into_tensor(ref_all.view(-1), want.view(-1))
+                ok = ok and bool(torch.equal(got_all, ref_all))
             flag = torch.tensor([int(ok)], device="cuda")
             torch.distributed.all_reduce(flag, op=torch.distributed.ReduceOp.MIN)
             ok = bool(flag.item())
@@ -405,91 +460,100 @@ def run_sweep(args, model, rank, world, local_rank, peaks):
     G = min(args.group_layers, L)
     ms_list = list(configs.SWEEP_M) if args.m == 0 else [args.m]
     head_m = 16 if 16 in ms_list else ms_list[0]
+    gather = args.gather if world > 1 else "none"
+    cap = 4 if world > 1 else 5  # steps per captured graph (even on several GPUs: the output buffers alternate)
     sweep, modes, verified, head = {}, {}, True, None
+
+    def rate(nbytes, ms):
+        per = ms / args.steps
+        return {"gbs": nbytes / per / 1e6, "ms_per_sweep": per, "frac": nbytes / per / 1e6 / world / peaks["hbm_gbs"]}
+
     for M in ms_list:
-        sw = Sweep(model, M, world)
+        sw = Sweep(model, M, world, gather)
         nbytes = configs.sweep_algorithmic_bytes(M, L)
+        mode = f"grouped, {G} layer(s) per launch" + (", whole tiles" if sw.whole_tiles(G) else "")
+        if world > 1:
+            mode += ", gather fused into the epilogue (peer stores)" if sw.fused else ", NCCL all-gather"
         if M == head_m:
             with ClockSampler(local_rank) as clk:  # covers the warm-up steps, the capture and the K timed steps
-                ms = timed(lambda i: sw.step_grouped(G), args.steps, args.warmup, world, graph_cap=5)
+                ms = timed(lambda i: sw.step_grouped(G, i), args.steps, args.warmup, world, graph_cap=cap)
             clocks = clk.summary()
         else:
-            ms = timed(lambda i: sw.step_grouped(G), args.steps, args.warmup, world, graph_cap=5)
+            ms = timed(lambda i: sw.step_grouped(G, i), args.steps, args.warmup, world, graph_cap=cap)
         ok = sw.verify(G)
         verified = verified and ok
-        per = ms / args.steps
-        sweep[str(M)] = {"gbs": nbytes / per / 1e6, "ms_per_sweep": per, "frac": nbytes / per / 1e6 / world / peaks["hbm_gbs"],
-                         "mode": f"grouped, {G} layer(s) per launch" + (", whole tiles" if sw.whole_tiles(G) else ""), "verified": ok}
-        if M > 16:
-            # many tokens: a cut tile is summed by the one CTA that delivers its last piece, which costs the grouped
-            # launch more than its saved launch boundaries; the per-GEMM form (fix-up kernel over the whole GPU) is
-            # timed as well and the faster of the two is reported, by name
+        sweep[str(M)] = dict(rate(nbytes, ms), mode=mode, verified=ok)
+        if M > 16 and world == 1:
+            # many tokens: the per-GEMM form is timed as well and the faster of the two is reported, by name
             sw.drop_groups()
-            ms2 = timed(lambda i: sw.step_per_gemm(), args.steps, args.warmup, world, graph_cap=5)
+            ms2 = timed(lambda i: sw.step_per_gemm(i), args.steps, args.warmup, world, graph_cap=cap)
             ok2 = sw.verify(0)
             verified = verified and ok2
             sweep[str(M)]["grouped_gbs"] = sweep[str(M)]["gbs"]
-            sweep[str(M)]["per_gemm_gbs"] = nbytes / (ms2 / args.steps) / 1e6
+            sweep[str(M)]["per_gemm_gbs"] = rate(nbytes, ms2)["gbs"]
             if ms2 < ms:
-                per = ms2 / args.steps
-                sweep[str(M)].update({"gbs": nbytes / per / 1e6, "ms_per_sweep": per, "frac": nbytes / per / 1e6 / world / peaks["hbm_gbs"],
-                                      "mode": "per GEMM (one launch per projection, programmatic dependent launch)", "verified": ok2})
+                sweep[str(M)].update(dict(rate(nbytes, ms2), mode="per GEMM (one launch per projection, programmatic dependent launch)",
+                                          verified=ok2))
         log(f"sweep M={M}: {sweep[str(M)]}")
         if M == head_m:
             head = dict(sweep[str(M)], clocks=clocks, bytes=nbytes)
-            # the same sweep in the other launch forms
-            for name, g in (("per_gemm", 0), ("group_1_layer", 1), ("group_4_layers", 4), ("group_8_layers", 8), ("group_64_layers", 64)):
-                if g > L or (g == G):
-                    continue
-                sw.drop_groups()
-                fn = (lambda i: sw.step_per_gemm()) if g == 0 else (lambda i, g=g: sw.step_grouped(g))
-                ms_mode = timed(fn, args.steps, args.warmup, world, graph_cap=5)
-                ok = sw.verify(g)
-                verified = verified and ok
-                modes[name] = {"gbs": nbytes / (ms_mode / args.steps) / 1e6, "ms_per_sweep": ms_mode / args.steps,
-                               "launches_per_sweep": sw.launches_per_step(g), "verified": ok}
-                log(f"mode {name}: {modes[name]}")
-            modes[f"group_{G}_layer{'s' if G > 1 else ''}"] = {"gbs": head["gbs"], "ms_per_sweep": head["ms_per_sweep"],
-                                                                 "launches_per_sweep": sw.launches_per_step(G), "verified": head["verified"]}
-            if world > 1:  # the same steps without the collective, for the cost of the gather
-                def step_no_gather(i):
-                    for l0 in range(0, L, G):
-                        sw.quantise(l0, min(l0 + G, L))
-                        sw.group(l0, min(l0 + G, L)).launch()
-                ms_ng = timed(step_no_gather, args.steps, args.warmup, world, graph_cap=5)
-                head["without_allgather"] = {"gbs": nbytes / (ms_ng / args.steps) / 1e6, "ms_per_sweep": ms_ng / args.steps}
+            modes[f"group_{G}_layer{'s' if G > 1 else ''}"] = dict(rate(nbytes, ms), launches_per_sweep=sw.launches_per_step(G), verified=ok)
+            if world == 1:  # the same sweep in the other launch forms
+                for name, g in (("per_gemm", 0), ("group_1_layer", 1), ("group_4_layers", 4), ("group_8_layers", 8), ("group_64_layers", 64)):
+                    if g > L or (g == G):
+                        continue
+                    sw.drop_groups()
+                    fn = (lambda i: sw.step_per_gemm(i)) if g == 0 else (lambda i, g=g: sw.step_grouped(g, i))
+                    ms_mode = timed(fn, args.steps, args.warmup, world, graph_cap=cap)
+                    okm = sw.verify(g)
+                    verified = verified and okm
+                    modes[name] = dict(rate(nbytes, ms_mode), launches_per_sweep=sw.launches_per_step(g), verified=okm)
+                    log(f"mode {name}: {modes[name]}")
+            else:  # the cost of the gather: the same steps without it, and with the other way of gathering
+                ms_ng = timed(lambda i: sw.step_grouped(G, i, gather=False), args.steps, args.warmup, world, graph_cap=cap)
+                head["without_gather"] = rate(nbytes, ms_ng)
+                log(f"without gather: {head['without_gather']}")
+                other = "nccl" if sw.fused else None
+                if other:
+                    sw2 = Sweep(model, M, world, other)
+                    ms_o = timed(lambda i: sw2.step_grouped(G, i), args.steps, args.warmup, world, graph_cap=cap)
+                    oko = sw2.verify(G)
+                    verified = verified and oko
+                    head["with_nccl_all_gather"] = dict(rate(nbytes, ms_o), verified=oko)
+                    log(f"with NCCL all-gather: {head['with_nccl_all_gather']}")
+                    del sw2
             # the same K steps after 0.4 s of uninterrupted replays: streaming at this rate runs into the board's power cap
             # (sw_power_cap, SM clock down to 1.5-1.7 GHz), which a long-running decode loop would see
             with ClockSampler(local_rank) as clk:
-                ms_sus = timed(lambda i: sw.step_grouped(G), args.steps, args.warmup, world, graph_cap=5, busy_ms=400.0)
-            head["sustained"] = {"gbs": nbytes / (ms_sus / args.steps) / 1e6, "ms_per_sweep": ms_sus / args.steps,
-                                 "frac": nbytes / (ms_sus / args.steps) / 1e6 / world / peaks["hbm_gbs"], "clocks": clk.summary(),
-                                 "how": "the K timed steps directly after 0.4 s of back-to-back replays of the same graph"}
-            sw.drop_groups()
+                ms_sus = timed(lambda i: sw.step_grouped(G, i), args.steps, args.warmup, world, graph_cap=cap, busy_ms=400.0)
+            head["sustained"] = dict(rate(nbytes, ms_sus), clocks=clk.summary(),
+                                     how="the K timed steps directly after 0.4 s of back-to-back replays of the same graph")
             # end to end from host buffers: activations in from pinned host memory, the last layer's outputs back out
-            y_host = torch.empty(M * sw.width, dtype=torch.bfloat16).pin_memory()
+            y_host = [torch.empty(M * sw.width, dtype=torch.bfloat16).pin_memory() for _ in range(len(sw.out_all))]
+
+            def last_layer(bb):  # the last layer's outputs as the step leaves them (on several GPUs: rank 0's block)
+                return sw.gathered[bb][0][-M * sw.width:] if world > 1 else sw.out_all[bb][L - 1]
 
             def step_e2e(i):
                 for k in ("h", "o", "d"):
                     sw.x[k].copy_(sw.x_host[k], non_blocking=True)
-                sw.step_grouped(G)
-                src = sw.gathered[0][-M * sw.width:] if world > 1 else sw.out_all[L - 1]
-                y_host.copy_(src, non_blocking=True)
+                sw.step_grouped(G, i)
+                y_host[sw.last_b].copy_(last_layer(sw.last_b), non_blocking=True)
 
-            ms_e2e = timed(step_e2e, args.steps, args.warmup, world, graph_cap=5)
-            ok = sw.verify(G) and bool(torch.equal(y_host.cuda(), (sw.gathered[0][-M * sw.width:] if world > 1 else sw.out_all[L - 1])))
-            verified = verified and ok
-            head["e2e"] = {"value": nbytes / (ms_e2e / args.steps) / 1e6, "unit": "GB/s",
+            ms_e2e = timed(step_e2e, args.steps, args.warmup, world, graph_cap=cap)
+            oke = sw.verify(G) and bool(torch.equal(y_host[sw.last_b].cuda(), last_layer(sw.last_b)))
+            verified = verified and oke
+            head["e2e"] = {"value": rate(nbytes, ms_e2e)["gbs"], "unit": "GB/s",
                            "h2d_bytes_per_step": sum(v.numel() * 2 for v in sw.x_host.values()),
-                           "d2h_bytes_per_step": y_host.numel() * 2, "ms_per_step": ms_e2e / args.steps, "verified": ok,
+                           "d2h_bytes_per_step": y_host[0].numel() * 2, "ms_per_step": ms_e2e / args.steps, "verified": oke,
                            "how": "per step: the three bf16 activations pinned host -> device, the sweep (quantisers + grouped "
-                                  "GEMM" + (" + all-gather" if world > 1 else "") + "), the last layer's outputs device -> pinned "
+                                  "GEMM" + (" + gather" if world > 1 else "") + "), the last layer's outputs device -> pinned "
                                   "host; all on the launching stream, replayed from a CUDA graph"}
             head["launches"] = sw.launches_per_step(G)
         del sw
         torch.cuda.empty_cache()
     assert device_status() == 0, "a bounded wait inside a kernel ran out"
-    return {"head_m": head_m, "G": G, "sweep": sweep, "modes": modes, "verified": verified, "head": head}
+    return {"head_m": head_m, "G": G, "sweep": sweep, "modes": modes, "verified": verified, "head": head, "gather": gather}
 
 
 # ------------------------------------------------------------------------------------------- single-GEMM configurations
@@ -660,6 +724,8 @@ def main():
     ap.add_argument("--m", type=int, default=0, help="the sweep at this token count only (0: all of 1..128)")
     ap.add_argument("--layers", type=int, default=64, help="layers in the sweep")
     ap.add_argument("--group-layers", type=int, default=64, help="layers per grouped launch in the headline mode")
+    ap.add_argument("--gather", default="fused", choices=["fused", "nccl"],
+                    help="several GPUs: how every rank gets every rank's outputs at the end of a step of the sweep")
     ap.add_argument("--cpu-steps", type=int, default=20)
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg (profiling runs)")
     args = ap.parse_args()
@@ -717,7 +783,9 @@ def main():
                        "step": f"per group of {G} layer(s): one launch quantising the layers' bf16 activations (q27b_quant_fp4_batch), "
                                f"one grouped weight-streaming GEMM over their projections (q27b_skinny_fp4_group"
                                + (", planned without the K split: whole tiles)" if G >= 8 else ")")
-                               + ("; then one NCCL all-gather of all outputs, inside the timed graph" if world > 1 else ""),
+                               + ("" if world == 1 else "; its epilogue stores every output into all peers' memory as well, a "
+                                  "one-warp kernel behind it waits for the peers' signals (inside the timed graph)" if r["gather"] == "fused"
+                                  else "; then one NCCL all-gather of all outputs, inside the timed graph"),
                        "timing": "CUDA-graph replay, CUDA events on the launching stream",
                        "sharding": f"weight rows N-sharded {world} way(s), no reduction"},
             "roofline": {"bound": "hbm", "achieved": h["gbs"] / world, "peak": peaks["hbm_gbs"], "unit": "GB/s",
@@ -727,7 +795,7 @@ def main():
                          "us_per_launch": h["ms_per_sweep"] * 1e3 / math.ceil(args.layers / G),
                          "peak_source": peaks["source"] + ": copy bandwidth"},
             "clocks": h["clocks"], "sustained": h["sustained"], "e2e": h["e2e"], "gpu_launches": args.steps * h["launches"],
-            **({"without_allgather": h["without_allgather"]} if "without_allgather" in h else {}),
+            **{k: h[k] for k in ("without_gather", "with_nccl_all_gather") if k in h},
             "sweep": r["sweep"], "modes": r["modes"]})
     subs = {}
     for idx in (0, 1, 2, 4):

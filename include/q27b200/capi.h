@@ -192,6 +192,28 @@ int q27b_skinny_group_build(int M, int n_problems, const q27b_group_problem* pro
  * written by the preceding kernel. Launches sharing a workspace must not overlap on the GPU. */
 int q27b_skinny_fp4_group(const void* table_host, const void* table_dev, void* ws, size_t ws_bytes, void* stream);
 
+/* ---- the gather fused into the grouped launch (several GPUs, weights sharded along N) -----------------------------
+ *
+ * Every GPU computes its block of output columns and all GPUs need all blocks. Instead of a collective after the
+ * kernel, the epilogue stores every output twice over: into this GPU's memory and, through peer-mapped pointers, into
+ * every peer's (plain stores; no multicast, no load from a peer), so the transfer over NVLink overlaps the weight
+ * stream. All outputs of the group must lie in ONE region of this GPU's memory; the copy of local address x in peer j
+ * is x + out_delta[j]. Each GPU owns a signal block of 16 int32 words in peer-accessible memory, zeroed once: the last
+ * CTA of a launch raises word `my_slot` in every peer's block; q27b_group_gather_wait, enqueued behind the launch,
+ * returns on the device once every listed peer has raised its word for this step (a bounded wait: status 8 if a peer
+ * never reports). The steps of all GPUs must be issued in the same order. No counterpart in the reference (one GPU). */
+typedef struct q27b_group_peers {
+  int n_peers;               /* 1..7 */
+  int my_slot;               /* 0..7: this GPU's word in every signal block (its rank) */
+  int64_t out_delta[7];      /* multiples of 16 */
+  int32_t* signals;          /* this GPU's signal block */
+  int32_t* peer_signals[7];  /* the peers' signal blocks (peer-mapped device pointers) */
+} q27b_group_peers;
+int q27b_skinny_fp4_group_gather(const void* table_host, const void* table_dev, void* ws, size_t ws_bytes,
+                                 const q27b_group_peers* peers, void* stream);
+/* peer_slots: the n_peers slots (0..7) to wait for; HOST array. */
+int q27b_group_gather_wait(int32_t* signals, int n_peers, const int* peer_slots, void* stream);
+
 /* d[m][n] = (A . W^T)[m][n] * (wscale[n] * ascale[m]), fp32: per-output-channel weight scales and per-token
  * activation scales (weights quantised at load, activations quantised dynamically). Replaces skinny_fp4_scaled
  * (engine/src/kernels.h:255-256, engine/src/skinny.cu:402,456,568-572). */

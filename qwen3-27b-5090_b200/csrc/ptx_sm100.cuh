@@ -19,6 +19,7 @@ enum : uint32_t {
   kStatusDrainTimeout = 5,       // a copy in flight did not land during unwinding
   kStatusProbeTimeout = 6,       // the self-test's wait on a barrier nothing arrives at ran out, as it must
   kStatusTileWaitTimeout = 7,    // grouped launch: the pieces of a cut tile never all arrived
+  kStatusPeerWaitTimeout = 8,    // fused gather: a peer GPU never reported its block of the outputs
 };
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) {

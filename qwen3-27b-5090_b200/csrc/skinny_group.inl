@@ -45,6 +45,12 @@ struct GroupLaunch {
   int M;
   int* counters;         // one per cut tile, zero between launches
   float* partials;       // [slots][M][128]
+  // Gather fused into the epilogue (several GPUs): every output store is repeated into the peers' memory, and the
+  // last CTA to finish tells every peer that this GPU's block of the outputs has been written.
+  PeerCopies peers;          // n = 0: single GPU
+  int32_t* signals;          // this GPU's signal block (kSignalWords words; see GatherWait)
+  int32_t* peer_signals[7];  // the peers' signal blocks, in their memory
+  int my_slot;               // the word of a signal block this GPU counts its finished launches in (its rank)
 #ifdef Q27B_TRACE
   unsigned long long* trace;  // [cta][16]: per-role busy / waiting times in ns (null: off)
 #endif
@@ -67,6 +73,7 @@ struct GroupLaunch {
 #define GTRACE_PUT(slot, v)
 #endif
 
+constexpr int kSignalStep = 8, kSignalDone = 9, kSignalWords = 16;  // layout of a signal block (see GatherWait)
 __device__ __forceinline__ int4 ldg16(const void* p) { return __ldg(reinterpret_cast<const int4*>(p)); }
 __device__ __forceinline__ int ld_acquire_gpu(const int* p) {
   int v;
@@ -332,9 +339,9 @@ __global__ void __launch_bounds__((Cfg<NB, STAGES, 2, true>::kThreads), 2) skinn
       dst.wscale = nullptr, e = q->epi;
     };
     auto store = [&](const GemmParams& q, int e, const float(&v)[8], int m0, int tile) {
-      if (e == kEpiGluBf16) store_swapped<kEpiGluBf16>(q, v, m0, tile, row, xchg);
-      else if (e == kEpiBf16) store_swapped<kEpiBf16>(q, v, m0, tile, row, xchg);
-      else store_swapped<kEpiF32>(q, v, m0, tile, row, xchg);
+      if (e == kEpiGluBf16) store_swapped<kEpiGluBf16>(q, v, m0, tile, row, xchg, g.peers);
+      else if (e == kEpiBf16) store_swapped<kEpiBf16>(q, v, m0, tile, row, xchg, g.peers);
+      else store_swapped<kEpiF32>(q, v, m0, tile, row, xchg, g.peers);
     };
     // Has every piece of the oldest queued tile arrived? One thread reads the counter; `wait`: keep reading (bounded).
     auto oldest_complete = [&](bool wait) -> bool {
@@ -502,6 +509,50 @@ __global__ void __launch_bounds__((Cfg<NB, STAGES, 2, true>::kThreads), 2) skinn
     tc_fence_after_sync();
     tmem_dealloc(tmem_base, C::kTmemCols);
   }
+  if (g.peers.n > 0 && threadIdx.x == 0) {
+    // every store of this CTA (local and into the peers) is ordered before the count; the CTA that counts last
+    // orders all of them before it raises this GPU's word in every peer's signal block
+    __threadfence_system();
+    if (atomicAdd(g.signals + kSignalDone, 1) == int(gridDim.x) - 1) {
+      g.signals[kSignalDone] = 0;
+      __threadfence_system();
+      for (int j = 0; j < g.peers.n; j++) atomicAdd_system(g.peer_signals[j] + g.my_slot, 1);
+    }
+  }
+}
+
+// The other half of the fused gather: a one-warp kernel, enqueued behind the grouped launch, that returns once every
+// peer has raised its word in this GPU's signal block for this step, i.e. once the peers' blocks of the outputs have
+// arrived in this GPU's memory. Words 0..7: launches finished by the GPU with that slot (written by the peers);
+// kSignalStep: steps waited for so far (this kernel); kSignalDone: CTAs of the running launch that have finished.
+// The wait is bounded; when it runs out the status word is set (8) and the kernel ends.
+struct GatherWait {
+  int32_t* signals;
+  int n;
+  int slot[7];
+};
+__global__ void group_gather_wait_kernel(const GatherWait w) {
+  const int lane = threadIdx.x;
+  const int step = w.signals[kSignalStep] + 1;
+  bool ok = true;
+  if (lane < w.n) {
+    const volatile int32_t* word = w.signals + w.slot[lane];
+    const long long t0 = clock64();
+    ok = false;
+    for (uint32_t it = 0; it < kMaxPolls; it++) {
+      int v;
+      asm volatile("ld.acquire.sys.global.s32 %0, [%1];" : "=r"(v) : "l"(word) : "memory");
+      if (v - step >= 0) {
+        ok = true;
+        break;
+      }
+      __nanosleep(100);
+      if ((it & 63u) == 63u && clock64() - t0 > kMaxWaitCycles) break;
+    }
+    if (!ok) atomicCAS(&g_status, 0u, uint32_t(kStatusPeerWaitTimeout));
+  }
+  __syncwarp();
+  if (lane == 0) w.signals[kSignalStep] = step;
 }
 
 // ------------------------------------------------------------------------------------------------ host side

@@ -221,10 +221,26 @@ __device__ __forceinline__ float finish_f32(const GemmParams& p, float acc, int 
 
 __device__ __forceinline__ void epi_bar() { asm volatile("bar.sync 1, 128;" ::: "memory"); }
 
+// Copies of an output in other GPUs' memory: a store to local address x is repeated at x + delta[j] for j < n (plain
+// stores through peer-mapped pointers). NoPeers: none, and the loops below vanish at compile time.
+struct NoPeers {
+  static constexpr int n = 0;
+  long long delta[1];
+};
+struct PeerCopies {
+  int n;
+  long long delta[7];
+};
+template <typename T, typename Peers>
+__device__ __forceinline__ void store_out(T* ptr, T val, const Peers& peers) {
+  *ptr = val;
+  for (int j = 0; j < peers.n; j++) *reinterpret_cast<T*>(reinterpret_cast<char*>(ptr) + peers.delta[j]) = val;
+}
+
 // Weight streaming: the epilogue of 8 tokens (m0 .. m0 + 7) of one weight row per thread (row = tile row 0..127).
-template <int kEpi>
+template <int kEpi, typename Peers = NoPeers>
 __device__ __forceinline__ void store_swapped(const GemmParams& p, const float (&v)[8], int m0, int tile, int row,
-                                              float* xchg) {
+                                              float* xchg, const Peers& peers = Peers()) {
   if constexpr (kEpi == kEpiGluBf16) {
     // rows 0..63 of the tile are gate rows, 64..127 the up rows of the same 64 outputs
     if (row >= 64) {
@@ -238,7 +254,7 @@ __device__ __forceinline__ void store_swapped(const GemmParams& p, const float (
 #pragma unroll
       for (int j = 0; j < 8; j++)
         if (m0 + j < p.M)
-          d[int64_t(m0 + j) * (p.N / 2)] = bf16_bits(silu_mul(__fmul_rn(ag, v[j]), __fmul_rn(au, xchg[j * 64 + row])));
+          store_out(d + int64_t(m0 + j) * (p.N / 2), bf16_bits(silu_mul(__fmul_rn(ag, v[j]), __fmul_rn(au, xchg[j * 64 + row]))), peers);
     }
     epi_bar();
   } else {
@@ -248,8 +264,8 @@ __device__ __forceinline__ void store_swapped(const GemmParams& p, const float (
       const int m = m0 + j;
       if (m < p.M) {
         const float out = finish_f32(p, v[j], m, n);
-        if constexpr (kEpi == kEpiF32) static_cast<float*>(p.d)[int64_t(m) * p.N + n] = out;
-        else static_cast<uint16_t*>(p.d)[int64_t(m) * p.N + n] = bf16_bits(out);
+        if constexpr (kEpi == kEpiF32) store_out(static_cast<float*>(p.d) + int64_t(m) * p.N + n, out, peers);
+        else store_out(static_cast<uint16_t*>(p.d) + int64_t(m) * p.N + n, bf16_bits(out), peers);
       }
     }
   }
@@ -687,7 +703,7 @@ struct Cfg2 {
   static constexpr int kStageBytes = kPBytes + kQBytes + 3 * kSfBytes;  // + scales: own tokens, 2 x 128 weight rows
   static constexpr int kOffQ = kPBytes, kOffSfP = kPBytes + kQBytes, kOffSfQ = kOffSfP + kSfBytes;
   static constexpr int kSfCols = 48;
-  static constexpr int kNumBars = 3 * STAGES + 2;
+  static constexpr int kNumBars = 5 * STAGES + 2;
   static constexpr int kSmemBytes = STAGES * kStageBytes + kNumBars * 8 + 16 + 1024;
   static constexpr int kTmemCols = 512, kSfCol0 = 256;
   static constexpr int kEpiWarps = 16, kFeederWarp0 = 2 + kEpiWarps, kThreads = (kFeederWarp0 + 4) * 32;
@@ -704,10 +720,14 @@ __global__ void __launch_bounds__(Cfg2<STAGES>::kThreads, 1) umma_gemm2_kernel(c
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + STAGES * C::kStageBytes);
-  const uint32_t full0 = smem_u32(bars), empty0 = full0 + 8 * STAGES, sfr0 = empty0 + 8 * STAGES, afull = sfr0 + 8 * STAGES,
-                 aempty = afull + 8;
+  // Per stage: `full` operand tiles landed (this CTA), `sffull` scale atoms landed (this CTA; they are small and are
+  // requested first, so the scale feeders finish while the operand tiles are still in flight), `sfr` scales are in
+  // tensor memory (leader: 8 feeder warps of both CTAs), `pfull` the partner's operand tiles landed (leader), `empty`.
+  const uint32_t full0 = smem_u32(bars), empty0 = full0 + 8 * STAGES, sfr0 = empty0 + 8 * STAGES, sffull0 = sfr0 + 8 * STAGES,
+                 pfull0 = sffull0 + 8 * STAGES, afull = pfull0 + 8 * STAGES, aempty = afull + 8;
   uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(bars + C::kNumBars);
   volatile uint32_t* abort_flag = tmem_holder + 1;
+  volatile uint32_t* epi_ok = tmem_holder + 2;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const uint32_t rank = cluster_ctarank();  // 0: leader
   const int pair = blockIdx.x >> 1, npairs = gridDim.x >> 1;
@@ -719,7 +739,9 @@ __global__ void __launch_bounds__(Cfg2<STAGES>::kThreads, 1) umma_gemm2_kernel(c
     TRACE(3, 0);
     prefetch_tensormap(&tmap_a);
     prefetch_tensormap(&tmap_w);
-    for (int s = 0; s < STAGES; s++) mbar_init(full0 + 8 * s, 1), mbar_init(empty0 + 8 * s, 1), mbar_init(sfr0 + 8 * s, 8);
+    for (int s = 0; s < STAGES; s++)
+      mbar_init(full0 + 8 * s, 1), mbar_init(empty0 + 8 * s, 1), mbar_init(sfr0 + 8 * s, 8), mbar_init(sffull0 + 8 * s, 1),
+          mbar_init(pfull0 + 8 * s, 1);
     mbar_init(afull, 1), mbar_init(aempty, 2 * C::kEpiWarps);
     *abort_flag = 0;
     mbar_init_fence();
@@ -749,20 +771,21 @@ __global__ void __launch_bounds__(Cfg2<STAGES>::kThreads, 1) umma_gemm2_kernel(c
             break;
           }
           const int nsteps = min(4, p.ksteps - 4 * c);
-          const uint32_t sbase = smem_base + stage * C::kStageBytes, bar = full0 + 8 * stage;
+          const uint32_t sbase = smem_base + stage * C::kStageBytes, bar = full0 + 8 * stage, sfbar = sffull0 + 8 * stage;
           TRACE(0, tk);
           tk++;
-          mbar_arrive_expect_tx(bar, C::kPBytes + C::kQBytes + (sfa_valid ? 3 : 2) * nsteps * 512);
+          mbar_arrive_expect_tx(sfbar, (sfa_valid ? 3 : 2) * nsteps * 512);
+          mbar_arrive_expect_tx(bar, C::kPBytes + C::kQBytes);
           armed |= 1u << stage;
           last_parity = (last_parity & ~(1u << stage)) | (phase << stage);
-          tma_load_2d(sbase + C::kOffQ, &tmap_w, c * 128, n0 + int(rank) * 128, bar, kEvictNormal);
-          for (int rb = 0; rb < 2; rb++)
+          for (int rb = 0; rb < 2; rb++)  // the weight scales first: small, and nothing of the preceding kernel
             bulk_load(sbase + C::kOffSfQ + rb * C::kSfBytes, p.sf_q + (int64_t(n0 / 128 + rb) * p.ksteps + 4 * c) * 512,
-                      nsteps * 512, bar, kEvictNormal);
+                      nsteps * 512, sfbar, kEvictNormal);
+          tma_load_2d(sbase + C::kOffQ, &tmap_w, c * 128, n0 + int(rank) * 128, bar, kEvictNormal);
           if (!waited) pdl_wait(), waited = true;  // the activations come from the preceding kernel
-          tma_load_2d(sbase, &tmap_a, c * 128, m0, bar, kEvictLast);
           if (sfa_valid)
-            bulk_load(sbase + C::kOffSfP, p.sf_p + (int64_t(m0 / 128) * p.ksteps + 4 * c) * 512, nsteps * 512, bar, kEvictLast);
+            bulk_load(sbase + C::kOffSfP, p.sf_p + (int64_t(m0 / 128) * p.ksteps + 4 * c) * 512, nsteps * 512, sfbar, kEvictLast);
+          tma_load_2d(sbase, &tmap_a, c * 128, m0, bar, kEvictLast);
           if (++stage == STAGES) stage = 0, phase ^= 1;
         }
       }
@@ -773,7 +796,7 @@ __global__ void __launch_bounds__(Cfg2<STAGES>::kThreads, 1) umma_gemm2_kernel(c
             bool landed = false;
             const long long t0 = clock64();
             for (uint32_t i = 0; i < kMaxPolls && !landed; i++) {
-              landed = mbar_try_wait(full0 + 8 * s, last_parity >> s & 1);
+              landed = mbar_try_wait(full0 + 8 * s, last_parity >> s & 1) && mbar_try_wait(sffull0 + 8 * s, last_parity >> s & 1);
               if ((i & 63u) == 63u && clock64() - t0 > kMaxWaitCycles) break;
             }
             if (!landed) atomicCAS(&g_status, 0u, uint32_t(kStatusDrainTimeout));
@@ -793,8 +816,11 @@ __global__ void __launch_bounds__(Cfg2<STAGES>::kThreads, 1) umma_gemm2_kernel(c
         tc_fence_after_sync();
         uint32_t accumulate = 0;
         for (int c = 0; c < p.chunks; c++) {
-          // eight arrivals: the scale feeders of both CTAs, each after its CTA's stage has landed
-          if (!mbar_wait_bounded(sfr0 + 8 * stage, phase, abort_flag, &g_status, kStatusFullWaitTimeout, 0, true)) {
+          // the operand tiles of this CTA and of the partner have landed, and the scale feeders of both CTAs (eight
+          // arrivals) have put the stage's scales into tensor memory
+          if (!mbar_wait_bounded(full0 + 8 * stage, phase, abort_flag, &g_status, kStatusFullWaitTimeout) ||
+              !mbar_wait_bounded(pfull0 + 8 * stage, phase, abort_flag, &g_status, kStatusFullWaitTimeout, 0, true) ||
+              !mbar_wait_bounded(sfr0 + 8 * stage, phase, abort_flag, &g_status, kStatusFullWaitTimeout, 0, true)) {
             ok = false;
             break;
           }
@@ -816,6 +842,20 @@ __global__ void __launch_bounds__(Cfg2<STAGES>::kThreads, 1) umma_gemm2_kernel(c
         if (ok) umma_commit_2sm(afull);
       }
       if (ok && ntiles > 0) mbar_wait_bounded(aempty, (ntiles - 1) & 1, abort_flag, &g_status, kStatusAccumFreeTimeout, 64, true);
+    } else if (lane == 0) {
+      // the partner's warp 1 has no MMAs to issue: it tells the leader when this CTA's operand tiles have landed
+      int stage = 0;
+      uint32_t phase = 0;
+      bool ok = true;
+      for (int item = pair; ok && item < items; item += npairs)
+        for (int c = 0; c < p.chunks; c++) {
+          if (!mbar_wait_bounded(full0 + 8 * stage, phase, abort_flag, &g_status, kStatusFullWaitTimeout, 20)) {
+            ok = false;
+            break;
+          }
+          mbar_arrive_remote(pfull0 + 8 * stage, 0);
+          if (++stage == STAGES) stage = 0, phase ^= 1;
+        }
     }
   } else if (warp >= C::kFeederWarp0) {
     // ------------------------------------------------------------------------------------------ scale feeders
@@ -825,7 +865,7 @@ __global__ void __launch_bounds__(Cfg2<STAGES>::kThreads, 1) umma_gemm2_kernel(c
     bool ok = true;
     for (int item = pair; ok && item < items; item += npairs) {
       for (int c = 0; c < p.chunks; c++) {
-        if (!warp_wait(full0 + 8 * stage, phase, abort_flag, &g_status, kStatusFullWaitTimeout, 32)) {
+        if (!warp_wait(sffull0 + 8 * stage, phase, abort_flag, &g_status, kStatusFullWaitTimeout, 32)) {
           ok = false;
           break;
         }
@@ -865,7 +905,15 @@ __global__ void __launch_bounds__(Cfg2<STAGES>::kThreads, 1) umma_gemm2_kernel(c
     int ntiles = 0;
     for (int item = pair; item < items; item += npairs, ntiles++) {
       const int m = (item % m_pairs) * 256 + int(rank) * 128 + row, n0 = (item / m_pairs) * 256;
-      if (!warp_wait(afull, ntiles & 1, abort_flag, &g_status, kStatusAccumWaitTimeout, 128)) break;
+      // One warp watches the accumulator barrier closely; the other fifteen sleep in a hardware barrier until it has
+      // seen the MMAs complete (sixteen polling warps would either poll rarely or crowd the shared-memory pipe).
+      if (warp == 2) {
+        const bool done = warp_wait(afull, ntiles & 1, abort_flag, &g_status, kStatusAccumWaitTimeout, 20);
+        if (lane == 0) *epi_ok = done;
+      }
+      asm volatile("bar.sync 2, %0;" ::"r"(C::kEpiWarps * 32) : "memory");
+      if (!*epi_ok) break;
+      mbar_wait_bounded(afull, ntiles & 1, abort_flag, &g_status, kStatusAccumWaitTimeout);  // (every thread observes the phase itself)
       tc_fence_after_sync();
       if (warp == 2 && lane == 0 && ntiles < 4) TRACE(3, 4 + ntiles);
       float g[kMine][16], u[kGlu ? kMine : 1][16];
@@ -1364,7 +1412,36 @@ int q27b_skinny_group_build(int M, int n_problems, const q27b_group_problem* pro
   return 0;
 }
 
+static int group_launch(const void* table_host, const void* table_dev, void* ws, size_t ws_bytes, const q27b_group_peers* peers,
+                        void* stream);
+
 int q27b_skinny_fp4_group(const void* table_host, const void* table_dev, void* ws, size_t ws_bytes, void* stream) {
+  return group_launch(table_host, table_dev, ws, ws_bytes, nullptr, stream);
+}
+int q27b_skinny_fp4_group_gather(const void* table_host, const void* table_dev, void* ws, size_t ws_bytes,
+                                 const q27b_group_peers* peers, void* stream) {
+  Q27B_REQUIRE(peers && peers->n_peers >= 1 && peers->n_peers <= 7, "skinny_group_gather: 1..7 peers");
+  Q27B_REQUIRE(peers->signals, "skinny_group_gather: null signal block");
+  for (int j = 0; j < peers->n_peers; j++)
+    Q27B_REQUIRE(peers->peer_signals[j] && peers->out_delta[j] % 16 == 0, "skinny_group_gather: peer %d: null signal block or misaligned delta", j);
+  Q27B_REQUIRE(peers->my_slot >= 0 && peers->my_slot < 8, "skinny_group_gather: my_slot must be 0..7");
+  return group_launch(table_host, table_dev, ws, ws_bytes, peers, stream);
+}
+int q27b_group_gather_wait(int32_t* signals, int n_peers, const int* peer_slots, void* stream) {
+  Q27B_REQUIRE(signals && n_peers >= 1 && n_peers <= 7 && peer_slots, "group_gather_wait: bad arguments");
+  GatherWait w = {};
+  w.signals = signals, w.n = n_peers;
+  for (int j = 0; j < n_peers; j++) {
+    Q27B_REQUIRE(peer_slots[j] >= 0 && peer_slots[j] < 8, "group_gather_wait: slots are 0..7");
+    w.slot[j] = peer_slots[j];
+  }
+  group_gather_wait_kernel<<<1, 32, 0, static_cast<cudaStream_t>(stream)>>>(w);
+  Q27B_CUDA(cudaGetLastError());
+  return 0;
+}
+
+static int group_launch(const void* table_host, const void* table_dev, void* ws, size_t ws_bytes, const q27b_group_peers* peers,
+                        void* stream) {
   Q27B_REQUIRE(table_host && table_dev, "skinny_group: null table");
   GroupHeader h;
   memcpy(&h, table_host, sizeof h);
@@ -1385,6 +1462,11 @@ int q27b_skinny_fp4_group(const void* table_host, const void* table_dev, void* w
 #ifdef Q27B_TRACE
   gl.trace = g_trace;
 #endif
+  if (peers) {
+    gl.peers.n = peers->n_peers;
+    gl.signals = peers->signals, gl.my_slot = peers->my_slot;
+    for (int j = 0; j < peers->n_peers; j++) gl.peers.delta[j] = peers->out_delta[j], gl.peer_signals[j] = peers->peer_signals[j];
+  }
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   switch (h.nb) {
     case 16: return launch_group<16, 4>(gl, h.n_ctas, s);

@@ -79,6 +79,12 @@ class Fp4Group:
         call("q27b_skinny_fp4_group", self.table_host, self.table_dev, self.ws, self.ws.numel(),
              torch.cuda.current_stream().cuda_stream)
 
+    def launch_gather(self, peers):
+        """The launch with the gather fused into its epilogue: every output is also stored into the peers' memory
+        (`peers`: a peer.GroupPeers; all outputs of the group must lie in the payload of one peer.PeerRegion)."""
+        call("q27b_skinny_fp4_group_gather", self.table_host, self.table_dev, self.ws, self.ws.numel(), ctypes.byref(peers),
+             torch.cuda.current_stream().cuda_stream)
+
     def run_sync(self):
         """Through the synchronous test wrapper (synchronises, checks the device status)."""
         call("q27t_skinny_fp4_group", self.table_host, self.table_dev, self.ws, self.ws.numel())

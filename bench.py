@@ -460,7 +460,22 @@ def run_sweep(args, model, rank, world, local_rank, peaks):
     G = min(args.group_layers, L)
     ms_list = list(configs.SWEEP_M) if args.m == 0 else [args.m]
     head_m = 16 if 16 in ms_list else ms_list[0]
-    gather = args.gather if world > 1 else "none"
+    gather, gather_note = (args.gather, None) if world > 1 else ("none", None)
+    if gather == "fused":
+        # peer-mapped memory is set up through torch's symmetric memory; where that is not available on a box every rank
+        # falls back to the NCCL all-gather together (and the line says so)
+        try:
+            from q27b200.peer import PeerRegion
+            probe = PeerRegion(4096)
+            okp, why = (len(probe.ptrs) == world), "unexpected pointer table"
+            del probe
+        except Exception as e:  # noqa: BLE001
+            okp, why = False, f"{type(e).__name__}: {e}"
+        flag = torch.tensor([int(okp)], device="cuda")
+        torch.distributed.all_reduce(flag, op=torch.distributed.ReduceOp.MIN)
+        if not bool(flag.item()):
+            gather, gather_note = "nccl", "peer-mapped memory could not be set up (" + (why if not okp else "on another rank") + "): NCCL all-gather instead"
+            log(gather_note)
     cap = 4 if world > 1 else 5  # steps per captured graph (even on several GPUs: the output buffers alternate)
     sweep, modes, verified, head = {}, {}, True, None
 
@@ -553,7 +568,8 @@ def run_sweep(args, model, rank, world, local_rank, peaks):
         del sw
         torch.cuda.empty_cache()
     assert device_status() == 0, "a bounded wait inside a kernel ran out"
-    return {"head_m": head_m, "G": G, "sweep": sweep, "modes": modes, "verified": verified, "head": head, "gather": gather}
+    return {"head_m": head_m, "G": G, "sweep": sweep, "modes": modes, "verified": verified, "head": head, "gather": gather,
+            "gather_note": gather_note}
 
 
 # ------------------------------------------------------------------------------------------- single-GEMM configurations
@@ -796,6 +812,7 @@ def main():
                          "peak_source": peaks["source"] + ": copy bandwidth"},
             "clocks": h["clocks"], "sustained": h["sustained"], "e2e": h["e2e"], "gpu_launches": args.steps * h["launches"],
             **{k: h[k] for k in ("without_gather", "with_nccl_all_gather") if k in h},
+            **({"gather_note": r["gather_note"]} if r["gather_note"] else {}),
             "sweep": r["sweep"], "modes": r["modes"]})
     subs = {}
     for idx in (0, 1, 2, 4):

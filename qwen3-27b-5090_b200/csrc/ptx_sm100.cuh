@@ -295,6 +295,25 @@ __device__ __forceinline__ void umma_nvfp4_2sm(uint32_t d_tmem, uint64_t adesc, 
       ::"r"(d_tmem), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate), "r"(sfa_tmem), "r"(sfb_tmem)
       : "memory");
 }
+// The same with the accumulate flag fixed at compile time (no predicate to evaluate between two MMAs).
+template <bool kAccumulate>
+__device__ __forceinline__ void umma_nvfp4_2sm_imm(uint32_t d_tmem, uint64_t adesc, uint64_t bdesc, uint32_t idesc,
+                                                   uint32_t sfa_tmem, uint32_t sfb_tmem) {
+  if constexpr (kAccumulate)
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.eq.b32 p, 0, 0;\n\t"
+        "tcgen05.mma.cta_group::2.kind::mxf4nvf4.block_scale.scale_vec::4X [%0], %1, %2, %3, [%4], [%5], p;\n\t}"
+        ::"r"(d_tmem), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(sfa_tmem), "r"(sfb_tmem)
+        : "memory");
+  else
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, 0, 0;\n\t"
+        "tcgen05.mma.cta_group::2.kind::mxf4nvf4.block_scale.scale_vec::4X [%0], %1, %2, %3, [%4], [%5], p;\n\t}"
+        ::"r"(d_tmem), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(sfa_tmem), "r"(sfb_tmem)
+        : "memory");
+}
 // Arrives on the barrier at this offset in both CTAs once the leader's tcgen05 operations so far have completed.
 __device__ __forceinline__ void umma_commit_2sm(uint32_t bar) {
   asm volatile(

@@ -28,6 +28,7 @@
 #include <algorithm>
 #include <cstdlib>
 #include <cstring>
+#include <type_traits>
 #include <vector>
 
 #include "../../include/q27b200/capi.h"
@@ -703,7 +704,7 @@ struct Cfg2 {
   static constexpr int kStageBytes = kPBytes + kQBytes + 3 * kSfBytes;  // + scales: own tokens, 2 x 128 weight rows
   static constexpr int kOffQ = kPBytes, kOffSfP = kPBytes + kQBytes, kOffSfQ = kOffSfP + kSfBytes;
   static constexpr int kSfCols = 48;
-  static constexpr int kNumBars = 5 * STAGES + 2;
+  static constexpr int kNumBars = 3 * STAGES + 2;
   static constexpr int kSmemBytes = STAGES * kStageBytes + kNumBars * 8 + 16 + 1024;
   static constexpr int kTmemCols = 512, kSfCol0 = 256;
   static constexpr int kEpiWarps = 16, kFeederWarp0 = 2 + kEpiWarps, kThreads = (kFeederWarp0 + 4) * 32;
@@ -720,11 +721,8 @@ __global__ void __launch_bounds__(Cfg2<STAGES>::kThreads, 1) umma_gemm2_kernel(c
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + STAGES * C::kStageBytes);
-  // Per stage: `full` operand tiles landed (this CTA), `sffull` scale atoms landed (this CTA; they are small and are
-  // requested first, so the scale feeders finish while the operand tiles are still in flight), `sfr` scales are in
-  // tensor memory (leader: 8 feeder warps of both CTAs), `pfull` the partner's operand tiles landed (leader), `empty`.
-  const uint32_t full0 = smem_u32(bars), empty0 = full0 + 8 * STAGES, sfr0 = empty0 + 8 * STAGES, sffull0 = sfr0 + 8 * STAGES,
-                 pfull0 = sffull0 + 8 * STAGES, afull = pfull0 + 8 * STAGES, aempty = afull + 8;
+  const uint32_t full0 = smem_u32(bars), empty0 = full0 + 8 * STAGES, sfr0 = empty0 + 8 * STAGES, afull = sfr0 + 8 * STAGES,
+                 aempty = afull + 8;
   uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(bars + C::kNumBars);
   volatile uint32_t* abort_flag = tmem_holder + 1;
   volatile uint32_t* epi_ok = tmem_holder + 2;
@@ -739,9 +737,7 @@ __global__ void __launch_bounds__(Cfg2<STAGES>::kThreads, 1) umma_gemm2_kernel(c
     TRACE(3, 0);
     prefetch_tensormap(&tmap_a);
     prefetch_tensormap(&tmap_w);
-    for (int s = 0; s < STAGES; s++)
-      mbar_init(full0 + 8 * s, 1), mbar_init(empty0 + 8 * s, 1), mbar_init(sfr0 + 8 * s, 8), mbar_init(sffull0 + 8 * s, 1),
-          mbar_init(pfull0 + 8 * s, 1);
+    for (int s = 0; s < STAGES; s++) mbar_init(full0 + 8 * s, 1), mbar_init(empty0 + 8 * s, 1), mbar_init(sfr0 + 8 * s, 8);
     mbar_init(afull, 1), mbar_init(aempty, 2 * C::kEpiWarps);
     *abort_flag = 0;
     mbar_init_fence();
@@ -771,20 +767,19 @@ __global__ void __launch_bounds__(Cfg2<STAGES>::kThreads, 1) umma_gemm2_kernel(c
             break;
           }
           const int nsteps = min(4, p.ksteps - 4 * c);
-          const uint32_t sbase = smem_base + stage * C::kStageBytes, bar = full0 + 8 * stage, sfbar = sffull0 + 8 * stage;
+          const uint32_t sbase = smem_base + stage * C::kStageBytes, bar = full0 + 8 * stage;
           TRACE(0, tk);
           tk++;
-          mbar_arrive_expect_tx(sfbar, (sfa_valid ? 3 : 2) * nsteps * 512);
-          mbar_arrive_expect_tx(bar, C::kPBytes + C::kQBytes);
+          mbar_arrive_expect_tx(bar, C::kPBytes + C::kQBytes + (sfa_valid ? 3 : 2) * nsteps * 512);
           armed |= 1u << stage;
           last_parity = (last_parity & ~(1u << stage)) | (phase << stage);
           for (int rb = 0; rb < 2; rb++)  // the weight scales first: small, and nothing of the preceding kernel
             bulk_load(sbase + C::kOffSfQ + rb * C::kSfBytes, p.sf_q + (int64_t(n0 / 128 + rb) * p.ksteps + 4 * c) * 512,
-                      nsteps * 512, sfbar, kEvictNormal);
+                      nsteps * 512, bar, kEvictNormal);
           tma_load_2d(sbase + C::kOffQ, &tmap_w, c * 128, n0 + int(rank) * 128, bar, kEvictNormal);
           if (!waited) pdl_wait(), waited = true;  // the activations come from the preceding kernel
           if (sfa_valid)
-            bulk_load(sbase + C::kOffSfP, p.sf_p + (int64_t(m0 / 128) * p.ksteps + 4 * c) * 512, nsteps * 512, sfbar, kEvictLast);
+            bulk_load(sbase + C::kOffSfP, p.sf_p + (int64_t(m0 / 128) * p.ksteps + 4 * c) * 512, nsteps * 512, bar, kEvictLast);
           tma_load_2d(sbase, &tmap_a, c * 128, m0, bar, kEvictLast);
           if (++stage == STAGES) stage = 0, phase ^= 1;
         }
@@ -796,7 +791,7 @@ __global__ void __launch_bounds__(Cfg2<STAGES>::kThreads, 1) umma_gemm2_kernel(c
             bool landed = false;
             const long long t0 = clock64();
             for (uint32_t i = 0; i < kMaxPolls && !landed; i++) {
-              landed = mbar_try_wait(full0 + 8 * s, last_parity >> s & 1) && mbar_try_wait(sffull0 + 8 * s, last_parity >> s & 1);
+              landed = mbar_try_wait(full0 + 8 * s, last_parity >> s & 1);
               if ((i & 63u) == 63u && clock64() - t0 > kMaxWaitCycles) break;
             }
             if (!landed) atomicCAS(&g_status, 0u, uint32_t(kStatusDrainTimeout));
@@ -806,56 +801,61 @@ __global__ void __launch_bounds__(Cfg2<STAGES>::kThreads, 1) umma_gemm2_kernel(c
   } else if (warp == 1) {
     // ------------------------------------------------------------------------------------------ MMA issuer (leader)
     if (lane == 0 && rank == 0) {
+      // This one thread feeds the tensor cores of both SMs, and every instruction it executes between two MMAs is time
+      // the tensor pipe idles: measured here, the loop around the four MMAs of a stage cost as much as the MMAs. So
+      // the body of a stage is generated once per ring slot with every shared-memory address, descriptor offset and
+      // tensor-memory column a compile-time constant, and the first stage of a tile (which overwrites the accumulator
+      // instead of adding to it) is a separate instantiation rather than a predicate evaluated per MMA.
       constexpr uint32_t idesc = umma_idesc_nvfp4_2sm(256);
-      int stage = 0, ntiles = 0, tk = 0;
+      int stage = 0, ntiles = 0;
       uint32_t phase = 0;
       bool ok = true;
+      const uint64_t desc_a0 = umma_desc_k_sw128(smem_base), desc_b0 = umma_desc_k_sw128(smem_base + C::kOffQ);
+      const uint32_t sf_col0 = tmem_base + C::kSfCol0;
+      auto issue_stage = [&](auto stage_c, auto first_c, int nsteps) -> bool {
+        constexpr int S = decltype(stage_c)::value;
+        constexpr bool kFirst = decltype(first_c)::value;
+        // eight arrivals: the scale feeders of both CTAs, each after its CTA's stage has landed
+        if (!mbar_wait_bounded(sfr0 + 8 * S, phase, abort_flag, &g_status, kStatusFullWaitTimeout, 0, true)) return false;
+        tc_fence_after_sync();
+        constexpr uint64_t kStageDesc = uint64_t(S) * (C::kStageBytes >> 4);  // the stage's offset in 16-byte units
+        const uint64_t da = desc_a0 + kStageDesc, db = desc_b0 + kStageDesc;
+        const uint32_t sf = sf_col0 + C::kSfCols * S;
+        if (nsteps == 4) {
+          umma_nvfp4_2sm_imm<!kFirst>(tmem_base, da, db, idesc, sf, sf + 16);
+          umma_nvfp4_2sm_imm<true>(tmem_base, da + 2, db + 2, idesc, sf + 4, sf + 24);
+          umma_nvfp4_2sm_imm<true>(tmem_base, da + 4, db + 4, idesc, sf + 8, sf + 32);
+          umma_nvfp4_2sm_imm<true>(tmem_base, da + 6, db + 6, idesc, sf + 12, sf + 40);
+        } else {
+          for (int ks = 0; ks < nsteps; ks++)
+            umma_nvfp4_2sm(tmem_base, da + 2 * ks, db + 2 * ks, idesc, sf + 4 * ks, sf + 16 + 8 * ks, (kFirst && ks == 0) ? 0u : 1u);
+        }
+        umma_commit_2sm(empty0 + 8 * S);  // frees the stage in both CTAs
+        return true;
+      };
+      auto issue = [&](auto first_c, int nsteps) -> bool {
+        bool r;
+        switch (stage) {
+          case 0: r = issue_stage(std::integral_constant<int, 0>(), first_c, nsteps); break;
+          case 1: r = issue_stage(std::integral_constant<int, 1 % STAGES>(), first_c, nsteps); break;
+          case 2: r = issue_stage(std::integral_constant<int, 2 % STAGES>(), first_c, nsteps); break;
+          case 3: r = issue_stage(std::integral_constant<int, 3 % STAGES>(), first_c, nsteps); break;
+          case 4: r = issue_stage(std::integral_constant<int, 4 % STAGES>(), first_c, nsteps); break;
+          default: r = issue_stage(std::integral_constant<int, 5 % STAGES>(), first_c, nsteps); break;
+        }
+        if (++stage == STAGES) stage = 0, phase ^= 1;
+        return r;
+      };
+      static_assert(STAGES <= 6, "one case per ring slot");
       for (int item = pair; ok && item < items; item += npairs, ntiles++) {
         // both CTAs' epilogues have read the accumulators of the previous tile
         if (!mbar_wait_bounded(aempty, (ntiles & 1) ^ 1, abort_flag, &g_status, kStatusAccumFreeTimeout, 0, true)) break;
         tc_fence_after_sync();
-        uint32_t accumulate = 0;
-        for (int c = 0; c < p.chunks; c++) {
-          // the operand tiles of this CTA and of the partner have landed, and the scale feeders of both CTAs (eight
-          // arrivals) have put the stage's scales into tensor memory
-          if (!mbar_wait_bounded(full0 + 8 * stage, phase, abort_flag, &g_status, kStatusFullWaitTimeout) ||
-              !mbar_wait_bounded(pfull0 + 8 * stage, phase, abort_flag, &g_status, kStatusFullWaitTimeout, 0, true) ||
-              !mbar_wait_bounded(sfr0 + 8 * stage, phase, abort_flag, &g_status, kStatusFullWaitTimeout, 0, true)) {
-            ok = false;
-            break;
-          }
-          tc_fence_after_sync();
-          TRACE(1, tk);
-          const int nsteps = min(4, p.ksteps - 4 * c);
-          const uint32_t sbase = smem_base + stage * C::kStageBytes;
-          const uint64_t desc_a = umma_desc_k_sw128(sbase), desc_b = umma_desc_k_sw128(sbase + C::kOffQ);
-          const uint32_t sf_col = tmem_base + C::kSfCol0 + C::kSfCols * stage;
-          for (int ks = 0; ks < nsteps; ks++) {
-            umma_nvfp4_2sm(tmem_base, desc_a + 2 * ks, desc_b + 2 * ks, idesc, sf_col + 4 * ks, sf_col + 16 + 8 * ks, accumulate);
-            accumulate = 1;
-          }
-          umma_commit_2sm(empty0 + 8 * stage);  // frees the stage in both CTAs
-          TRACE(2, tk);
-          tk++;
-          if (++stage == STAGES) stage = 0, phase ^= 1;
-        }
+        ok = issue(std::true_type(), min(4, p.ksteps));
+        for (int c = 1; ok && c < p.chunks; c++) ok = issue(std::false_type(), min(4, p.ksteps - 4 * c));
         if (ok) umma_commit_2sm(afull);
       }
       if (ok && ntiles > 0) mbar_wait_bounded(aempty, (ntiles - 1) & 1, abort_flag, &g_status, kStatusAccumFreeTimeout, 64, true);
-    } else if (lane == 0) {
-      // the partner's warp 1 has no MMAs to issue: it tells the leader when this CTA's operand tiles have landed
-      int stage = 0;
-      uint32_t phase = 0;
-      bool ok = true;
-      for (int item = pair; ok && item < items; item += npairs)
-        for (int c = 0; c < p.chunks; c++) {
-          if (!mbar_wait_bounded(full0 + 8 * stage, phase, abort_flag, &g_status, kStatusFullWaitTimeout, 20)) {
-            ok = false;
-            break;
-          }
-          mbar_arrive_remote(pfull0 + 8 * stage, 0);
-          if (++stage == STAGES) stage = 0, phase ^= 1;
-        }
     }
   } else if (warp >= C::kFeederWarp0) {
     // ------------------------------------------------------------------------------------------ scale feeders
@@ -865,7 +865,7 @@ __global__ void __launch_bounds__(Cfg2<STAGES>::kThreads, 1) umma_gemm2_kernel(c
     bool ok = true;
     for (int item = pair; ok && item < items; item += npairs) {
       for (int c = 0; c < p.chunks; c++) {
-        if (!warp_wait(sffull0 + 8 * stage, phase, abort_flag, &g_status, kStatusFullWaitTimeout, 32)) {
+        if (!warp_wait(full0 + 8 * stage, phase, abort_flag, &g_status, kStatusFullWaitTimeout, 32)) {
           ok = false;
           break;
         }

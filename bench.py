@@ -575,6 +575,10 @@ def run_sweep(args, model, rank, world, local_rank, peaks):
 # ------------------------------------------------------------------------------------------- single-GEMM configurations
 
 
+def total_bytes_of(cfg):
+    return cfg.algorithmic_bytes()
+
+
 def run_single(cfg, args, rank, world, local_rank, peaks):
     """One of cfg0 / cfg1 / cfg2 / cfg4: step = quantise the bf16 activation + the GEMM with its epilogue, weights
     rotating through more than L2-size of distinct copies, replayed from a CUDA graph until the region is long enough."""
@@ -636,6 +640,42 @@ def run_single(cfg, args, rank, world, local_rank, peaks):
         torch.distributed.all_reduce(flag, op=torch.distributed.ReduceOp.MIN)
         ok = bool(flag.item())
     ms_gemm = timed(gemm_only, steps, args.warmup, world, graph_cap=per)
+    grouped = None
+    if world == 1 and M <= 128:
+        # The same GEMM on all the rotating weight copies as ONE grouped launch (behind one quantiser launch): what the
+        # shape streams at once the launch boundaries are out of the way. One launch = nbuf GEMMs; reported per GEMM.
+        from q27b200.group import Fp4Group, problem_of
+
+        g_outs = [torch.zeros(M, n_local, dtype=torch.bfloat16, device="cuda") for _ in range(nbuf)]
+        best = None
+        for whole in (True, False):
+            grp = Fp4Group(M, [problem_of(l, act.q, act.sf, o) for l, o in zip(layers, g_outs)], whole_tiles=whole)
+
+            def step_grouped(i, grp=grp):
+                act.quantize(xd, in_scale)
+                grp.launch()
+
+            reps = max(4, int(MIN_REGION_MS / max(est * nbuf, 1e-3)) // 4 * 4)
+            ms_g = timed(step_grouped, reps, 3, world, graph_cap=4)
+            want_g = torch.zeros_like(g_outs[0])
+            with serial_launches():
+                q, sf = act.quantize(xd, in_scale)
+                torch.cuda.synchronize()
+                if whole:  # (no K split: the many-row GEMM's bits)
+                    layers[0]._dispatch(M, q, sf, want_g, None, False, layers[0].rows(), cfg.K, torch.cuda.current_stream().cuda_stream)
+                else:
+                    layers[0].gemm(M, q, sf, want_g)
+                torch.cuda.synchronize()
+            ok_g = all(bool(torch.equal(o, want_g)) for o in g_outs)
+            ok = ok and ok_g
+            per_gemm_s = ms_g / reps / nbuf / 1e3
+            r = {"value": total_bytes_of(cfg) / per_gemm_s / 1e9, "unit": "GB/s", "us_per_gemm": per_gemm_s * 1e6,
+                 "frac": total_bytes_of(cfg) / per_gemm_s / 1e9 / peaks["hbm_gbs"], "gemms_per_launch": nbuf,
+                 "plan": "whole tiles" if whole else "the stand-alone launch's K split", "imbalance": grp.imbalance, "verified": ok_g}
+            if best is None or r["value"] > best["value"]:
+                best = r
+            del grp
+        grouped = best
     assert device_status() == 0, "a bounded wait inside a kernel ran out"
     per_step_s, gemm_s = ms / steps / 1e3, ms_gemm / steps / 1e3
     total_bytes, flops = cfg.algorithmic_bytes(), cfg.flops()
@@ -667,7 +707,10 @@ def run_single(cfg, args, rank, world, local_rank, peaks):
            + (" + all-gather (NCCL, in the graph)" if world > 1 else ""),
            "l2": f"weights rotate through {nbuf} distinct copies ({nbuf * layers[0].weight_bytes() / 2**20:.0f} MiB per GPU > 126 MiB L2)",
            "roofline": roof, "clocks": clocks, "verified": ok}
-    log(f"{cfg.name}: {value:.1f} {unit}, GEMM {gemm_s * 1e6:.2f} us, frac {roof['frac']:.3f}, verified {ok}")
+    if grouped:
+        res["grouped_over_the_weight_copies"] = grouped
+    log(f"{cfg.name}: {value:.1f} {unit}, GEMM {gemm_s * 1e6:.2f} us, frac {roof['frac']:.3f}, verified {ok}"
+        + (f"; grouped {grouped['value']:.0f} GB/s ({grouped['frac']:.2f}, {grouped['plan']})" if grouped else ""))
     del layers, codes, sfs
     torch.cuda.empty_cache()
     return res

@@ -194,10 +194,21 @@ __device__ __forceinline__ unsigned long long gtime() {
   do {                                                                                                    \
     if (p.trace && (idx) < 64) p.trace[(size_t(blockIdx.x) * 4 + (kind)) * 64 + (idx)] = gtime();         \
   } while (0)
+#define TRACE_DECL(name) unsigned long long name = 0
+#define TRACE_T0(t) const unsigned long long t = gtime()
+#define TRACE_ADD(acc, t) acc += gtime() - t
+#define TRACE_PUT(idx, v)                                                           \
+  do {                                                                              \
+    if (p.trace) p.trace[(size_t(blockIdx.x) * 4 + 3) * 64 + (idx)] = (v);          \
+  } while (0)
 #else
 #define TRACE(kind, idx) \
   do {                   \
   } while (0)
+#define TRACE_DECL(name)
+#define TRACE_T0(t)
+#define TRACE_ADD(acc, t)
+#define TRACE_PUT(idx, v)
 #endif
 
 // silu(g) * u with the fast exponential and reciprocal (the reference's fused epilogue uses the same pair,
@@ -758,29 +769,33 @@ __global__ void __launch_bounds__(Cfg2<STAGES>::kThreads, 1) umma_gemm2_kernel(c
       int stage = 0, tk = 0;
       uint32_t phase = 0, armed = 0, last_parity = 0;
       bool ok = true, waited = false;
+      // (the time between a slot coming free and its loads being issued is part of every slot's round trip: per tile the
+      //  source pointers are set up once and only stepped per stage)
       for (int item = pair; ok && item < items; item += npairs) {
         const int m0 = (item % m_pairs) * 256 + int(rank) * 128, n0 = (item / m_pairs) * 256;
         const bool sfa_valid = m0 / 128 < m_blocks;  // the partner half of the last token tile may not exist
-        for (int c = 0; c < p.chunks; c++) {
+        const uint8_t* sfq = p.sf_q + int64_t(n0 / 128) * p.ksteps * 512;  // scale atoms of weight rows n0 .. n0 + 127
+        const uint8_t* sfp = p.sf_p + int64_t(m0 / 128) * p.ksteps * 512;  // scale atoms of this CTA's tokens
+        const int64_t sfq_block = int64_t(p.ksteps) * 512;                 // ... and of the next 128 weight rows
+        const int wrow = n0 + int(rank) * 128;
+        for (int c = 0; c < p.chunks; c++, sfq += 2048, sfp += 2048) {
           if (!mbar_wait_bounded(empty0 + 8 * stage, phase ^ 1, abort_flag, &g_status, kStatusEmptyWaitTimeout)) {
             ok = false;
             break;
           }
-          const int nsteps = min(4, p.ksteps - 4 * c);
+          const uint32_t sf_bytes = uint32_t(min(4, p.ksteps - 4 * c)) * 512;
           const uint32_t sbase = smem_base + stage * C::kStageBytes, bar = full0 + 8 * stage;
           TRACE(0, tk);
           tk++;
-          mbar_arrive_expect_tx(bar, C::kPBytes + C::kQBytes + (sfa_valid ? 3 : 2) * nsteps * 512);
+          mbar_arrive_expect_tx(bar, C::kPBytes + C::kQBytes + (sfa_valid ? 3 : 2) * sf_bytes);
           armed |= 1u << stage;
           last_parity = (last_parity & ~(1u << stage)) | (phase << stage);
-          for (int rb = 0; rb < 2; rb++)  // the weight scales first: small, and nothing of the preceding kernel
-            bulk_load(sbase + C::kOffSfQ + rb * C::kSfBytes, p.sf_q + (int64_t(n0 / 128 + rb) * p.ksteps + 4 * c) * 512,
-                      nsteps * 512, bar, kEvictNormal);
-          tma_load_2d(sbase + C::kOffQ, &tmap_w, c * 128, n0 + int(rank) * 128, bar, kEvictNormal);
+          tma_load_2d(sbase + C::kOffQ, &tmap_w, c * 128, wrow, bar, kEvictNormal);
+          bulk_load(sbase + C::kOffSfQ, sfq, sf_bytes, bar, kEvictNormal);
+          bulk_load(sbase + C::kOffSfQ + C::kSfBytes, sfq + sfq_block, sf_bytes, bar, kEvictNormal);
           if (!waited) pdl_wait(), waited = true;  // the activations come from the preceding kernel
-          if (sfa_valid)
-            bulk_load(sbase + C::kOffSfP, p.sf_p + (int64_t(m0 / 128) * p.ksteps + 4 * c) * 512, nsteps * 512, bar, kEvictLast);
           tma_load_2d(sbase, &tmap_a, c * 128, m0, bar, kEvictLast);
+          if (sfa_valid) bulk_load(sbase + C::kOffSfP, sfp, sf_bytes, bar, kEvictLast);
           if (++stage == STAGES) stage = 0, phase ^= 1;
         }
       }
@@ -812,11 +827,16 @@ __global__ void __launch_bounds__(Cfg2<STAGES>::kThreads, 1) umma_gemm2_kernel(c
       bool ok = true;
       const uint64_t desc_a0 = umma_desc_k_sw128(smem_base), desc_b0 = umma_desc_k_sw128(smem_base + C::kOffQ);
       const uint32_t sf_col0 = tmem_base + C::kSfCol0;
+      TRACE_DECL(w_stage);
+      TRACE_DECL(w_acc);
+      TRACE_T0(t_begin);
       auto issue_stage = [&](auto stage_c, auto first_c, int nsteps) -> bool {
         constexpr int S = decltype(stage_c)::value;
         constexpr bool kFirst = decltype(first_c)::value;
         // eight arrivals: the scale feeders of both CTAs, each after its CTA's stage has landed
+        TRACE_T0(t_s);
         if (!mbar_wait_bounded(sfr0 + 8 * S, phase, abort_flag, &g_status, kStatusFullWaitTimeout, 0, true)) return false;
+        TRACE_ADD(w_stage, t_s);
         tc_fence_after_sync();
         constexpr uint64_t kStageDesc = uint64_t(S) * (C::kStageBytes >> 4);  // the stage's offset in 16-byte units
         const uint64_t da = desc_a0 + kStageDesc, db = desc_b0 + kStageDesc;
@@ -849,12 +869,18 @@ __global__ void __launch_bounds__(Cfg2<STAGES>::kThreads, 1) umma_gemm2_kernel(c
       static_assert(STAGES <= 6, "one case per ring slot");
       for (int item = pair; ok && item < items; item += npairs, ntiles++) {
         // both CTAs' epilogues have read the accumulators of the previous tile
+        TRACE_T0(t_e);
         if (!mbar_wait_bounded(aempty, (ntiles & 1) ^ 1, abort_flag, &g_status, kStatusAccumFreeTimeout, 0, true)) break;
+        TRACE_ADD(w_acc, t_e);
         tc_fence_after_sync();
         ok = issue(std::true_type(), min(4, p.ksteps));
         for (int c = 1; ok && c < p.chunks; c++) ok = issue(std::false_type(), min(4, p.ksteps - 4 * c));
         if (ok) umma_commit_2sm(afull);
       }
+      TRACE_PUT(58, w_stage);
+      TRACE_PUT(59, w_acc);
+      TRACE_PUT(60, gtime() - t_begin);
+      TRACE_PUT(61, (unsigned long long)ntiles);
       if (ok && ntiles > 0) mbar_wait_bounded(aempty, (ntiles - 1) & 1, abort_flag, &g_status, kStatusAccumFreeTimeout, 64, true);
     }
   } else if (warp >= C::kFeederWarp0) {

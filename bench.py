@@ -460,22 +460,7 @@ def run_sweep(args, model, rank, world, local_rank, peaks):
     G = min(args.group_layers, L)
     ms_list = list(configs.SWEEP_M) if args.m == 0 else [args.m]
     head_m = 16 if 16 in ms_list else ms_list[0]
-    gather, gather_note = (args.gather, None) if world > 1 else ("none", None)
-    if gather == "fused":
-        # peer-mapped memory is set up through torch's symmetric memory; where that is not available on a box every rank
-        # falls back to the NCCL all-gather together (and the line says so)
-        try:
-            from q27b200.peer import PeerRegion
-            probe = PeerRegion(4096)
-            okp, why = (len(probe.ptrs) == world), "unexpected pointer table"
-            del probe
-        except Exception as e:  # noqa: BLE001
-            okp, why = False, f"{type(e).__name__}: {e}"
-        flag = torch.tensor([int(okp)], device="cuda")
-        torch.distributed.all_reduce(flag, op=torch.distributed.ReduceOp.MIN)
-        if not bool(flag.item()):
-            gather, gather_note = "nccl", "peer-mapped memory could not be set up (" + (why if not okp else "on another rank") + "): NCCL all-gather instead"
-            log(gather_note)
+    gather, gather_note = args.gather_mode, args.gather_note
     cap = 4 if world > 1 else 5  # steps per captured graph (even on several GPUs: the output buffers alternate)
     sweep, modes, verified, head = {}, {}, True, None
 
@@ -603,24 +588,42 @@ def run_single(cfg, args, rank, world, local_rank, peaks):
               for i in range(nbuf)]
     M = cfg.M
     xd = x.cuda()
-    outs = [torch.zeros(M, n_local, dtype=torch.bfloat16, device="cuda") for _ in range(2)]
     act = ActQuant(max(M, 128), cfg.K)
-    gathered = torch.empty(world, M, n_local, dtype=torch.bfloat16, device="cuda") if world > 1 else None
+    fused = world > 1 and args.gather_mode == "fused" and cfg.glu and M > 128 and (e - b) % 256 == 0
+    if fused:
+        # outputs in peer-mapped memory, two buffers used alternately; the GEMM's epilogue stores into the peers' copies too
+        from q27b200.peer import PeerRegion
+        from q27b200.q27lib import call
 
-    def step(i):
+        region = PeerRegion(2 * world * M * n_local * 2)
+        pay = region.payload()[:2 * world * M * n_local * 2].view(torch.bfloat16).view(2, world, M, n_local)
+        outs, gath = [pay[0][rank], pay[1][rank]], [pay[0], pay[1]]
+        peers, wait_slots = region.peers(), (ctypes.c_int * (world - 1))(*region.peer_slots())
+    else:
+        outs = [torch.zeros(M, n_local, dtype=torch.bfloat16, device="cuda") for _ in range(2)]
+        gath = [torch.empty(world, M, n_local, dtype=torch.bfloat16, device="cuda") for _ in range(2)] if world > 1 else None
+
+    def step(i, gather=True):
         q, sf = act.quantize(xd, in_scale)
-        layers[i % nbuf].gemm(M, q, sf, outs[i & 1])
-        if world > 1:
-            torch.distributed.all_gather_into_tensor(gathered.view(-1), outs[i & 1].view(-1))
+        lin, s_ = layers[i % nbuf], torch.cuda.current_stream().cuda_stream
+        if fused and gather:
+            call("q27b_gemm_fp4_glu_bf16_gather", M, lin.out, cfg.K, q, sf, lin.w, lin.sf, lin.alpha, lin.alpha, outs[i & 1],
+                 ctypes.byref(peers), s_)
+            call("q27b_group_gather_wait", region.ptrs[rank], world - 1, wait_slots, s_)
+        else:
+            lin.gemm(M, q, sf, outs[i & 1])
+            if world > 1 and gather:
+                torch.distributed.all_gather_into_tensor(gath[i & 1].view(-1), outs[i & 1].view(-1))
 
     q0, sf0 = act.quantize(xd, in_scale)
 
     def gemm_only(i):
         layers[i % nbuf].gemm(M, q0, sf0, outs[i & 1])
 
+    total_bytes, flops = cfg.algorithmic_bytes(), cfg.flops()
     # how many steps make a region of MIN_REGION_MS: from a short graph-replayed run
     est = timed(step, 40, 5, world, graph_cap=40) / 40
-    per = int(min(200, max(10, MIN_REGION_MS / max(est, 1e-4) / 4)))
+    per = int(min(200, max(10, MIN_REGION_MS / max(est, 1e-4) / 4))) // 2 * 2  # (even: the output buffers alternate)
     steps = per * max(1, math.ceil(MIN_REGION_MS / max(est, 1e-4) / per))
     with ClockSampler(local_rank) as clk:
         ms = timed(step, steps, args.warmup, world, graph_cap=per)
@@ -634,11 +637,28 @@ def run_single(cfg, args, rank, world, local_rank, peaks):
         layers[last % nbuf].gemm(M, q, sf, want)
         torch.cuda.synchronize()
     ok = bool(torch.equal(got, want)) and bool(got.any())
+    extra = {}
     if world > 1:
-        ok = ok and bool(torch.equal(gathered[rank], want))
+        ref_all = torch.empty(world, M, n_local, dtype=torch.bfloat16, device="cuda")
+        torch.distributed.all_gather_into_tensor(ref_all.view(-1), want.view(-1))
+        ok = ok and bool(torch.equal(gath[last & 1], ref_all))  # every rank holds every rank's block
         flag = torch.tensor([int(ok)], device="cuda")
         torch.distributed.all_reduce(flag, op=torch.distributed.ReduceOp.MIN)
         ok = bool(flag.item())
+        ms_ng = timed(lambda i: step(i, gather=False), steps, args.warmup, world, graph_cap=per)
+        extra["without_gather"] = {"value": flops / (ms_ng / steps / 1e3) / 1e12 if M > 128 else cfg.algorithmic_bytes() / (ms_ng / steps / 1e3) / 1e9,
+                                   "ms_per_step": ms_ng / steps}
+        if fused:  # the same step with one NCCL all-gather after the GEMM instead
+            g2 = torch.empty(world, M, n_local, dtype=torch.bfloat16, device="cuda")
+
+            def step_nccl(i):
+                q, sf = act.quantize(xd, in_scale)
+                layers[i % nbuf].gemm(M, q, sf, outs[i & 1])
+                torch.distributed.all_gather_into_tensor(g2.view(-1), outs[i & 1].view(-1))
+
+            ms_nc = timed(step_nccl, steps, args.warmup, world, graph_cap=per)
+            extra["with_nccl_all_gather"] = {"value": flops / (ms_nc / steps / 1e3) / 1e12 if M > 128 else cfg.algorithmic_bytes() / (ms_nc / steps / 1e3) / 1e9,
+                                             "ms_per_step": ms_nc / steps}
     ms_gemm = timed(gemm_only, steps, args.warmup, world, graph_cap=per)
     grouped = None
     if world == 1 and M <= 128:
@@ -678,7 +698,6 @@ def run_single(cfg, args, rank, world, local_rank, peaks):
         grouped = best
     assert device_status() == 0, "a bounded wait inside a kernel ran out"
     per_step_s, gemm_s = ms / steps / 1e3, ms_gemm / steps / 1e3
-    total_bytes, flops = cfg.algorithmic_bytes(), cfg.flops()
     tensor_bound = M > 128
     n_rows_local = e - b
     launch_bytes = n_rows_local * cfg.K // 2 + n_rows_local * cfg.K // 16 + 2 * M * cfg.K + 2 * M * n_local
@@ -704,9 +723,11 @@ def run_single(cfg, args, rank, world, local_rank, peaks):
         value, unit, metric = flops / per_step_s / 1e12, "TFLOP/s", "nvfp4_gemm_tflops"
     res = {"workload": cfg.name, "metric": metric, "value": value, "unit": unit, "ms_per_step": ms / steps, "steps": steps,
            "timed_region_ms": ms, "step": "quant_fp4_bf16 + " + ("skinny_fp4" if M <= 128 else "gemm_fp4") + ("_glu_bf16" if cfg.glu else "_bf16")
-           + (" + all-gather (NCCL, in the graph)" if world > 1 else ""),
+           + ("" if world == 1 else " with the gather fused into its epilogue (peer stores) + wait for the peers" if fused
+              else " + all-gather (NCCL, in the graph)"),
            "l2": f"weights rotate through {nbuf} distinct copies ({nbuf * layers[0].weight_bytes() / 2**20:.0f} MiB per GPU > 126 MiB L2)",
            "roofline": roof, "clocks": clocks, "verified": ok}
+    res.update(extra)
     if grouped:
         res["grouped_over_the_weight_copies"] = grouped
     log(f"{cfg.name}: {value:.1f} {unit}, GEMM {gemm_s * 1e6:.2f} us, frac {roof['frac']:.3f}, verified {ok}"
@@ -769,6 +790,30 @@ def cpu_sweep_sample(M, steps, warmup, frac_rows=8):
     return nbytes / dt / 1e9, dt, cores, desc
 
 
+def pick_gather(requested, world):
+    """How every rank gets every rank's outputs on several GPUs: "fused" (peer stores from the epilogues) needs
+    peer-mapped memory, set up through torch's symmetric memory; where that is not available on a box every rank falls
+    back to the NCCL all-gather together (and the line says so)."""
+    if world == 1:
+        return "none", None
+    if requested != "fused":
+        return requested, None
+    try:
+        from q27b200.peer import PeerRegion
+        probe = PeerRegion(4096)
+        okp, why = (len(probe.ptrs) == world), "unexpected pointer table"
+        del probe
+    except Exception as e:  # noqa: BLE001
+        okp, why = False, f"{type(e).__name__}: {e}"
+    flag = torch.tensor([int(okp)], device="cuda")
+    torch.distributed.all_reduce(flag, op=torch.distributed.ReduceOp.MIN)
+    if bool(flag.item()):
+        return "fused", None
+    note = "peer-mapped memory could not be set up (" + (why if not okp else "on another rank") + "): NCCL all-gather instead"
+    log(note)
+    return "nccl", note
+
+
 def workload_name(layers, M):
     return f"cfg3 decode weight sweep, {layers} layers x (q|k|v, o, gate_up, down), M={M}"
 
@@ -820,6 +865,7 @@ def main():
     if world > 1:
         torch.distributed.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
     peaks = measured_peaks()
+    args.gather_mode, args.gather_note = pick_gather(args.gather, world)
     only = [s for s in args.only.split(",") if s]
     want = lambda name: not only or name in only  # noqa: E731
 

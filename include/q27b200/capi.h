@@ -213,6 +213,14 @@ int q27b_skinny_fp4_group_gather(const void* table_host, const void* table_dev, 
                                  const q27b_group_peers* peers, void* stream);
 /* peer_slots: the n_peers slots (0..7) to wait for; HOST array. */
 int q27b_group_gather_wait(int32_t* signals, int n_peers, const int* peer_slots, void* stream);
+/* The same for the prefill gate | up GEMM (q27b_gemm_fp4_glu_bf16 on CTA pairs: M > 128, 2 I a multiple of 256): its
+ * epilogue stores every 32-byte piece of the bf16 output into the peers' copies as well, the last CTA raises the
+ * signal, q27b_group_gather_wait waits for the peers. d must lie in the peer-mirrored region. At 8 GPUs the floor of
+ * this step is the transfer itself (7/8 of the 142.6 MB output into every GPU: 162 us at the 770 GB/s a peer copy
+ * reaches here), against about 50 us of GEMM per GPU. */
+int q27b_gemm_fp4_glu_bf16_gather(int M, int I, int K, const uint8_t* a, const uint8_t* a_sf, const uint8_t* gate_up,
+                                  const uint8_t* gate_up_sf, float alpha_gate, float alpha_up, void* d,
+                                  const q27b_group_peers* peers, void* stream);
 
 /* d[m][n] = (A . W^T)[m][n] * (wscale[n] * ascale[m]), fp32: per-output-channel weight scales and per-token
  * activation scales (weights quantised at load, activations quantised dynamically). Replaces skinny_fp4_scaled

@@ -77,6 +77,13 @@ struct GemmParams {
   int m_tiles, items;   // many rows
   int n_tile;           // many rows: weight rows per tile (128 or 256)
   int ext_reduce;       // weight streaming: cut tiles are summed by skinny_fixup_kernel, not by the last CTA to arrive
+  // many rows, gather fused into the epilogue (several GPUs; see q27b_group_peers): bf16 stores are repeated into the
+  // peers' memory, and the last CTA of the launch raises this GPU's word in every peer's signal block
+  int n_peers;
+  long long peer_delta[7];
+  int32_t* signals;
+  int32_t* peer_signals[7];
+  int my_slot;
 #ifdef Q27B_TRACE
   unsigned long long* trace;  // [cta][4][64] globaltimer samples (null: off)
 #endif
@@ -315,6 +322,11 @@ __device__ __forceinline__ void emit_many(const GemmParams& p, int m, bool valid
     uint4* d = reinterpret_cast<uint4*>(static_cast<uint16_t*>(p.d) + int64_t(m) * (p.N / 2) + (q_row0 + c0) / 2 + (c0 & 63) / 2);
     d[0] = make_uint4(pk[0], pk[1], pk[2], pk[3]);
     d[1] = make_uint4(pk[4], pk[5], pk[6], pk[7]);
+    for (int j = 0; j < p.n_peers; j++) {  // the same 32 bytes into every peer's copy of the output (plain peer stores)
+      uint4* dp = reinterpret_cast<uint4*>(reinterpret_cast<char*>(d) + p.peer_delta[j]);
+      dp[0] = make_uint4(pk[0], pk[1], pk[2], pk[3]);
+      dp[1] = make_uint4(pk[4], pk[5], pk[6], pk[7]);
+    }
   } else {
     const int n0 = q_row0 + c0;
     float out[16];
@@ -973,6 +985,16 @@ __global__ void __launch_bounds__(Cfg2<STAGES>::kThreads, 1) umma_gemm2_kernel(c
     tc_fence_after_sync();
     tmem_dealloc_2sm(tmem_base, C::kTmemCols);
   }
+  if (p.n_peers > 0 && threadIdx.x == 0) {
+    // every store of this CTA (local and into the peers) is ordered before the count; the CTA that counts last orders
+    // all of them before it raises this GPU's word in every peer's signal block (words as in skinny_group.inl)
+    __threadfence_system();
+    if (atomicAdd(p.signals + 9, 1) == int(gridDim.x) - 1) {
+      p.signals[9] = 0;
+      __threadfence_system();
+      for (int j = 0; j < p.n_peers; j++) atomicAdd_system(p.peer_signals[j] + p.my_slot, 1);
+    }
+  }
 }
 
 // Self-test of the bounded waits: one thread waits on a barrier that nothing ever arrives at, with a short budget;
@@ -1151,7 +1173,7 @@ int check_operands(const char* what, int M, int N, int K, const void* a, const v
 
 int many_common(int kEpi, int M, int N, int K, const uint8_t* a, const uint8_t* a_sf, const uint8_t* w,
                 const uint8_t* w_sf, float alpha, float alpha_up, const float* c, float beta, void* d, cudaStream_t s,
-                uint8_t* d_sf, float out_scale);
+                uint8_t* d_sf, float out_scale, const q27b_group_peers* peers = nullptr);
 
 int skinny_common(int kEpi, int M, int N, int K, const uint8_t* a, const uint8_t* a_sf, const uint8_t* w,
                   const uint8_t* w_sf, const AlphaSeg& alpha, float alpha_up, const float* c, float beta, void* d,
@@ -1252,7 +1274,7 @@ int run_many(const uint8_t* a, const uint8_t* w, GemmParams& p, cudaStream_t s) 
 
 int many_common(int kEpi, int M, int N, int K, const uint8_t* a, const uint8_t* a_sf, const uint8_t* w,
                 const uint8_t* w_sf, float alpha, float alpha_up, const float* c, float beta, void* d, cudaStream_t s,
-                uint8_t* d_sf, float out_scale) {
+                uint8_t* d_sf, float out_scale, const q27b_group_peers* peers) {
   Q27B_REQUIRE(M >= 0, "gemm_fp4: M must not be negative");
   if (M == 0) return 0;
   if (int rc = check_operands("gemm_fp4", M, N, K, a, a_sf, w, w_sf, d)) return rc;
@@ -1264,6 +1286,13 @@ int many_common(int kEpi, int M, int N, int K, const uint8_t* a, const uint8_t* 
   p.c = (c && beta != 0.f) ? c : nullptr, p.beta = beta, p.d = d;
   p.m_tiles = (M + 127) / 128;
   p.d_sf = d_sf, p.out_gs = 1.f / out_scale;  // (IEEE division, as the quantiser kernels compute it)
+  if (peers) {
+    Q27B_REQUIRE(kEpi == kEpiGluBf16 && N % 256 == 0 && M > 128, "gemm_fp4 gather: the SiLU*mul bf16 GEMM on CTA pairs only (M > 128, 2 I a multiple of 256)");
+    const char* force = getenv("Q27B_MANY");
+    Q27B_REQUIRE(!force || !*force || !strcmp(force, "pairs"), "gemm_fp4 gather: Q27B_MANY forces a kernel without the fused gather");
+    p.n_peers = peers->n_peers, p.signals = peers->signals, p.my_slot = peers->my_slot;
+    for (int j = 0; j < peers->n_peers; j++) p.peer_delta[j] = peers->out_delta[j], p.peer_signals[j] = peers->peer_signals[j];
+  }
 #ifdef Q27B_TRACE
   p.trace = g_trace;
 #endif
@@ -1356,6 +1385,17 @@ int q27b_gemm_fp4_glu_bf16(int M, int I, int K, const uint8_t* a, const uint8_t*
   Q27B_REQUIRE(I > 0 && I % 64 == 0, "gemm_fp4_glu_bf16: I must be a positive multiple of 64 (I = %d)", I);
   return many_common(kEpiGluBf16, M, 2 * I, K, a, a_sf, gate_up, gate_up_sf, alpha_gate, alpha_up, nullptr, 0.f, d,
                      static_cast<cudaStream_t>(stream), nullptr, 1.f);
+}
+int q27b_gemm_fp4_glu_bf16_gather(int M, int I, int K, const uint8_t* a, const uint8_t* a_sf, const uint8_t* gate_up,
+                                  const uint8_t* gate_up_sf, float alpha_gate, float alpha_up, void* d,
+                                  const q27b_group_peers* peers, void* stream) {
+  Q27B_REQUIRE(I > 0 && I % 64 == 0, "gemm_fp4_glu_bf16_gather: I must be a positive multiple of 64 (I = %d)", I);
+  Q27B_REQUIRE(peers && peers->n_peers >= 1 && peers->n_peers <= 7 && peers->signals && peers->my_slot >= 0 && peers->my_slot < 8,
+               "gemm_fp4_glu_bf16_gather: 1..7 peers, a signal block and a slot 0..7");
+  for (int j = 0; j < peers->n_peers; j++)
+    Q27B_REQUIRE(peers->peer_signals[j] && peers->out_delta[j] % 16 == 0, "gemm_fp4_glu_bf16_gather: peer %d: null signal block or misaligned delta", j);
+  return many_common(kEpiGluBf16, M, 2 * I, K, a, a_sf, gate_up, gate_up_sf, alpha_gate, alpha_up, nullptr, 0.f, d,
+                     static_cast<cudaStream_t>(stream), nullptr, 1.f, peers);
 }
 int q27b_gemm_fp4_glu(int M, int I, int K, const uint8_t* a, const uint8_t* a_sf, const uint8_t* gate_up,
                       const uint8_t* gate_up_sf, float alpha_gate, float alpha_up, float out_scale, uint8_t* q,

@@ -45,6 +45,7 @@ SIGNATURES = {
     "q27t_skinny_fp4_group": ([P, P, P, SZ], I),
     "q27b_skinny_fp4_group_gather": ([P, P, P, SZ, P, P], I),
     "q27b_group_gather_wait": ([P, I, P, P], I),
+    "q27b_gemm_fp4_glu_bf16_gather": ([I, I, I, P, P, P, P, F, F, P, P, P], I),
     "q27b_gemm_fp4": ([I, I, I, P, P, P, P, F, P, F, P, P], I),
     "q27b_gemm_fp4_bf16": ([I, I, I, P, P, P, P, F, P, P], I),
     "q27b_gemm_fp4_glu_bf16": ([I, I, I, P, P, P, P, F, F, P, P], I),

@@ -322,11 +322,7 @@ __device__ __forceinline__ void emit_many(const GemmParams& p, int m, bool valid
     uint4* d = reinterpret_cast<uint4*>(static_cast<uint16_t*>(p.d) + int64_t(m) * (p.N / 2) + (q_row0 + c0) / 2 + (c0 & 63) / 2);
     d[0] = make_uint4(pk[0], pk[1], pk[2], pk[3]);
     d[1] = make_uint4(pk[4], pk[5], pk[6], pk[7]);
-    for (int j = 0; j < p.n_peers; j++) {  // the same 32 bytes into every peer's copy of the output (plain peer stores)
-      uint4* dp = reinterpret_cast<uint4*>(reinterpret_cast<char*>(d) + p.peer_delta[j]);
-      dp[0] = make_uint4(pk[0], pk[1], pk[2], pk[3]);
-      dp[1] = make_uint4(pk[4], pk[5], pk[6], pk[7]);
-    }
+
   } else {
     const int n0 = q_row0 + c0;
     float out[16];
@@ -728,7 +724,9 @@ struct Cfg2 {
   static constexpr int kOffQ = kPBytes, kOffSfP = kPBytes + kQBytes, kOffSfQ = kOffSfP + kSfBytes;
   static constexpr int kSfCols = 48;
   static constexpr int kNumBars = 3 * STAGES + 2;
-  static constexpr int kSmemBytes = STAGES * kStageBytes + kNumBars * 8 + 16 + 1024;
+  static constexpr int kOutOff = STAGES * kStageBytes + (kNumBars * 8 + 16 + 15) / 16 * 16;  // staging of an output tile
+  static constexpr int kOutBytes = 128 * 256;  // 128 tokens x 128 bf16 outputs (SiLU*mul epilogue)
+  static constexpr int kSmemBytes = kOutOff + kOutBytes + 1024;
   static constexpr int kTmemCols = 512, kSfCol0 = 256;
   static constexpr int kEpiWarps = 16, kFeederWarp0 = 2 + kEpiWarps, kThreads = (kFeederWarp0 + 4) * 32;
   static_assert(kStageBytes % 1024 == 0, "stage tiles must stay 1024-byte aligned");
@@ -969,10 +967,47 @@ __global__ void __launch_bounds__(Cfg2<STAGES>::kThreads, 1) umma_gemm2_kernel(c
         else mbar_arrive_remote(aempty, 0);
       }
       if (warp == 2 && lane == 0 && ntiles < 4) TRACE(3, 8 + ntiles);
+      if constexpr (kEpi == kEpiGluBf16) {
+        // The CTA's 128 tokens x 128 outputs go through shared memory so that global memory (this GPU's and, with the
+        // fused gather, the peers') is written in whole 256-byte rows: a lane holds one token, so direct stores would
+        // be 32-byte pieces of 32 different rows per instruction - 1.4 x the bytes in local DRAM traffic, and far worse
+        // as NVLink packets. 16-byte chunks are XOR-swizzled by the row so that neither side has bank conflicts.
+        uint8_t* stage_out = smem + C::kOutOff;
+        const float ag = p.alpha.alpha[0], au = p.alpha_up;
+        asm volatile("bar.sync 3, %0;" ::"r"(C::kEpiWarps * 32) : "memory");  // the previous tile has left the staging area
 #pragma unroll
-      for (int j = 0; j < kMine; j++) {
-        const int un = sub + 4 * j, c0 = kGlu ? (un >> 2) * 128 + (un & 3) * 16 : un * 16;
-        emit_many<kEpi>(p, m, m < p.M, n0, c0, g[j], u[kGlu ? j : 0]);
+        for (int j = 0; j < kMine; j++) {
+          const int un = sub + 4 * j, chunk0 = (un >> 2) * 8 + (un & 3) * 2;  // first of the unit's two 16-byte chunks
+          uint32_t pk[8];
+#pragma unroll
+          for (int i = 0; i < 8; i++) {
+            const uint32_t lo = bf16_bits(silu_mul(__fmul_rn(ag, g[j][2 * i]), __fmul_rn(au, u[j][2 * i])));
+            const uint32_t hi = bf16_bits(silu_mul(__fmul_rn(ag, g[j][2 * i + 1]), __fmul_rn(au, u[j][2 * i + 1])));
+            pk[i] = lo | (hi << 16);
+          }
+          uint4* r = reinterpret_cast<uint4*>(stage_out + row * 256);
+          r[chunk0 ^ (row & 15)] = make_uint4(pk[0], pk[1], pk[2], pk[3]);
+          r[(chunk0 + 1) ^ (row & 15)] = make_uint4(pk[4], pk[5], pk[6], pk[7]);
+        }
+        asm volatile("bar.sync 3, %0;" ::"r"(C::kEpiWarps * 32) : "memory");
+        const int m_base = (item % m_pairs) * 256 + int(rank) * 128, chunk = lane & 15;
+        uint16_t* out0 = static_cast<uint16_t*>(p.d) + n0 / 2 + chunk * 8;
+#pragma unroll
+        for (int it = 0; it < 4; it++) {  // a warp copies 8 rows, two per instruction: 2 x 256 contiguous bytes
+          const int r = (warp - 2) * 8 + it * 2 + (lane >> 4), mr = m_base + r;
+          if (mr < p.M) {
+            const uint4 v = reinterpret_cast<const uint4*>(stage_out + r * 256)[chunk ^ (r & 15)];
+            uint4* dst = reinterpret_cast<uint4*>(out0 + int64_t(mr) * (p.N / 2));
+            *dst = v;
+            for (int q = 0; q < p.n_peers; q++) *reinterpret_cast<uint4*>(reinterpret_cast<char*>(dst) + p.peer_delta[q]) = v;
+          }
+        }
+      } else {
+#pragma unroll
+        for (int j = 0; j < kMine; j++) {
+          const int un = sub + 4 * j, c0 = kGlu ? (un >> 2) * 128 + (un & 3) * 16 : un * 16;
+          emit_many<kEpi>(p, m, m < p.M, n0, c0, g[j], u[kGlu ? j : 0]);
+        }
       }
     }
   }

@@ -661,7 +661,7 @@ def run_single(cfg, args, rank, world, local_rank, peaks):
                                              "ms_per_step": ms_nc / steps}
     ms_gemm = timed(gemm_only, steps, args.warmup, world, graph_cap=per)
     grouped = None
-    if world == 1 and M <= 128:
+    if world == 1 and M <= 128 and MIN_REGION_MS >= 20.0:
         # The same GEMM on all the rotating weight copies as ONE grouped launch (behind one quantiser launch): what the
         # shape streams at once the launch boundaries are out of the way. One launch = nbuf GEMMs; reported per GEMM.
         from q27b200.group import Fp4Group, problem_of
@@ -716,7 +716,7 @@ def run_single(cfg, args, rank, world, local_rank, peaks):
         launch_flops = 2 * M * n_rows_local * cfg.K
         achieved = launch_flops / gemm_s / 1e12
         roof = {"bound": "tensor", "achieved": achieved, "peak": tpeak, "unit": "TFLOP/s", "frac": achieved / tpeak,
-                "traffic": None, "algorithmic_flops": launch_flops, "kernel": "umma_gemm2_kernel (many rows, CTA pairs)",
+                "traffic": ncu_traffic().get(f"cfg{cfg.index}") if world == 1 else None, "algorithmic_flops": launch_flops, "kernel": "umma_gemm2_kernel (many rows, CTA pairs)",
                 "us_per_launch": gemm_s * 1e6, "peak_sustained": 4.0 * peaks["bf16_tflops_sustained"],
                 "frac_of_sustained": achieved / (4.0 * peaks["bf16_tflops_sustained"]),
                 "peak_source": "4 x bf16_tflops (burst) of " + peaks["source"] + "; no FP4 peak is measured on this pool, nominal dense FP4 is 9000"}
@@ -832,8 +832,11 @@ def main():
                     help="several GPUs: how every rank gets every rank's outputs at the end of a step of the sweep")
     ap.add_argument("--cpu-steps", type=int, default=20)
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg (profiling runs)")
+    ap.add_argument("--region-ms", type=float, default=MIN_REGION_MS,
+                    help="single-GEMM configurations are replayed until their timed region is this long (profiling runs: a few ms)")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)
+    globals()["MIN_REGION_MS"] = args.region_ms
 
     from q27b200 import configs
 

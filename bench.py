@@ -175,11 +175,14 @@ def timed(fn, steps, warmup, world, graph=True, graph_cap=None, busy_ms=0.0):
         g.replay()  # once untimed
         sync_all(world)
         if busy_ms > 0:
+            # the number of untimed replays is agreed between the ranks (their steps may contain a gather: every rank must
+            # run the same number of them)
             t0 = time.perf_counter()
-            while (time.perf_counter() - t0) * 1e3 < busy_ms:
-                for _ in range(4):
-                    g.replay()
-                torch.cuda.synchronize()
+            g.replay()
+            torch.cuda.synchronize()
+            one = max_over_ranks((time.perf_counter() - t0) * 1e3, world)
+            for _ in range(int(min(2000, max(1, busy_ms / max(one, 1e-3))))):
+                g.replay()
             sync_all(world)
 
         def run():

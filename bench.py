@@ -349,7 +349,7 @@ class Sweep:
                 for n in self.NAMES:
                     a = self.act[l][self.src[n]]
                     probs.append(problem_of(self.model[l][n], a.q, a.sf, self.outs[b][l][n]))
-            self._groups[key] = Fp4Group(self.M, probs, whole_tiles=self.whole_tiles(l1 - l0))
+            self._groups[key] = Fp4Group(self.M, probs, whole_tiles=self.whole_tiles(l1 - l0), tokens_on_n=self.fused)  # (256-row tiles have no fused gather)
         return self._groups[key]
 
     def drop_groups(self):

@@ -66,10 +66,13 @@ struct GroupSchedule {
 };
 
 // The pieces of one problem exactly as its stand-alone launch cuts them, in (tile, K) order.
-inline void problem_pieces(int prob, const GroupShape& s, int cta_slots, bool whole_tiles, int64_t& next_slot,
+inline void problem_pieces(int prob, const GroupShape& s, int cta_slots, bool whole_tiles, int tile_rows, int64_t& next_slot,
                            int& next_counter, std::vector<GroupItem>& out) {
   SkinnyPlan plan = choose_skinny_plan(s.N, s.K, cta_slots);
-  if (whole_tiles) plan.split = 1, plan.grid = plan.tiles < cta_slots ? plan.tiles : cta_slots;  // every tile in one piece
+  if (whole_tiles) {  // every tile in one piece (tiles of tile_rows weight rows: 128, or 256 for the many-row roles)
+    plan.tiles = s.N / tile_rows, plan.units = int64_t(plan.tiles) * plan.chunks;
+    plan.split = 1, plan.grid = plan.tiles < cta_slots ? plan.tiles : cta_slots;
+  }
   std::vector<GroupItem> pieces;
   for (int g = 0; g < plan.grid; g++) {
     int64_t u = -1;
@@ -104,12 +107,13 @@ inline void problem_pieces(int prob, const GroupShape& s, int cta_slots, bool wh
 }
 
 // Deals the pieces of all problems to at most `cta_slots` CTAs (the CTAs that can be resident at once).
-inline GroupSchedule schedule_group(const GroupShape* shapes, int n, int cta_slots, bool whole_tiles = false, bool rotate = false) {
+inline GroupSchedule schedule_group(const GroupShape* shapes, int n, int cta_slots, bool whole_tiles = false, bool rotate = false,
+                                    int tile_rows = 128) {
   GroupSchedule sch;
   std::vector<GroupItem> all;
   int64_t next_slot = 0;
   int next_counter = 0;
-  for (int p = 0; p < n; p++) problem_pieces(p, shapes[p], cta_slots, whole_tiles, next_slot, next_counter, all);
+  for (int p = 0; p < n; p++) problem_pieces(p, shapes[p], cta_slots, whole_tiles, tile_rows, next_slot, next_counter, all);
   sch.slots = next_slot, sch.counters = next_counter;
   const int ctas = int(std::min<size_t>(size_t(cta_slots), all.size()));
   // longest piece first onto the CTA with the least to stream (ties: the lower index)

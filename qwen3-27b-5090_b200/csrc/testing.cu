@@ -93,10 +93,10 @@ int q27b_skinny_group_plan(int n, const int* N, const int* K, int slots, int who
   if (n <= 0 || !N || !K || slots <= 0) return fail("skinny_group_plan: bad arguments");
   std::vector<GroupShape> shapes(n);
   for (int i = 0; i < n; i++) {
-    if (N[i] <= 0 || N[i] % 128 || K[i] <= 0 || K[i] % 64) return fail("skinny_group_plan: bad shape");
+    if (N[i] <= 0 || N[i] % (whole_tiles == 2 ? 256 : 128) || K[i] <= 0 || K[i] % 64) return fail("skinny_group_plan: bad shape");
     shapes[i] = {N[i], K[i]};
   }
-  const GroupSchedule sch = schedule_group(shapes.data(), n, slots, whole_tiles != 0, rotate != 0);
+  const GroupSchedule sch = schedule_group(shapes.data(), n, slots, whole_tiles != 0, rotate != 0, whole_tiles == 2 ? 256 : 128);
   if (ctas_out) *ctas_out = int(sch.cta_units.size());
   if (slots_out) *slots_out = sch.slots;
   if (counters_out) *counters_out = sch.counters;

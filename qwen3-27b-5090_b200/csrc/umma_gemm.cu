@@ -1340,6 +1340,7 @@ int many_common(int kEpi, int M, int N, int K, const uint8_t* a, const uint8_t* 
 }
 
 #include "skinny_group.inl"
+#include "wide_group.inl"
 
 AlphaSeg make_alpha(int count, const int* begin, const float* alpha) {
   AlphaSeg a = {};
@@ -1456,7 +1457,7 @@ int q27b_trace_set(void* buf) {
 
 int q27b_skinny_group_build(int M, int n_problems, const q27b_group_problem* problems, int flags, void* table_host,
                             size_t table_cap, size_t* table_bytes, size_t* ws_bytes) {
-  Q27B_REQUIRE((flags & ~Q27B_GROUP_WHOLE_TILES) == 0, "skinny_group: unknown flags 0x%x", flags);
+  Q27B_REQUIRE((flags & ~(Q27B_GROUP_WHOLE_TILES | Q27B_GROUP_TOKENS_ON_N)) == 0, "skinny_group: unknown flags 0x%x", flags);
   Q27B_REQUIRE(M >= 1 && M <= 128, "skinny_group: M must be 1..128 (M = %d)", M);
   Q27B_REQUIRE(n_problems >= 1 && n_problems <= kGroupMaxProblems && problems, "skinny_group: 1..%d problems", kGroupMaxProblems);
   const int sms = sm_count();
@@ -1466,10 +1467,15 @@ int q27b_skinny_group_build(int M, int n_problems, const q27b_group_problem* pro
     if (int rc = check_group_problem(i, problems[i])) return rc;
     shapes[i] = {problems[i].N, problems[i].K};
   }
-  const GroupSchedule sch = schedule_group(shapes.data(), n_problems, 2 * sms, (flags & Q27B_GROUP_WHOLE_TILES) != 0);
+  // 65..128 tokens, whole tiles, every weight a multiple of 256 rows: the many-row roles (tokens on the MMA's M side,
+  // 256 weight rows per tile, one CTA per SM) bring fewer activation bytes into the SM per weight byte (wide_group.inl)
+  bool wide = (flags & Q27B_GROUP_WHOLE_TILES) && !(flags & Q27B_GROUP_TOKENS_ON_N) && M > 64;
+  for (int i = 0; wide && i < n_problems; i++) wide = problems[i].N % 256 == 0;
+  const GroupSchedule sch = wide ? schedule_group(shapes.data(), n_problems, sms, true, false, 256)
+                                 : schedule_group(shapes.data(), n_problems, 2 * sms, (flags & Q27B_GROUP_WHOLE_TILES) != 0);
   const int ctas = int(sch.cta_units.size());
   GroupHeader h = {};
-  h.magic = kGroupMagic, h.M = M, h.nb = group_tokens_tile(M), h.n_problems = n_problems, h.n_ctas = ctas;
+  h.magic = kGroupMagic, h.M = M, h.nb = wide ? 256 : group_tokens_tile(M), h.n_problems = n_problems, h.n_ctas = ctas;
   h.n_items = int(sch.items.size()), h.counters = sch.counters, h.sms = sms, h.slots = sch.slots;
   h.imbalance_permille = int(sch.imbalance() * 1000.0 + 0.5);
   h.off_problems = sizeof(GroupHeader);
@@ -1492,8 +1498,8 @@ int q27b_skinny_group_build(int M, int n_problems, const q27b_group_problem* pro
     Q27B_REQUIRE(aligned16(q.a) && aligned16(q.a_sf) && aligned16(q.w) && aligned16(q.w_sf) && aligned16(q.d) && aligned16(q.c),
                  "skinny_group: problem %d: operands, scales, residual and output must be 16-byte aligned", i);
     GroupProblemDev d = {};
-    if (int rc = make_operand_map(&d.tmap_w, q.w, q.N, q.K, 128)) return rc;
-    if (int rc = make_operand_map(&d.tmap_a, q.a, M, q.K, h.nb)) return rc;
+    if (int rc = make_operand_map(&d.tmap_w, q.w, q.N, q.K, wide ? 256 : 128)) return rc;
+    if (int rc = make_operand_map(&d.tmap_a, q.a, M, q.K, wide ? 128 : h.nb)) return rc;
     d.d = q.d, d.c = (q.c && q.beta != 0.f) ? q.c : nullptr, d.beta = q.beta;
     d.alpha = make_alpha(q.alpha_count, q.alpha_begin, q.alpha), d.alpha_up = q.alpha_up;
     d.N = q.N, d.epi = q.epilogue == 2 ? kEpiGluBf16 : q.epilogue == 1 ? kEpiBf16 : kEpiF32;
@@ -1506,7 +1512,7 @@ int q27b_skinny_group_build(int M, int n_problems, const q27b_group_problem* pro
   for (int i = 0; i < h.n_items; i++) {
     GroupItem it = sch.items[i];
     const q27b_group_problem& q = problems[it.prob];
-    it.w_sf_tile = q.w_sf + int64_t(it.tile) * it.ksteps * 512;
+    it.w_sf_tile = q.w_sf + int64_t(it.tile) * (wide ? 2 : 1) * it.ksteps * 512;
     it.a_sf = q.a_sf;
     items[i] = it;
   }
@@ -1573,7 +1579,10 @@ static int group_launch(const void* table_host, const void* table_dev, void* ws,
     case 16: return launch_group<16, 4>(gl, h.n_ctas, s);
     case 32: return launch_group<32, 4>(gl, h.n_ctas, s);
     case 64: return launch_group<64, 3>(gl, h.n_ctas, s);
-    default: return launch_group<128, 3>(gl, h.n_ctas, s);
+    case 128: return launch_group<128, 3>(gl, h.n_ctas, s);
+    default:
+      Q27B_REQUIRE(!peers, "skinny_group_gather: a table planned with 256-row tiles has no fused gather; build it with Q27B_GROUP_TOKENS_ON_N");
+      return launch_wide_group(gl, h.n_ctas, s);
   }
 }
 

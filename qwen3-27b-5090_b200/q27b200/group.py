@@ -16,6 +16,7 @@ from .q27lib import call
 
 EPI_F32, EPI_BF16, EPI_GLU_BF16 = 0, 1, 2
 WHOLE_TILES = 1  # Q27B_GROUP_WHOLE_TILES
+TOKENS_ON_N = 2  # Q27B_GROUP_TOKENS_ON_N
 
 
 class GroupProblem(ctypes.Structure):
@@ -53,11 +54,13 @@ class Fp4Group:
     GroupProblem; the tensors they point to must stay alive (and in place) as long as the group is used."""
 
     def __init__(self, M: int, problems: list[GroupProblem], device="cuda", workspace: torch.Tensor | None = None,
-                 whole_tiles: bool = False):
+                 whole_tiles: bool = False, tokens_on_n: bool = False):
         """whole_tiles: no tile is cut along K (for groups of several layers: fastest, and bit-identical to the
-        many-row GEMM instead of to the weight-streaming launch)."""
+        many-row GEMM instead of to the weight-streaming launch). With whole tiles and 65..128 tokens the group is
+        planned on tiles of 256 weight rows with the tokens on the MMA's M side (`self.tokens_tile == 256`) unless
+        tokens_on_n is set, which the fused gather needs; the results are the same bits either way."""
         self.M, self.n = M, len(problems)
-        flags = WHOLE_TILES if whole_tiles else 0
+        flags = (WHOLE_TILES if whole_tiles else 0) | (TOKENS_ON_N if tokens_on_n else 0)
         arr = (GroupProblem * self.n)(*problems)
         tb, wb = ctypes.c_size_t(), ctypes.c_size_t()
         call("q27b_skinny_group_build", M, self.n, arr, flags, None, 0, ctypes.byref(tb), ctypes.byref(wb))

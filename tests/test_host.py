@@ -304,3 +304,12 @@ def test_group_schedule_whole_tiles():
     for p in pieces:
         loads[p[0]] += p[4] - p[3]
     assert loads.max() == 68 and loads.max() > 1.9 * loads.sum() / 296
+    # tiles of 256 weight rows on one CTA per SM (65..128 tokens): half as many pieces of the same lengths
+    ctas, nslots, counters, pieces = group_plan(LAYER_SHAPES * 8, 148, whole=2)
+    assert ctas == 148 and nslots == 0 and counters == 0 and len(pieces) == 8 * 204
+    assert sorted(p[2] for p in pieces if p[1] == 2) == list(range(34816 // 256))
+    loads = np.zeros(ctas, dtype=np.int64)
+    for p in pieces:
+        assert p[3] == 0 and p[4] == chunks[p[1]]
+        loads[p[0]] += p[4]
+    assert loads.sum() == 8 * 5040 and loads.max() <= 1.07 * loads.mean()

@@ -177,7 +177,7 @@ typedef struct q27b_group_problem {
  * (q27b_gemm_fp4 / _bf16 / _glu_bf16) rather than to the weight-streaming launch. With few tiles (one layer) the
  * CTAs are loaded unevenly; the table's header reports the imbalance, and the default mode is the better choice. */
 #define Q27B_GROUP_WHOLE_TILES 1
-/* With WHOLE_TILES, 65..128 tokens and every weight a multiple of 256 rows the group is planned on tiles of
+/* With WHOLE_TILES, 33..128 tokens and every weight a multiple of 256 rows the group is planned on tiles of
  * 256 weight rows with the tokens on the MMA's M side (fewer activation bytes into the SM per weight byte). TOKENS_ON_N
  * keeps the few-token roles instead; the fused gather (q27b_skinny_fp4_group_gather) needs it. Same bits either way. */
 #define Q27B_GROUP_TOKENS_ON_N 2

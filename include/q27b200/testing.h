@@ -25,7 +25,7 @@ int q27b_skinny_plan(int N, int K, int slots, int cta, int* seg, int cap, int* g
 int q27b_skinny_tile_parts(int N, int K, int slots, int tile, int* slot, int cap);
 /* Schedule of a grouped launch over n problems of shapes (N[i], K[i]) for `slots` resident CTAs: writes up to `cap`
  * pieces as 9 ints each {cta, problem, tile, c0, c1, slot, nparts, slot0, sums}, grouped by CTA in the order the CTA
- * walks them (whole_tiles != 0: no tile is cut, see Q27B_GROUP_WHOLE_TILES, 2: tiles of 256 weight rows as planned for 65..128 tokens; problem order, the launcher's; rotate != 0: every CTA starts at a different point of its list, kept for
+ * walks them (whole_tiles != 0: no tile is cut, see Q27B_GROUP_WHOLE_TILES, 2: tiles of 256 weight rows as planned for 33..128 tokens; problem order, the launcher's; rotate != 0: every CTA starts at a different point of its list, kept for
  * experiments); sums = 1 marks the one piece of a cut tile whose CTA sums the tile; returns the number of pieces. ctas_out / slots_out / counters_out: CTAs launched, partial-tile slots and arrival
  * counters of the workspace. */
 int q27b_skinny_group_plan(int n, const int* N, const int* K, int slots, int whole_tiles, int rotate, int* pieces, int cap, int* ctas_out,

@@ -1467,9 +1467,9 @@ int q27b_skinny_group_build(int M, int n_problems, const q27b_group_problem* pro
     if (int rc = check_group_problem(i, problems[i])) return rc;
     shapes[i] = {problems[i].N, problems[i].K};
   }
-  // 65..128 tokens, whole tiles, every weight a multiple of 256 rows: the many-row roles (tokens on the MMA's M side,
+  // 33..128 tokens, whole tiles, every weight a multiple of 256 rows: the many-row roles (tokens on the MMA's M side,
   // 256 weight rows per tile, one CTA per SM) bring fewer activation bytes into the SM per weight byte (wide_group.inl)
-  bool wide = (flags & Q27B_GROUP_WHOLE_TILES) && !(flags & Q27B_GROUP_TOKENS_ON_N) && M > 64;
+  bool wide = (flags & Q27B_GROUP_WHOLE_TILES) && !(flags & Q27B_GROUP_TOKENS_ON_N) && M > env_int("Q27_GROUP_WIDE_ABOVE_M", 32, 0, 128);
   for (int i = 0; wide && i < n_problems; i++) wide = problems[i].N % 256 == 0;
   const GroupSchedule sch = wide ? schedule_group(shapes.data(), n_problems, sms, true, false, 256)
                                  : schedule_group(shapes.data(), n_problems, 2 * sms, (flags & Q27B_GROUP_WHOLE_TILES) != 0);

@@ -1,11 +1,13 @@
-// The grouped launch for 65..128 tokens (part of umma_gemm.cu, after skinny_group.inl): the same persistent walk over
+// The grouped launch for 33..128 tokens (part of umma_gemm.cu, after skinny_group.inl): the same persistent walk over
 // a device-side list of whole weight tiles, with the roles of the many-row GEMM - the tokens (one tile of 128) on the
 // MMA's M side, 256 weight rows per tile on its N side, one CTA per SM.
 //
 // Why a second form: with the tokens on the N side a stage brings 16 KiB of weights AND 16 KiB of activations into the
 // SM at 128 tokens, twice the weight bytes, and the stream stops at what an SM can ingest from L2 (58 % of the HBM
 // peak over the 64-layer sweep). A 256-row weight tile shares one activation tile: 1.5 bytes into the SM per weight
-// byte instead of 2, and 4 x 36 KiB of weights in flight per SM as in the few-token configuration.
+// byte instead of 2 (1.25 instead of 1.5 at 64 tokens: rows past M are not read), and 4 x 36 KiB of weights in flight
+// per SM as in the few-token configuration. Measured over the sweep: 83 % at 128 tokens, 91 % at 64 (tokens on N: 88 %),
+// 93 % at 32 (tokens on N: 101 %) - hence the planner takes this form from 33 tokens (Q27_GROUP_WIDE_ABOVE_M moves that).
 // Whole tiles only (Q27B_GROUP_WHOLE_TILES): every output is one accumulation chain over all of K, bit-identical to the
 // many-row GEMM. No partial tiles, no sums, no workspace use.
 

@@ -56,7 +56,7 @@ class Fp4Group:
     def __init__(self, M: int, problems: list[GroupProblem], device="cuda", workspace: torch.Tensor | None = None,
                  whole_tiles: bool = False, tokens_on_n: bool = False):
         """whole_tiles: no tile is cut along K (for groups of several layers: fastest, and bit-identical to the
-        many-row GEMM instead of to the weight-streaming launch). With whole tiles and 65..128 tokens the group is
+        many-row GEMM instead of to the weight-streaming launch). With whole tiles and 33..128 tokens the group is
         planned on tiles of 256 weight rows with the tokens on the MMA's M side (`self.tokens_tile == 256`) unless
         tokens_on_n is set, which the fused gather needs; the results are the same bits either way."""
         self.M, self.n = M, len(problems)

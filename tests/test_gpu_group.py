@@ -162,11 +162,11 @@ def test_group_rejects_bad_arguments():
         call("q27t_skinny_fp4_group", grp.table_host, grp.table_dev, small, small.numel())
 
 
-@pytest.mark.parametrize("M,tokens_on_n", [(1, False), (16, False), (64, False), (65, False), (100, False), (128, False), (128, True)])
+@pytest.mark.parametrize("M,tokens_on_n", [(1, False), (16, False), (32, False), (33, False), (64, False), (64, True), (100, False), (128, False), (128, True)])
 def test_group_of_whole_tiles_equals_the_many_row_gemm(M, tokens_on_n):
     """Whole-tile mode (no K split): every output is one accumulation chain over all of K, exactly what the many-row
     GEMM computes - bit for bit, for every epilogue; a stacked weight with three alphas equals the many-row GEMM of
-    each part with its own alpha. Two layers in one launch. From 65 tokens the group is planned on tiles of 256 weight
+    each part with its own alpha. Two layers in one launch. From 33 tokens the group is planned on tiles of 256 weight
     rows with the tokens on the MMA's M side (another kernel, the same bits) unless the caller keeps the few-token roles."""
     res = torch.randn(128, 5120, device=DEV)
     a5, a5sf, _ = operand(128, 5120, 11)
@@ -193,7 +193,7 @@ def test_group_of_whole_tiles_equals_the_many_row_gemm(M, tokens_on_n):
     for got in outs:
         probs += layer_problems(M, res[:M].contiguous(), got)
     grp = Fp4Group(M, probs, whole_tiles=True, tokens_on_n=tokens_on_n)
-    wide = M > 64 and not tokens_on_n
+    wide = M > 32 and not tokens_on_n
     assert grp.tokens_tile == (256 if wide else 16 if M <= 16 else 32 if M <= 32 else 64 if M <= 64 else 128)
     assert grp.slots == 0 and grp.counters == 0 and grp.pieces == 2 * (204 if wide else 408) and grp.ctas <= (148 if wide else 296)
     grp.run_sync()

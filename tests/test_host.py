@@ -304,7 +304,7 @@ def test_group_schedule_whole_tiles():
     for p in pieces:
         loads[p[0]] += p[4] - p[3]
     assert loads.max() == 68 and loads.max() > 1.9 * loads.sum() / 296
-    # tiles of 256 weight rows on one CTA per SM (65..128 tokens): half as many pieces of the same lengths
+    # tiles of 256 weight rows on one CTA per SM (33..128 tokens): half as many pieces of the same lengths
     ctas, nslots, counters, pieces = group_plan(LAYER_SHAPES * 8, 148, whole=2)
     assert ctas == 148 and nslots == 0 and counters == 0 and len(pieces) == 8 * 204
     assert sorted(p[2] for p in pieces if p[1] == 2) == list(range(34816 // 256))

@@ -58,6 +58,46 @@ int64_t q27b_glu_row(int64_t r, int half);
  * engine/src/kernels.cu:587-592,824-827). */
 int q27b_swizzle_sf(const uint8_t* src, int rows, int kblocks, uint8_t* dst, int glu_half, void* stream);
 
+/* ---- checkpoints (load time; csrc/checkpoint.cu) -------------------------------------------------------------- */
+
+/* Bytes [off, off + len) of the gate (half 0) or the up (half 1) matrix, in HOST memory at host_src, copied to their
+ * places in the interleaved gate | up that starts at dst (device): blocks of `block` bytes (64 rows), the gate's block b
+ * at 2 b, the up's at 2 b + 1; whole blocks go as one strided copy. Asynchronous on `stream`; host_src must stay
+ * untouched until the copy has run. Replaces copy_glu (engine/src/weights.cc:218-234). */
+int q27b_copy_glu(void* dst, size_t off, const void* host_src, size_t len, size_t block, int half, void* stream);
+
+/* A safetensors checkpoint: one file, or a directory whose *.safetensors files are its shards. Replaces the reading
+ * side of SafeTensors (engine/src/safetensors.h:24-41: has / info / read_range). */
+typedef struct q27b_ckpt q27b_ckpt;
+int q27b_ckpt_open(const char* path, q27b_ckpt** out);
+void q27b_ckpt_close(q27b_ckpt* c);
+int q27b_ckpt_count(const q27b_ckpt* c); /* tensors in the checkpoint */
+/* 0 and the tensor's dtype ("U8", "F8_E4M3", "F32", "BF16", ...), shape and size; 1 if the checkpoint has no such
+ * tensor (not an error); -1 on bad arguments. Any output pointer may be null. */
+int q27b_ckpt_tensor(const q27b_ckpt* c, const char* name, char* dtype, int dtype_cap, int64_t* shape, int shape_cap, int* ndim,
+                     int64_t* nbytes);
+/* Bytes [begin, begin + len) of a tensor into host memory. */
+int q27b_ckpt_read(const q27b_ckpt* c, const char* name, int64_t begin, int64_t len, void* host_dst);
+
+/* One NVFP4 projection as the checkpoint stores it, in either naming (modelopt: <p>.weight, .weight_scale,
+ * .weight_scale_2, .input_scale; compressed-tensors: <p>.weight_packed, .weight_scale, .weight_global_scale =
+ * 1 / weight_scale_2, .input_global_scale = 1 / input_scale). The LinearFp4 record of the reference
+ * (engine/src/weights.h:25-31) as filled by Weights::fp4 (engine/src/weights.cc:125-141). */
+typedef struct q27b_fp4_layer {
+  int out, in;              /* rows of the weight, reduction length */
+  float w_scale2, in_scale; /* tensor scales of the weight and of its activation; alpha = in_scale * w_scale2 */
+  int compressed_tensors;   /* 1: the reciprocal-scale naming */
+} q27b_fp4_layer;
+int q27b_ckpt_fp4_layer(const q27b_ckpt* c, const char* prefix, q27b_fp4_layer* info);
+/* Uploads the projection into the layout the GEMMs read: codes to w (device, [out][in / 2]), block scales swizzled
+ * to sf (device, q27b_sf_bytes(out, in / 16) bytes of a buffer the caller zeroed; for gate | up the buffer of the
+ * whole interleaved matrix). glu_half -1: as stored; 0 / 1: this projection is the gate / the up of an MLP and w, sf
+ * are the START of the interleaved gate | up matrix (out must be a multiple of 64). scratch: device memory of at
+ * least out * in / 16 bytes (the row-major scales on their way). Reads through two pinned staging buffers owned by the
+ * handle; returns after the stream has been synchronised. Load-time only. */
+int q27b_ckpt_load_fp4(q27b_ckpt* c, const char* prefix, int glu_half, uint8_t* w, uint8_t* sf, void* scratch, size_t scratch_bytes,
+                       void* stream);
+
 /* ---- activation quantisers (K, I multiples of 64; x 16-byte aligned) ------------------------------------------ */
 
 /* fp32 [M][K] -> codes [M][K/2] + swizzled scales. Replaces quant_fp4 (engine/src/kernels.h:124-126,

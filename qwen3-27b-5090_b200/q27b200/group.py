@@ -41,7 +41,9 @@ def problem_of(lin, q: torch.Tensor, sf: torch.Tensor, out: torch.Tensor, residu
     p.alpha_count = lin._nseg
     for i in range(lin._nseg):
         p.alpha_begin[i], p.alpha[i] = lin._zero[i], lin._alpha[i]
-    p.alpha_up = lin.alpha
+    if lin.glu:
+        p.alpha[0] = lin.alpha_gate
+    p.alpha_up = lin.alpha_up
     p.beta = 1.0 if residual is not None else 0.0
     p.a, p.a_sf, p.w, p.w_sf = q.data_ptr(), sf.data_ptr(), lin.w.data_ptr(), lin.sf.data_ptr()
     p.c = residual.data_ptr() if residual is not None else None

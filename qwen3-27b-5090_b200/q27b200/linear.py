@@ -53,6 +53,10 @@ class Fp4Linear:
         self.w_scale2, self.in_scale = float(w_scale2), float(in_scale)
         self.out, self.inp, self.glu = out_features, in_features, glu
         self.alpha = self.in_scale * self.w_scale2  # engine/src/weights.cc:286
+        # gate | up: the two halves may carry tensor scales of their own (a checkpoint's gate_proj and up_proj); the
+        # SiLU*mul epilogue applies them (engine/src/weights.cc:302-310)
+        self.w_scale2_gate = self.w_scale2_up = self.w_scale2
+        self.alpha_gate = self.alpha_up = self.alpha
         dev = codes.device
         # zeroed once: the head of the workspace holds arrival counters that the kernels leave at zero
         self.ws = workspace if workspace is not None else torch.zeros(WORKSPACE_BYTES, dtype=torch.uint8, device=dev)
@@ -70,6 +74,7 @@ class Fp4Linear:
         """A new activation tensor scale: alpha = in_scale * w_scale2 per segment."""
         self.in_scale = float(in_scale)
         self.alpha = self.in_scale * self.w_scale2
+        self.alpha_gate, self.alpha_up = self.in_scale * self.w_scale2_gate, self.in_scale * self.w_scale2_up
         for i, g in enumerate(getattr(self, "_w_scales", [self.w_scale2])):
             self._alpha[i] = self.in_scale * g
 
@@ -147,10 +152,10 @@ class Fp4Linear:
         if self.glu:
             assert out.dtype == torch.bfloat16 and residual is None
             if skinny:
-                call("q27b_skinny_fp4_glu_bf16", M, self.out, K, q, sf, self.w, self.sf, self.alpha, self.alpha, out,
+                call("q27b_skinny_fp4_glu_bf16", M, self.out, K, q, sf, self.w, self.sf, self.alpha_gate, self.alpha_up, out,
                      self.ws, self.ws.numel(), s)
             else:
-                call("q27b_gemm_fp4_glu_bf16", M, self.out, K, q, sf, self.w, self.sf, self.alpha, self.alpha, out, s)
+                call("q27b_gemm_fp4_glu_bf16", M, self.out, K, q, sf, self.w, self.sf, self.alpha_gate, self.alpha_up, out, s)
         elif out.dtype == torch.bfloat16:
             assert residual is None
             if skinny:
@@ -182,8 +187,8 @@ class Fp4Mlp:
     def __init__(self, gate_up: Fp4Linear, down: Fp4Linear, alpha_gate: float | None = None, alpha_up: float | None = None):
         assert gate_up.glu and not down.glu and gate_up.out == down.inp
         self.gate_up, self.down = gate_up, down
-        self.alpha_gate = gate_up.alpha if alpha_gate is None else float(alpha_gate)
-        self.alpha_up = gate_up.alpha if alpha_up is None else float(alpha_up)
+        self.alpha_gate = gate_up.alpha_gate if alpha_gate is None else float(alpha_gate)
+        self.alpha_up = gate_up.alpha_up if alpha_up is None else float(alpha_up)
         self._one = (ctypes.c_float * 1)(1.0)
         self._zero = (ctypes.c_int * 1)(0)
         self._rows = 0

@@ -21,6 +21,14 @@ SIGNATURES = {
     "q27b_sf_offset": ([I64, I64, I64], I64),
     "q27b_glu_row": ([I64, I], I64),
     "q27b_swizzle_sf": ([P, I, I, P, I, P], I),
+    "q27b_copy_glu": ([P, SZ, P, SZ, SZ, I, P], I),
+    "q27b_ckpt_open": ([ctypes.c_char_p, ctypes.POINTER(P)], I),
+    "q27b_ckpt_close": ([P], None),
+    "q27b_ckpt_count": ([P], I),
+    "q27b_ckpt_tensor": ([P, ctypes.c_char_p, ctypes.c_char_p, I, ctypes.POINTER(I64), I, ctypes.POINTER(I), ctypes.POINTER(I64)], I),
+    "q27b_ckpt_read": ([P, ctypes.c_char_p, I64, I64, P], I),
+    "q27b_ckpt_fp4_layer": ([P, ctypes.c_char_p, P], I),
+    "q27b_ckpt_load_fp4": ([P, ctypes.c_char_p, I, P, P, P, SZ, P], I),
     "q27b_quant_fp4": ([P, I, I, F, P, P, P], I),
     "q27b_quant_fp4_bf16": ([P, I, I, F, P, P, P], I),
     "q27b_quant_fp4_batch": ([P, P, I, P], I),

@@ -1002,6 +1002,64 @@ __global__ void __launch_bounds__(Cfg2<STAGES>::kThreads, 1) umma_gemm2_kernel(c
             for (int q = 0; q < p.n_peers; q++) *reinterpret_cast<uint4*>(reinterpret_cast<char*>(dst) + p.peer_delta[q]) = v;
           }
         }
+      } else if constexpr (kEpi == kEpiBf16 || kEpi == kEpiF32) {
+        // The same whole-row stores for the plain epilogues: the CTA's 128 tokens x 256 channels leave in passes of
+        // 256 bytes per token (bf16: two passes of 128 channels; fp32: four of 64), staged as above. The residual of
+        // the fp32 epilogue is added on the way out, where a warp reads it in whole rows too: the same
+        // fma(beta, c, alpha * acc) as finish_f32, so the bits do not depend on which path stored them.
+        uint8_t* stage_out = smem + C::kOutOff;
+        constexpr int kPasses = kEpi == kEpiBf16 ? 2 : 4, kPerPass = kMine / kPasses, kPassCols = 256 / kPasses;
+        const int m_base = (item % m_pairs) * 256 + int(rank) * 128, chunk = lane & 15;
+#pragma unroll
+        for (int ps = 0; ps < kPasses; ps++) {
+          asm volatile("bar.sync 3, %0;" ::"r"(C::kEpiWarps * 32) : "memory");  // the previous pass has left the staging area
+#pragma unroll
+          for (int jj = 0; jj < kPerPass; jj++) {
+            const int j = ps * kPerPass + jj, un = sub + 4 * j, col = un * 16, n = n0 + col;
+            uint4* r = reinterpret_cast<uint4*>(stage_out + row * 256);
+            float out[16];
+#pragma unroll
+            for (int i = 0; i < 16; i++) {
+              out[i] = __fmul_rn(alpha_of(p.alpha, n + i), g[j][i]);
+              if (p.wscale) out[i] = __fmul_rn(out[i], __fmul_rn(p.wscale[n + i], p.ascale[min(m, p.M - 1)]));
+            }
+            if constexpr (kEpi == kEpiBf16) {
+              const int chunk0 = (col - ps * kPassCols) / 8;
+              uint32_t pk[8];
+#pragma unroll
+              for (int i = 0; i < 8; i++) pk[i] = uint32_t(bf16_bits(out[2 * i])) | (uint32_t(bf16_bits(out[2 * i + 1])) << 16);
+              r[chunk0 ^ (row & 15)] = make_uint4(pk[0], pk[1], pk[2], pk[3]);
+              r[(chunk0 + 1) ^ (row & 15)] = make_uint4(pk[4], pk[5], pk[6], pk[7]);
+            } else {
+              const int chunk0 = (col - ps * kPassCols) / 4;
+#pragma unroll
+              for (int i = 0; i < 4; i++)
+                r[(chunk0 + i) ^ (row & 15)] = make_uint4(__float_as_uint(out[4 * i]), __float_as_uint(out[4 * i + 1]),
+                                                          __float_as_uint(out[4 * i + 2]), __float_as_uint(out[4 * i + 3]));
+            }
+          }
+          asm volatile("bar.sync 3, %0;" ::"r"(C::kEpiWarps * 32) : "memory");
+          constexpr int kElem = kEpi == kEpiBf16 ? 2 : 4;
+          char* out0 = static_cast<char*>(p.d) + (int64_t(n0) + ps * kPassCols) * kElem + chunk * 16;
+#pragma unroll
+          for (int it = 0; it < 4; it++) {  // a warp copies 8 rows, two per instruction: 2 x 256 contiguous bytes
+            const int rr = (warp - 2) * 8 + it * 2 + (lane >> 4), mr = m_base + rr;
+            if (mr < p.M) {
+              uint4 v = reinterpret_cast<const uint4*>(stage_out + rr * 256)[chunk ^ (rr & 15)];
+              const int64_t off = int64_t(mr) * p.N * kElem;
+              if constexpr (kEpi == kEpiF32) {
+                if (p.c) {
+                  const float4 c = *reinterpret_cast<const float4*>(reinterpret_cast<const char*>(p.c) + (out0 - static_cast<char*>(p.d)) + off);
+                  v.x = __float_as_uint(__fmaf_rn(p.beta, c.x, __uint_as_float(v.x)));
+                  v.y = __float_as_uint(__fmaf_rn(p.beta, c.y, __uint_as_float(v.y)));
+                  v.z = __float_as_uint(__fmaf_rn(p.beta, c.z, __uint_as_float(v.z)));
+                  v.w = __float_as_uint(__fmaf_rn(p.beta, c.w, __uint_as_float(v.w)));
+                }
+              }
+              *reinterpret_cast<uint4*>(out0 + off) = v;
+            }
+          }
+        }
       } else {
 #pragma unroll
         for (int j = 0; j < kMine; j++) {

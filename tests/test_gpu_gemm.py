@@ -130,3 +130,31 @@ def test_gemm_fp4_glu_nvfp4_out(M, I, K):
     codes, sfo = O.quant_act_codes(h, out_scale)
     assert (sf_u != sfo).mean() < 1e-3
     assert _code_mismatch(q, dev(codes)) < 2e-3
+
+
+@pytest.mark.parametrize("M", [129, 300, 1000])
+def test_many_row_kernels_agree_bit_for_bit(M, monkeypatch):
+    """The three many-row kernels (CTA pairs with staged whole-row stores, 128 x 256 tiles, 128 x 128 tiles) run the
+    same accumulation chain per output and the same roundings in their epilogues: identical bits for the fp32 output
+    with and without a residual, the bf16 output and the SiLU*mul output (Q27B_MANY is read at every launch)."""
+    N, K = 512, 1024
+    rng = np.random.RandomState(M)
+    a, asf, _ = fp4_operand(M, K, rng)
+    b, bsf, _ = fp4_operand(N, K, rng)
+    ad, bd, asw, bsw = dev(a), dev(b), swizzled_dev(asf), swizzled_dev(bsf)
+    c = torch.randn(M, N, device=DEV)
+    got = {}
+    for kind in ("pairs", "wide", "narrow"):
+        monkeypatch.setenv("Q27B_MANY", kind)
+        d = torch.full((M, N), float("nan"), device=DEV)
+        call("q27t_gemm_fp4", M, N, K, ad, asw, bd, bsw, 0.37, None, 0.0, d)
+        r = c.clone()
+        call("q27t_gemm_fp4", M, N, K, ad, asw, bd, bsw, 0.37, r, 0.75, r)
+        h = torch.zeros(M, N, dtype=torch.bfloat16, device=DEV)
+        call("q27t_gemm_fp4_bf16", M, N, K, ad, asw, bd, bsw, 0.37, h)
+        g = torch.zeros(M, N // 2, dtype=torch.bfloat16, device=DEV)
+        call("q27t_gemm_fp4_glu_bf16", M, N // 2, K, ad, asw, bd, bsw, 0.013, 0.021, g)
+        got[kind] = (d, r, h, g)
+    for kind in ("wide", "narrow"):
+        for x, y, what in zip(got["pairs"], got[kind], ("fp32", "fp32 + residual", "bf16", "SiLU*mul")):
+            assert torch.equal(x, y), f"{what}: pairs vs {kind} at M={M}"

@@ -567,6 +567,17 @@ def total_bytes_of(cfg):
     return cfg.algorithmic_bytes()
 
 
+def many_row_kernel_name(M, fused_gather):
+    """Which many-row kernel the library picks for the prefill shape (its rule: csrc/umma_gemm.cu run_many)."""
+    from q27b200.q27lib import lib
+
+    forced = os.environ.get("Q27B_MANY", "")
+    quad = lib().q27b_quad_available() and not fused_gather and forced == "quad" and M > 128 and ((M + 255) // 256) % 2 == 0
+    if quad:
+        return "quad_gemm_kernel (many rows, clusters of four CTAs sharing the weight tile; optional single-GPU library)"
+    return "umma_gemm2_kernel (many rows, CTA pairs)" if forced in ("", "pairs", "quad") else f"umma_gemm_kernel ({forced} tiles)"
+
+
 def run_single(cfg, args, rank, world, local_rank, peaks):
     """One of cfg0 / cfg1 / cfg2 / cfg4: step = quantise the bf16 activation + the GEMM with its epilogue, weights
     rotating through more than L2-size of distinct copies, replayed from a CUDA graph until the region is long enough."""
@@ -719,7 +730,7 @@ def run_single(cfg, args, rank, world, local_rank, peaks):
         launch_flops = 2 * M * n_rows_local * cfg.K
         achieved = launch_flops / gemm_s / 1e12
         roof = {"bound": "tensor", "achieved": achieved, "peak": tpeak, "unit": "TFLOP/s", "frac": achieved / tpeak,
-                "traffic": ncu_traffic().get(f"cfg{cfg.index}") if world == 1 else None, "algorithmic_flops": launch_flops, "kernel": "umma_gemm2_kernel (many rows, CTA pairs)",
+                "traffic": ncu_traffic().get(f"cfg{cfg.index}") if world == 1 else None, "algorithmic_flops": launch_flops, "kernel": many_row_kernel_name(M, fused),
                 "us_per_launch": gemm_s * 1e6, "peak_sustained": 4.0 * peaks["bf16_tflops_sustained"],
                 "frac_of_sustained": achieved / (4.0 * peaks["bf16_tflops_sustained"]),
                 "peak_source": "4 x bf16_tflops (burst) of " + peaks["source"] + "; no FP4 peak is measured on this pool, nominal dense FP4 is 9000"}

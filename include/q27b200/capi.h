@@ -303,6 +303,14 @@ int q27b_gemm_fp4_glu(int M, int I, int K, const uint8_t* a, const uint8_t* a_sf
 
 /* ---- diagnostics -------------------------------------------------------------------------------------------------- */
 
+/* 1 if the optional single-GPU library libq27b200_quad.so (csrc/quad_gemm.cu: the many-row GEMM on clusters of four
+ * CTAs that share their weight tile through TMA multicast of this GPU's own memory) lies beside this library and was
+ * loaded. With Q27B_MANY=quad (read at every launch, like pairs | wide | narrow) q27b_gemm_fp4 / _bf16 / _glu_bf16 then run
+ * it for M > 128 in an even number of 256-token tiles with N and K multiples of 256: same bits as the pair kernel, 29 %
+ * fewer bytes out of L2 per flop. It is opt-in because it measured no faster here (the prefill GEMM is bound by the
+ * board's power cap). The fused gather never uses it. */
+int q27b_quad_available(void);
+
 /* Synchronises the device, returns and clears the status word kernels set when a bounded wait runs out
  * (0 = none; codes in csrc/ptx_sm100.cuh). No counterpart in the reference, whose kernels wait unboundedly. */
 int q27b_device_status(uint32_t* status);

@@ -24,6 +24,7 @@
 // gemm_fp4_bf16 (engine/src/gemm_mma.cu:463-626) and the gate | up SiLU*mul epilogue (gemm_mma.cu:350-399,
 // kernels.cu:319-339) of the reference.
 #include <cuda.h>
+#include <dlfcn.h>
 
 #include <algorithm>
 #include <cstdlib>
@@ -36,6 +37,7 @@
 #include "group_plan.h"
 #include "layout.h"
 #include "ptx_sm100.cuh"
+#include "quad_abi.h"
 #include "quant_block.cuh"
 
 namespace q27b {
@@ -202,7 +204,10 @@ __device__ __forceinline__ unsigned long long gtime() {
     if (p.trace && (idx) < 64) p.trace[(size_t(blockIdx.x) * 4 + (kind)) * 64 + (idx)] = gtime();         \
   } while (0)
 #define TRACE_DECL(name) unsigned long long name = 0
+#define TRACE_INC(name) name++
 #define TRACE_T0(t) const unsigned long long t = gtime()
+#define TRACE_C0(c) const long long c = clock64()
+#define TRACE_CPUT(idx, c) TRACE_PUT(idx, (unsigned long long)(clock64() - c))
 #define TRACE_ADD(acc, t) acc += gtime() - t
 #define TRACE_PUT(idx, v)                                                           \
   do {                                                                              \
@@ -213,7 +218,10 @@ __device__ __forceinline__ unsigned long long gtime() {
   do {                   \
   } while (0)
 #define TRACE_DECL(name)
+#define TRACE_INC(name)
 #define TRACE_T0(t)
+#define TRACE_C0(c)
+#define TRACE_CPUT(idx, c)
 #define TRACE_ADD(acc, t)
 #define TRACE_PUT(idx, v)
 #endif
@@ -840,6 +848,8 @@ __global__ void __launch_bounds__(Cfg2<STAGES>::kThreads, 1) umma_gemm2_kernel(c
       TRACE_DECL(w_stage);
       TRACE_DECL(w_acc);
       TRACE_T0(t_begin);
+      TRACE_C0(c_begin);
+      TRACE_DECL(tk_mma);
       auto issue_stage = [&](auto stage_c, auto first_c, int nsteps) -> bool {
         constexpr int S = decltype(stage_c)::value;
         constexpr bool kFirst = decltype(first_c)::value;
@@ -847,6 +857,7 @@ __global__ void __launch_bounds__(Cfg2<STAGES>::kThreads, 1) umma_gemm2_kernel(c
         TRACE_T0(t_s);
         if (!mbar_wait_bounded(sfr0 + 8 * S, phase, abort_flag, &g_status, kStatusFullWaitTimeout, 0, true)) return false;
         TRACE_ADD(w_stage, t_s);
+        TRACE(1, tk_mma);
         tc_fence_after_sync();
         constexpr uint64_t kStageDesc = uint64_t(S) * (C::kStageBytes >> 4);  // the stage's offset in 16-byte units
         const uint64_t da = desc_a0 + kStageDesc, db = desc_b0 + kStageDesc;
@@ -861,6 +872,8 @@ __global__ void __launch_bounds__(Cfg2<STAGES>::kThreads, 1) umma_gemm2_kernel(c
             umma_nvfp4_2sm(tmem_base, da + 2 * ks, db + 2 * ks, idesc, sf + 4 * ks, sf + 16 + 8 * ks, (kFirst && ks == 0) ? 0u : 1u);
         }
         umma_commit_2sm(empty0 + 8 * S);  // frees the stage in both CTAs
+        TRACE(2, tk_mma);
+        TRACE_INC(tk_mma);
         return true;
       };
       auto issue = [&](auto first_c, int nsteps) -> bool {
@@ -891,6 +904,7 @@ __global__ void __launch_bounds__(Cfg2<STAGES>::kThreads, 1) umma_gemm2_kernel(c
       TRACE_PUT(59, w_acc);
       TRACE_PUT(60, gtime() - t_begin);
       TRACE_PUT(61, (unsigned long long)ntiles);
+      TRACE_CPUT(62, c_begin);  // with 60: the SM clock this kernel really ran at
       if (ok && ntiles > 0) mbar_wait_bounded(aempty, (ntiles - 1) & 1, abort_flag, &g_status, kStatusAccumFreeTimeout, 64, true);
     }
   } else if (warp >= C::kFeederWarp0) {
@@ -905,7 +919,7 @@ __global__ void __launch_bounds__(Cfg2<STAGES>::kThreads, 1) umma_gemm2_kernel(c
           ok = false;
           break;
         }
-        if (warp == C::kFeederWarp0 && lane == 0 && tkf < 20) TRACE(3, 16 + 2 * tkf);
+        if (warp == C::kFeederWarp0 && lane == 0 && tkf >= 24 && tkf < 44) TRACE(3, 16 + 2 * (tkf - 24));
         const uint8_t* sb = smem + stage * C::kStageBytes;
         const uint4* sfp = reinterpret_cast<const uint4*>(sb + C::kOffSfP) + lane;
         const uint4* sfq = reinterpret_cast<const uint4*>(sb + C::kOffSfQ) + lane;
@@ -927,7 +941,7 @@ __global__ void __launch_bounds__(Cfg2<STAGES>::kThreads, 1) umma_gemm2_kernel(c
           if (rank == 0) mbar_arrive(sfr0 + 8 * stage);
           else mbar_arrive_remote(sfr0 + 8 * stage, 0);
         }
-        if (warp == C::kFeederWarp0 && lane == 0 && tkf < 20) TRACE(3, 17 + 2 * tkf);
+        if (warp == C::kFeederWarp0 && lane == 0 && tkf >= 24 && tkf < 44) TRACE(3, 17 + 2 * (tkf - 24));
         tkf++;
         if (++stage == STAGES) stage = 0, phase ^= 1;
       }
@@ -1352,12 +1366,65 @@ int run_many_pairs(const uint8_t* a, const uint8_t* w, GemmParams& p, cudaStream
   return 0;
 }
 
-// Which many-row kernel runs (read at every launch): Q27B_MANY=pairs|wide|narrow forces one, else the best that
+// The optional libq27b200_quad.so (quad_gemm.cu: clusters of four CTAs that share their weight tile), looked for once
+// beside this library. It is a single-GPU accelerator: a process that does not find it runs the pair kernel.
+struct QuadLib {
+  QuadGemmFn gemm = nullptr;
+  QuadErrorFn error = nullptr;
+};
+const QuadLib& quad_lib() {
+  static const QuadLib lib = [] {
+    QuadLib l;
+    Dl_info info;
+    if (!dladdr(reinterpret_cast<const void*>(&q27b_device_status), &info) || !info.dli_fname) return l;
+    std::string path = info.dli_fname;
+    const size_t slash = path.rfind('/');
+    path = (slash == std::string::npos ? std::string(".") : path.substr(0, slash)) + "/libq27b200_quad.so";
+    if (void* h = dlopen(path.c_str(), RTLD_NOW | RTLD_LOCAL)) {
+      l.gemm = reinterpret_cast<QuadGemmFn>(dlsym(h, "q27b_quad_gemm"));
+      l.error = reinterpret_cast<QuadErrorFn>(dlsym(h, "q27b_quad_last_error"));
+      if (!l.gemm || !l.error) l = QuadLib();
+    }
+    return l;
+  }();
+  return lib;
+}
+
+template <int kEpi>
+int run_many_quad(const uint8_t* a, const uint8_t* w, const GemmParams& p, cudaStream_t s) {
+  const QuadLib& lib = quad_lib();
+  QuadParams qp = {};
+  qp.M = p.M, qp.N = p.N, qp.K = p.K, qp.ksteps = p.ksteps, qp.chunks = p.chunks, qp.sf_p = p.sf_p, qp.sf_q = p.sf_q;
+  qp.alpha = p.alpha.alpha[0], qp.alpha_up = p.alpha_up, qp.c = p.c, qp.beta = p.beta, qp.d = p.d, qp.epi = kEpi;
+  qp.status = device_status_ptr();
+  Q27B_REQUIRE(qp.status, "gemm_fp4: no device status word");
+  CUtensorMap ma, mw;
+  if (int rc = make_operand_map(&ma, a, p.M, p.K, 128)) return rc;
+  if (int rc = make_operand_map(&mw, w, p.N, p.K, 64)) return rc;
+  if (lib.gemm(&ma, &mw, &qp, s)) return fail("%s", lib.error());
+  return 0;
+}
+
+// Which many-row kernel runs (read at every launch): Q27B_MANY=quad|pairs|wide|narrow forces one, else the best that
 // the shape allows.
 template <int kEpi>
 int run_many(const uint8_t* a, const uint8_t* w, GemmParams& p, cudaStream_t s) {
   const char* e = getenv("Q27B_MANY");
   const bool force_wide = e && !strcmp(e, "wide"), force_narrow = e && !strcmp(e, "narrow");
+  const bool force_quad = e && !strcmp(e, "quad"), free_choice = !e || !*e;
+  if constexpr (kEpi == kEpiF32 || kEpi == kEpiBf16 || kEpi == kEpiGluBf16) {
+    // Clusters of four (two pairs sharing their weight tile, delivered once per cluster): 29 % fewer bytes from L2 per flop.
+    const bool fits = p.M > 128 && ((p.M + 255) / 256) % 2 == 0 && p.N % 256 == 0 && p.K % 256 == 0 && !p.n_peers && !p.wscale &&
+                      p.alpha.count == 1;
+    Q27B_REQUIRE(!force_quad || (fits && quad_lib().gemm), "gemm_fp4: Q27B_MANY=quad, but %s",
+                 fits ? "libq27b200_quad.so is not beside this library" : "the shape does not fit (M > 128 in an even number of 256-token tiles, N and K multiples of 256)");
+    // Opt-in: measured on this pool it is no faster than the pair kernel (both run into the board's power cap, not
+    // into L2 bandwidth), and clusters of four leave SMs unused where a GPC's SM count is not a multiple of four.
+    (void)free_choice;
+    if (force_quad) return run_many_quad<kEpi>(a, w, p, s);
+  } else {
+    Q27B_REQUIRE(!force_quad, "gemm_fp4: Q27B_MANY=quad has no NVFP4 epilogue");
+  }
   // CTA pairs, 256 x 256 tiles: least L2 traffic per flop. One CTA per 128 x 256 tile where there is less than one
   // pair tile per SM pair to go round. 128 x 128 tiles on two CTAs per SM when the weight rows do not divide by 256.
   if (p.N % 256 == 0 && p.M > 128 && !force_wide && !force_narrow) return run_many_pairs<kEpi>(a, w, p, s);
@@ -1408,6 +1475,18 @@ AlphaSeg make_alpha(int count, const int* begin, const float* alpha) {
 }
 
 }  // namespace
+
+uint32_t* device_status_ptr() {
+  static uint32_t* ptr[64] = {};
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return nullptr;
+  if (!ptr[dev]) {
+    void* p = nullptr;
+    if (cudaGetSymbolAddress(&p, g_status) != cudaSuccess) return nullptr;
+    ptr[dev] = static_cast<uint32_t*>(p);
+  }
+  return ptr[dev];
+}
 
 int sm_count() {
   static int sms[64] = {};
@@ -1701,6 +1780,8 @@ int q27b_probe_wait_timeout(int budget_us, void* stream) {
 }
 
 // Reads and clears the device status word (0 = no bounded wait ran out since the last call). Synchronises.
+int q27b_quad_available(void) { return quad_lib().gemm != nullptr; }
+
 int q27b_device_status(uint32_t* status) {
   Q27B_REQUIRE(status, "device_status: null pointer");
   Q27B_CUDA(cudaDeviceSynchronize());

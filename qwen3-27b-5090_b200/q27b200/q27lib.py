@@ -59,6 +59,7 @@ SIGNATURES = {
     "q27b_gemm_fp4_glu_bf16": ([I, I, I, P, P, P, P, F, F, P, P], I),
     "q27b_gemm_fp4_glu": ([I, I, I, P, P, P, P, F, F, F, P, P, P], I),
     "q27b_device_status": ([U32P], I),
+    "q27b_quad_available": ([], I),
     "q27t_last_us": ([], F),
     "q27t_sf_bytes": ([I64, I64], I64),
     "q27t_quant_fp4": ([P, I, I, F, P, P], I),

@@ -2,6 +2,8 @@
 reference's engine/tests/test_gemm.py:25-110: residual in place, plain, C apart from D, bf16 == rounded fp32,
 gate | up with the fused SiLU*mul epilogue)."""
 
+import os
+
 import numpy as np
 import pytest
 import torch
@@ -9,7 +11,7 @@ import torch
 from helpers import DEV, bf16_to_f32, dev, fp4_operand, rel_err, swizzled_dev, workspace
 from oracle import nvfp4_oracle as O
 from q27b200 import layouts
-from q27b200.q27lib import call, lib
+from q27b200.q27lib import LIB_PATH, call, lib
 
 pytestmark = pytest.mark.gpu
 
@@ -134,7 +136,8 @@ def test_gemm_fp4_glu_nvfp4_out(M, I, K):
 
 @pytest.mark.parametrize("M", [129, 300, 1000])
 def test_many_row_kernels_agree_bit_for_bit(M, monkeypatch):
-    """The three many-row kernels (CTA pairs with staged whole-row stores, 128 x 256 tiles, 128 x 128 tiles) run the
+    """The many-row kernels (CTA pairs with staged whole-row stores, 128 x 256 tiles, 128 x 128 tiles and, where the
+    optional single-GPU library is present and the token tiles pair up, clusters of four) run the
     same accumulation chain per output and the same roundings in their epilogues: identical bits for the fp32 output
     with and without a residual, the bf16 output and the SiLU*mul output (Q27B_MANY is read at every launch)."""
     N, K = 512, 1024
@@ -144,7 +147,8 @@ def test_many_row_kernels_agree_bit_for_bit(M, monkeypatch):
     ad, bd, asw, bsw = dev(a), dev(b), swizzled_dev(asf), swizzled_dev(bsf)
     c = torch.randn(M, N, device=DEV)
     got = {}
-    for kind in ("pairs", "wide", "narrow"):
+    quad = os.path.exists(os.path.join(os.path.dirname(LIB_PATH), "libq27b200_quad.so")) and ((M + 255) // 256) % 2 == 0
+    for kind in ("pairs", "wide", "narrow") + (("quad",) if quad else ()):
         monkeypatch.setenv("Q27B_MANY", kind)
         d = torch.full((M, N), float("nan"), device=DEV)
         call("q27t_gemm_fp4", M, N, K, ad, asw, bd, bsw, 0.37, None, 0.0, d)
@@ -155,6 +159,6 @@ def test_many_row_kernels_agree_bit_for_bit(M, monkeypatch):
         g = torch.zeros(M, N // 2, dtype=torch.bfloat16, device=DEV)
         call("q27t_gemm_fp4_glu_bf16", M, N // 2, K, ad, asw, bd, bsw, 0.013, 0.021, g)
         got[kind] = (d, r, h, g)
-    for kind in ("wide", "narrow"):
+    for kind in [k for k in got if k != "pairs"]:
         for x, y, what in zip(got["pairs"], got[kind], ("fp32", "fp32 + residual", "bf16", "SiLU*mul")):
             assert torch.equal(x, y), f"{what}: pairs vs {kind} at M={M}"

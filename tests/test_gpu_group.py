@@ -200,3 +200,49 @@ def test_group_of_whole_tiles_equals_the_many_row_gemm(M, tokens_on_n):
     for got in outs:
         for name in want:
             assert torch.equal(got[name], want[name]), f"{name} differs at M={M}"
+
+
+@pytest.mark.parametrize("M", [33, 77, 128])
+def test_whole_tile_group_on_256_row_tiles_of_small_and_odd_shapes(M):
+    """The 256-row form (33..128 tokens, whole tiles): a reduction length that ends inside a stage (K = 384: the last
+    stage holds two of four MMA steps), a single tile, fewer tiles than CTAs, one tile per CTA and more, every epilogue -
+    against the many-row GEMM, bit for bit, twice (the second launch finds the first one's state). A weight whose rows
+    are not a multiple of 256 sends the whole group back to 128-row tiles."""
+    shapes = [(256, 384, EPI_F32), (512, 5120, EPI_BF16), (256, 128, EPI_F32), (148 * 256, 256, EPI_BF16), (1024, 1024, EPI_GLU_BF16),
+              (6400, 640, EPI_F32)]
+    probs, got, want, keep = [], [], [], []
+    res = torch.randn(M, 6400, device=DEV)
+    for i, (N, K, epi) in enumerate(shapes):
+        a, asf, _ = operand(128, K, 300 + i)
+        w, wsf, _ = operand(N, K, 400 + i)
+        if epi == EPI_GLU_BF16:
+            d = torch.empty(M, N // 2, dtype=torch.bfloat16, device=DEV)
+            call("q27t_gemm_fp4_glu_bf16", M, N // 2, K, a, asf, w, wsf, 0.013, 0.021, d)
+            g = torch.zeros_like(d)
+            probs.append(problem(N, K, epi, a, asf, w, wsf, g, (0.013,), alpha_up=0.021))
+        elif epi == EPI_BF16:
+            d = torch.empty(M, N, dtype=torch.bfloat16, device=DEV)
+            call("q27t_gemm_fp4_bf16", M, N, K, a, asf, w, wsf, 0.37, d)
+            g = torch.zeros_like(d)
+            probs.append(problem(N, K, epi, a, asf, w, wsf, g, (0.37,)))
+        else:
+            c = res[:, :N].contiguous() if N == 6400 else None
+            keep.append(c)  # (the problem record holds its address)
+            d = torch.empty(M, N, device=DEV)
+            call("q27t_gemm_fp4", M, N, K, a, asf, w, wsf, 0.37, c, 0.5 if c is not None else 0.0, d)
+            g = torch.full((M, N), float("nan"), device=DEV)
+            p = problem(N, K, epi, a, asf, w, wsf, g, (0.37,), c=c)
+            p.beta = 0.5 if c is not None else 0.0
+            probs.append(p)
+        got.append(g)
+        want.append(d)
+    grp = Fp4Group(M, probs, whole_tiles=True)
+    assert grp.tokens_tile == 256 and grp.ctas <= 148 and grp.slots == 0
+    for _ in range(2):
+        grp.run_sync()
+        for s, g, w_ in zip(shapes, got, want):
+            assert torch.equal(g, w_), s
+    a, asf, _ = operand(128, 256, 1)
+    w, wsf, _ = operand(384, 256, 2)
+    odd = Fp4Group(M, probs + [problem(384, 256, EPI_F32, a, asf, w, wsf, torch.empty(M, 384, device=DEV))], whole_tiles=True)
+    assert odd.tokens_tile in (64, 128)

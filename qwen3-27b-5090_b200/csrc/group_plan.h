@@ -5,9 +5,10 @@
 // Each problem keeps exactly the K split its stand-alone launch would use (choose_skinny_plan, layout.h): the
 // pieces {tile, chunk range} and the order in which the pieces of a cut tile are summed are the same, which makes
 // the grouped results bit-identical to per-GEMM calls. What changes is only WHO streams a piece: the pieces of
-// all problems are dealt to the CTAs longest first onto the least loaded CTA, and every CTA walks its pieces in
-// problem order: the pieces of one tile are then streamed at about the same time by their CTAs, so the CTA that
-// sums the tile (fixed by the plan: piece tile % pieces) finds the other pieces there soon after its own.
+// all problems are dealt to the CTAs longest first onto the least loaded CTA, and every CTA walks first its pieces
+// of cut tiles, then its whole tiles, each in problem order: the pieces of one tile are then streamed at about the
+// same time by their CTAs, and early, so the CTA that sums the tile (fixed by the plan: piece tile % pieces) finds
+// the other pieces there soon after its own and sums while whole tiles are still streaming.
 // (`rotate`: every CTA starts at a different point of its list instead; kept for experiments only - it spreads the
 // pieces of a tile over the whole run of the kernel.)
 //
@@ -136,7 +137,14 @@ inline GroupSchedule schedule_group(const GroupShape* shapes, int n, int cta_slo
   }
   sch.cta_first.assign(ctas + 1, 0);
   for (int g = 0; g < ctas; g++) {
-    std::sort(mine[g].begin(), mine[g].end());  // problem order, then tile, then K
+    // Pieces of cut tiles first, whole tiles last, each in problem order (then tile, then K): a cut tile can be summed
+    // only when all its pieces have been streamed, so they are streamed early by every CTA and summed while the whole
+    // tiles (each finished by its own CTA alone) are still streaming. With the plain problem order the pieces of the last
+    // problem's cut tiles end every CTA's list and all their sums pile up behind the stream: 13 of 46 us for one layer.
+    std::stable_sort(mine[g].begin(), mine[g].end(), [&](int a, int b) {
+      const bool wa = all[a].nparts == 1, wb = all[b].nparts == 1;
+      return wa != wb ? wb : a < b;
+    });
     if (rotate && !mine[g].empty()) std::rotate(mine[g].begin(), mine[g].begin() + g % int(mine[g].size()), mine[g].end());
     for (int i : mine[g]) sch.items.push_back(all[i]);
     sch.cta_first[g + 1] = int(sch.items.size());

@@ -147,8 +147,9 @@ def test_group_schedule_keeps_each_problems_own_split(shapes, slots):
         assert 0 <= cta < ctas
         by_problem.setdefault(prob, []).append((tile, c0, c1, slot, nparts, slot0, sums))
         loads[cta] += c1 - c0
-        assert last_key.get(cta, (-1, -1, -1)) < (prob, tile, c0)  # a CTA walks its pieces in problem order
-        last_key[cta] = (prob, tile, c0)
+        # a CTA walks its pieces of cut tiles first, then its whole tiles, each in problem order
+        assert last_key.get(cta, (-1, -1, -1, -1)) < (int(nparts == 1), prob, tile, c0)
+        last_key[cta] = (int(nparts == 1), prob, tile, c0)
     used_slots = set()
     cut_tiles = 0
     for prob, (N, K) in enumerate(shapes):

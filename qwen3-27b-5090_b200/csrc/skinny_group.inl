@@ -94,7 +94,11 @@ struct GroupCfg {
   static constexpr int kSfCol0 = kAccBufs * NB;
   static constexpr int kXchgBytes = 8 * 64 * 4 + 16 * 16;      // SiLU*mul exchange between the gate and the up warps + the queue of tiles to sum
   static constexpr int kNumBars = 3 * STAGES + 2 * kAccBufs;
-  static constexpr int kSmemBytes = STAGES * C::kStageBytes + kXchgBytes + kNumBars * 8 + 16 + 1024;
+  // Fused gather at up to 16 tokens: a finished tile (16 tokens x 128 channels, at most fp32) is laid out token-major
+  // in shared memory and leaves as 16-byte pieces of whole token rows (see flush_staged_tile)
+  static constexpr int kStageOutBytes = NB == 16 ? 16 * 128 * 4 : 0;
+  static constexpr int kStageOutOff = STAGES * C::kStageBytes + kXchgBytes + (kNumBars * 8 + 16 + 15) / 16 * 16;
+  static constexpr int kSmemBytes = kStageOutOff + kStageOutBytes + 1024;
   static_assert(kAccBufs >= 1 && kSfCol0 + C::kSfCols * STAGES <= C::kTmemCols, "tensor memory budget");
   static_assert(2 * (kSmemBytes + 1024) <= 228 * 1024, "shared memory budget");
 };
@@ -138,6 +142,59 @@ struct GroupUnits {
     }
   }
 };
+
+// Fused gather, few tokens: with the tokens on the MMA's N side a thread holds ONE channel of every token, and stores
+// straight from registers are 2-byte pieces, 64 contiguous bytes per warp instruction - once per destination GPU. At
+// eight GPUs the epilogue then issues 128 such stores per thread and tile and the NVLink packets are small. Instead the
+// finished values go token-major into shared memory (stage_swapped: the arithmetic of store_swapped, bit for bit) and
+// leave as 16-byte pieces of whole token rows, a quarter of the store instructions and rows of 128-512 contiguous bytes.
+template <int kEpi>
+__device__ __forceinline__ void stage_swapped(const GemmParams& p, const float (&v)[8], int m0, int tile, int row, float* xchg,
+                                              uint8_t* stage_out) {
+  if constexpr (kEpi == kEpiGluBf16) {
+    if (row >= 64) {
+#pragma unroll
+      for (int j = 0; j < 8; j++) xchg[j * 64 + row - 64] = v[j];
+    }
+    epi_bar();
+    if (row < 64) {
+      const float ag = p.alpha.alpha[0], au = p.alpha_up;
+      uint16_t* d = reinterpret_cast<uint16_t*>(stage_out) + row;
+#pragma unroll
+      for (int j = 0; j < 8; j++)
+        if (m0 + j < p.M) d[(m0 + j) * 64] = bf16_bits(silu_mul(__fmul_rn(ag, v[j]), __fmul_rn(au, xchg[j * 64 + row])));
+    }
+    epi_bar();
+  } else {
+    const int n = tile * 128 + row;
+#pragma unroll
+    for (int j = 0; j < 8; j++) {
+      const int m = m0 + j;
+      if (m < p.M) {
+        const float out = finish_f32(p, v[j], m, n);
+        if constexpr (kEpi == kEpiF32) reinterpret_cast<float*>(stage_out)[m * 128 + row] = out;
+        else reinterpret_cast<uint16_t*>(stage_out)[m * 128 + row] = bf16_bits(out);
+      }
+    }
+  }
+}
+// The staged tile to this GPU's memory and to every peer's: thread t moves 16-byte pieces t, t + 128, ... of the M token
+// rows (128, 256 or 512 bytes each). Called by the four epilogue warps together.
+template <int kEpi>
+__device__ __forceinline__ void flush_staged_tile(const GemmParams& p, int tile, const uint8_t* stage_out, const PeerCopies& peers) {
+  constexpr int kRowBytes = kEpi == kEpiF32 ? 512 : kEpi == kEpiBf16 ? 256 : 128, kPieces = kRowBytes / 16;
+  const int64_t ld = kEpi == kEpiF32 ? int64_t(p.N) * 4 : kEpi == kEpiBf16 ? int64_t(p.N) * 2 : int64_t(p.N);  // bytes between token rows
+  epi_bar();  // the tile is staged
+  char* d0 = static_cast<char*>(p.d) + int64_t(tile) * kRowBytes;
+  for (int i = threadIdx.x - 64; i < p.M * kPieces; i += 128) {
+    const int m = i / kPieces, piece = i % kPieces;
+    const uint4 val = *reinterpret_cast<const uint4*>(stage_out + m * kRowBytes + piece * 16);
+    char* d = d0 + m * ld + piece * 16;
+    *reinterpret_cast<uint4*>(d) = val;
+    for (int j = 0; j < peers.n; j++) *reinterpret_cast<uint4*>(d + peers.delta[j]) = val;
+  }
+  epi_bar();  // ... and may be overwritten by the next tile
+}
 
 template <int NB, int STAGES>
 __global__ void __launch_bounds__((Cfg<NB, STAGES, 2, true>::kThreads), 2) skinny_group_kernel(const __grid_constant__ GroupLaunch g) {
@@ -326,6 +383,7 @@ __global__ void __launch_bounds__((Cfg<NB, STAGES, 2, true>::kThreads), 2) skinn
     const int M = g.M;
     constexpr int kQueue = 16;
     int4* queue = reinterpret_cast<int4*>(xchg + 8 * 64);  // {first slot, pieces | problem << 16, counter, tile}
+    uint8_t* stage_out = smem + G::kStageOutOff;           // (16-token configuration only)
     int head = 0, queued = 0, polls = 0;
     bool ok = true;
     GTRACE_DECL(t_wait_mma);
@@ -448,15 +506,24 @@ __global__ void __launch_bounds__((Cfg<NB, STAGES, 2, true>::kThreads), 2) skinn
         GemmParams p;
         int epi;
         load_problem(prob, p, epi);
+        const bool staged = G::kStageOutBytes > 0 && g.peers.n > 0;  // (uniform over the CTA)
         for (int m0 = 0; m0 < M; m0 += 8) {
           float v[8];
           tmem_ld8(taddr + m0, v);
           tmem_ld_wait();
-          store(p, epi, v, m0, tile);
+          if (!staged) store(p, epi, v, m0, tile);
+          else if (epi == kEpiGluBf16) stage_swapped<kEpiGluBf16>(p, v, m0, tile, row, xchg, stage_out);
+          else if (epi == kEpiBf16) stage_swapped<kEpiBf16>(p, v, m0, tile, row, xchg, stage_out);
+          else stage_swapped<kEpiF32>(p, v, m0, tile, row, xchg, stage_out);
         }
         tc_fence_before_sync();
         __syncwarp();
         if (lane == 0) mbar_arrive(aempty0 + 8 * buf);
+        if (staged) {
+          if (epi == kEpiGluBf16) flush_staged_tile<kEpiGluBf16>(p, tile, stage_out, g.peers);
+          else if (epi == kEpiBf16) flush_staged_tile<kEpiBf16>(p, tile, stage_out, g.peers);
+          else flush_staged_tile<kEpiF32>(p, tile, stage_out, g.peers);
+        }
         continue;
       }
       for (int m0 = 0; m0 < M; m0 += 16) {

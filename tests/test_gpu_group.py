@@ -246,3 +246,50 @@ def test_whole_tile_group_on_256_row_tiles_of_small_and_odd_shapes(M):
     w, wsf, _ = operand(384, 256, 2)
     odd = Fp4Group(M, probs + [problem(384, 256, EPI_F32, a, asf, w, wsf, torch.empty(M, 384, device=DEV))], whole_tiles=True)
     assert odd.tokens_tile in (64, 128)
+
+
+@pytest.mark.parametrize("M", [1, 5, 16, 32])
+def test_fused_gather_stores_on_one_gpu(M):
+    """The stores of the fused gather without a second GPU: the "peers" are two more buffers in this GPU's memory, so
+    every output must appear three times, identical to a launch without peers - for the fp32 (+ residual), bf16 and
+    SiLU*mul epilogues, whole tiles (up to 16 tokens these leave through the token-major staging tile) and cut tiles -
+    and the launch must raise this GPU's word once in each peer's signal block."""
+    from q27b200.peer import GroupPeers
+
+    shapes = [(256, 384, EPI_F32), (640, 5120, EPI_BF16), (1024, 1024, EPI_GLU_BF16), (5120, 5120, EPI_F32)]
+    res = torch.randn(M, 5120, device=DEV)
+    for whole in (True, False):
+        sizes = [M * (N // 2 if epi == EPI_GLU_BF16 else N) * (4 if epi == EPI_F32 else 2) for N, K, epi in shapes]
+        offs = np.concatenate([[0], np.cumsum([(sz + 255) // 256 * 256 for sz in sizes])])
+        region = torch.zeros(3, int(offs[-1]), dtype=torch.uint8, device=DEV)  # [local, "peer" 0, "peer" 1]
+        plain = torch.zeros(int(offs[-1]), dtype=torch.uint8, device=DEV)
+        signals = torch.zeros(3, 64, dtype=torch.int32, device=DEV)
+
+        def problems(base):
+            ps = []
+            for i, (N, K, epi) in enumerate(shapes):
+                a, asf, _ = operand(128, K, 500 + i)
+                w, wsf, _ = operand(N, K, 600 + i)
+                d = base[int(offs[i]):int(offs[i]) + sizes[i]]
+                c = res if N == 5120 and epi == EPI_F32 else None
+                al = (0.013,) if epi == EPI_GLU_BF16 else (0.37,)
+                ps.append(problem(N, K, epi, a, asf, w, wsf, d, al, alpha_up=0.021, c=c))
+            return ps
+
+        Fp4Group(M, problems(plain), whole_tiles=whole, tokens_on_n=True).run_sync()
+        grp = Fp4Group(M, problems(region[0]), whole_tiles=whole, tokens_on_n=True)
+        peers = GroupPeers()
+        peers.n_peers, peers.my_slot, peers.signals = 2, 3, signals[0].data_ptr()
+        for j in range(2):
+            peers.out_delta[j] = region[j + 1].data_ptr() - region[0].data_ptr()
+            peers.peer_signals[j] = signals[j + 1].data_ptr()
+        for launch in (1, 2):
+            region.zero_()
+            grp.launch_gather(peers)
+            torch.cuda.synchronize()
+            for j in range(3):
+                assert torch.equal(region[j], plain), f"copy {j} differs (M={M}, whole={whole})"
+            assert signals[1:, 3].tolist() == [launch, launch] and int(signals[0, 9]) == 0
+    from q27b200.q27lib import device_status
+
+    assert device_status() == 0

@@ -48,42 +48,47 @@ CHILD = textwrap.dedent("""
     block = M * sum(widths)
     region = PeerRegion(2 * world * block * 2)
     pay = region.payload()[:2 * world * block * 2].view(torch.bfloat16).view(2, world, block)
-    groups, outs = [], []
-    for b in range(2):
-        o, off, probs = {}, 0, []
-        for (n, *_), wd in zip(shapes, widths):
-            o[n] = pay[b][rank][off:off + M * wd].view(M, wd)
-            off += M * wd
-        for n, N, K, glu in shapes:
-            k = "d" if n == "down" else "h"
-            lins[n].set_in_scale(scales[k])
-            probs.append(problem_of(lins[n], acts[k].q, acts[k].sf, o[n]))
-        groups.append(Fp4Group(M, probs))
-        outs.append(o)
-    # reference: per-GEMM launches, then an NCCL all-gather
-    want = torch.zeros(block, dtype=torch.bfloat16, device="cuda")
-    off = 0
-    for (n, N, K, glu), wd in zip(shapes, widths):
-        k = "d" if n == "down" else "h"
-        q, sf = acts[k].quantize(xd if k == "d" else xh, scales[k])
-        lins[n].gemm(M, q, sf, want[off:off + M * wd].view(M, wd))
-        off += M * wd
-    want_all = torch.empty(world, block, dtype=torch.bfloat16, device="cuda")
-    dist.all_gather_into_tensor(want_all.view(-1), want)
-    torch.cuda.synchronize()
     peers = region.peers()
     slots = (ctypes.c_int * (world - 1))(*region.peer_slots())
     stream = torch.cuda.current_stream().cuda_stream
-    for step in range(6):
-        b = step & 1
-        pay[b].zero_()           # (both ranks clear the buffer the step before last used ...
+    # default plan (cut tiles summed in the kernel: same bits as the weight-streaming launches) and whole tiles (same
+    # bits as the many-row GEMM; at 16 tokens finished tiles leave through the token-major staging tile)
+    for whole in (False, True):
+        groups, outs = [], []
+        for b in range(2):
+            o, off, probs = {}, 0, []
+            for (n, *_), wd in zip(shapes, widths):
+                o[n] = pay[b][rank][off:off + M * wd].view(M, wd)
+                off += M * wd
+            for n, N, K, glu in shapes:
+                k = "d" if n == "down" else "h"
+                lins[n].set_in_scale(scales[k])
+                probs.append(problem_of(lins[n], acts[k].q, acts[k].sf, o[n]))
+            groups.append(Fp4Group(M, probs, whole_tiles=whole, tokens_on_n=True))
+            outs.append(o)
+        # reference: per-GEMM launches, then an NCCL all-gather
+        want = torch.zeros(block, dtype=torch.bfloat16, device="cuda")
+        off = 0
+        os.environ["Q27_NO_SKINNY"] = "1" if whole else "0"
+        for (n, N, K, glu), wd in zip(shapes, widths):
+            k = "d" if n == "down" else "h"
+            q, sf = acts[k].quantize(xd if k == "d" else xh, scales[k])
+            lins[n].gemm(M, q, sf, want[off:off + M * wd].view(M, wd))
+            off += M * wd
+        os.environ["Q27_NO_SKINNY"] = "0"
+        want_all = torch.empty(world, block, dtype=torch.bfloat16, device="cuda")
+        dist.all_gather_into_tensor(want_all.view(-1), want)
         torch.cuda.synchronize()
-        dist.barrier()           #  ... before either writes into the other's copy of it)
-        acts["h"].quantize(xh, scales["h"]); acts["d"].quantize(xd, scales["d"])
-        groups[b].launch_gather(peers)
-        call("q27b_group_gather_wait", region.ptrs[rank], world - 1, slots, stream)
-        torch.cuda.synchronize()
-        assert torch.equal(pay[b], want_all), f"rank {rank} step {step}: gathered outputs differ"
+        for step in range(6):
+            b = step & 1
+            pay[b].zero_()           # (both ranks clear the buffer the step before last used ...
+            torch.cuda.synchronize()
+            dist.barrier()           #  ... before either writes into the other's copy of it)
+            acts["h"].quantize(xh, scales["h"]); acts["d"].quantize(xd, scales["d"])
+            groups[b].launch_gather(peers)
+            call("q27b_group_gather_wait", region.ptrs[rank], world - 1, slots, stream)
+            torch.cuda.synchronize()
+            assert torch.equal(pay[b], want_all), f"rank {rank} step {step} whole={whole}: gathered outputs differ"
     assert device_status() == 0
     dist.barrier()
     dist.destroy_process_group()

@@ -497,6 +497,20 @@ def run_sweep(args, model, rank, world, local_rank, peaks):
             if ms2 < ms:
                 sweep[str(M)].update(dict(rate(nbytes, ms2), mode="per GEMM (one launch per projection, programmatic dependent launch)",
                                           verified=ok2))
+        if M > 32 and world > 1 and sw.fused:
+            # many tokens on several GPUs: the outputs are large and the fused gather has to keep the tokens on the MMA's N
+            # side (small peer stores); the other way - 256-row tiles and one NCCL all-gather per sweep - is timed as well
+            # and the faster of the two is reported, by name
+            sw2 = Sweep(model, M, world, "nccl")
+            ms2 = timed(lambda i: sw2.step_grouped(G, i), args.steps, args.warmup, world, graph_cap=cap)
+            ok2 = sw2.verify(G)
+            verified = verified and ok2
+            sweep[str(M)]["fused_gather_gbs"] = sweep[str(M)]["gbs"]
+            sweep[str(M)]["nccl_gather_gbs"] = rate(nbytes, ms2)["gbs"]
+            if ms2 < ms:
+                sweep[str(M)].update(dict(rate(nbytes, ms2), mode=f"grouped, {G} layer(s) per launch, whole tiles of 256 rows, NCCL all-gather",
+                                          verified=ok2))
+            del sw2
         log(f"sweep M={M}: {sweep[str(M)]}")
         if M == head_m:
             head = dict(sweep[str(M)], clocks=clocks, bytes=nbytes)

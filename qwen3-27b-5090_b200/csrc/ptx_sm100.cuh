@@ -314,6 +314,16 @@ __device__ __forceinline__ void umma_nvfp4_2sm_imm(uint32_t d_tmem, uint64_t ade
         ::"r"(d_tmem), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(sfa_tmem), "r"(sfb_tmem)
         : "memory");
 }
+// One 512-byte scale atom of EACH CTA of the pair (same shared-memory offset) -> 4 columns of that CTA's own tensor memory
+// (lanes 0..31, replicated to the four lane quarters). Issued by one thread of the leader CTA. (Measured: the partner's
+// tensor memory receives the partner's own shared memory, not the leader's.)
+__device__ __forceinline__ void tmem_cp_sf_atom_2sm(uint32_t taddr, uint64_t sdesc) {
+  asm volatile("tcgen05.cp.cta_group::2.32x128b.warpx4 [%0], %1;" ::"r"(taddr), "l"(sdesc) : "memory");
+}
+// Arrives on the issuing CTA's barrier once this thread's tcgen05 operations so far have completed in both CTAs.
+__device__ __forceinline__ void umma_commit_2sm_local(uint32_t bar) {
+  asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
 // Arrives on the barrier at this offset in both CTAs once the leader's tcgen05 operations so far have completed.
 __device__ __forceinline__ void umma_commit_2sm(uint32_t bar) {
   asm volatile(

@@ -346,29 +346,27 @@ __global__ void __launch_bounds__((Cfg<NB, STAGES, 2, true>::kThreads), 2) skinn
                                kStatusAccumFreeTimeout, 64);
     }
   } else if (warp >= C::kFeederWarp0) {
-    // ------------------------------------------------------------------------------------------ scale feeders
-    const uint32_t lane_base = uint32_t((warp & 3) * 32) << 16;
-    const int units = __ldg(g.cta_units + blockIdx.x);
-    int stage = 0;
-    uint32_t phase = 0;
-    for (int u = 0; u < units; u++) {
-      if (!warp_wait(full0 + 8 * stage, phase, abort_flag, &g_status, kStatusFullWaitTimeout, 32)) break;
-      const uint8_t* sb = smem + stage * C::kStageBytes;
-      const uint4* sfp = reinterpret_cast<const uint4*>(sb + C::kOffSfP) + lane;
-      const uint4* sfq = reinterpret_cast<const uint4*>(sb + C::kOffSfQ) + lane;
-      const uint32_t taddr = tmem_base + lane_base + G::kSfCol0 + C::kSfCols * stage;
-      uint4 a[4];
-#pragma unroll
-      for (int ks = 0; ks < 4; ks++) a[ks] = sfp[32 * ks];
-      tmem_st16(taddr, a);
-#pragma unroll
-      for (int ks = 0; ks < 4; ks++) a[ks] = sfq[32 * ks];
-      tmem_st16(taddr + 16, a);
-      tmem_st_wait();
-      tc_fence_before_sync();
-      __syncwarp();
-      if (lane == 0) mbar_arrive(sfr0 + 8 * stage);
-      if (++stage == STAGES) stage = 0, phase ^= 1;
+    // ------------------------------------------------------------------------------------------ scales -> tensor memory
+    // One thread of each of the four warps copies two of a landed stage's eight scale atoms (four of the weight rows,
+    // four of the tokens) shared memory -> tensor memory with tcgen05.cp (a 512-byte atom becomes 4 columns, replicated
+    // to the four lane quarters as the MMA expects) and commits: the commit arrives on the barrier the MMA issuer waits
+    // on once the copies have completed. (On the MMA-issuing thread itself these copies cost ~90 cycles each and capped
+    // the stream; through registers - four warps, tcgen05.st - they cost 16 KiB of shared-memory reads per stage.)
+    if (lane == 0) {
+      const int j = warp - C::kFeederWarp0;  // 0..3: MMA step whose atoms this thread copies
+      const int units = __ldg(g.cta_units + blockIdx.x);
+      const uint64_t atom0 = umma_desc_sf_atom(smem_base + C::kOffSfP);  // atoms 0..3: weight rows, 4..7: tokens
+      int stage = 0;
+      uint32_t phase = 0;
+      for (int u = 0; u < units; u++) {
+        if (!mbar_wait_bounded(full0 + 8 * stage, phase, abort_flag, &g_status, kStatusFullWaitTimeout, 32)) break;
+        const uint64_t d0 = atom0 + uint64_t(stage) * (C::kStageBytes >> 4);
+        const uint32_t t0 = tmem_base + G::kSfCol0 + C::kSfCols * stage;
+        tmem_cp_sf_atom(t0 + 4 * j, d0 + uint64_t(j) * (512 >> 4));
+        tmem_cp_sf_atom(t0 + 16 + 4 * j, d0 + uint64_t(4 + j) * (512 >> 4));
+        umma_commit(sfr0 + 8 * stage);
+        if (++stage == STAGES) stage = 0, phase ^= 1;
+      }
     }
   } else {
     // ------------------------------------------------------------------------------------------ epilogue

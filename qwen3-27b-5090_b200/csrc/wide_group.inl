@@ -138,32 +138,25 @@ __global__ void __launch_bounds__((Cfg<256, 4, 1, false>::kThreads), 1) wide_gro
       if (ok && ntiles > 0) mbar_wait_bounded(aempty, (ntiles - 1) & 1, abort_flag, &g_status, kStatusAccumFreeTimeout, 64);
     }
   } else if (warp >= C::kFeederWarp0) {
-    // ------------------------------------------------------------------------------------------ scale feeders
-    const uint32_t lane_base = uint32_t((warp & 3) * 32) << 16;
-    const int units = __ldg(g.cta_units + blockIdx.x);
-    int stage = 0;
-    uint32_t phase = 0;
-    for (int u = 0; u < units; u++) {
-      if (!warp_wait(full0 + 8 * stage, phase, abort_flag, &g_status, kStatusFullWaitTimeout, 32)) break;
-      const uint8_t* sb = smem + stage * C::kStageBytes;
-      const uint4* sfp = reinterpret_cast<const uint4*>(sb + C::kOffSfP) + lane;
-      const uint4* sfq = reinterpret_cast<const uint4*>(sb + C::kOffSfQ) + lane;
-      const uint32_t taddr = tmem_base + lane_base + C::kSfCol0 + C::kSfCols * stage;
-      uint4 a[4];
-#pragma unroll
-      for (int ks = 0; ks < 4; ks++) a[ks] = sfp[32 * ks];
-      tmem_st16(taddr, a);
-#pragma unroll
-      for (int h = 0; h < 2; h++) {  // per MMA step the columns of weight rows 0..127, then those of rows 128..255
-#pragma unroll
-        for (int ks = 0; ks < 2; ks++) a[2 * ks] = sfq[32 * (2 * h + ks)], a[2 * ks + 1] = sfq[32 * (4 + 2 * h + ks)];
-        tmem_st16(taddr + 16 + 16 * h, a);
+    // ------------------------------------------------------------------------------------------ scales -> tensor memory
+    // (as in skinny_group_kernel: tcgen05.cp by one thread of each of four warps; three atoms each - the tokens' atom of
+    //  MMA step j and the atoms of both blocks of 128 weight rows of that step)
+    if (lane == 0) {
+      const int j = warp - C::kFeederWarp0;
+      const int units = __ldg(g.cta_units + blockIdx.x);
+      const uint64_t atom0 = umma_desc_sf_atom(smem_base + C::kOffSfP);  // atoms 0..3: tokens; 4..7, 8..11: weight rows 0..127, 128..255
+      int stage = 0;
+      uint32_t phase = 0;
+      for (int u = 0; u < units; u++) {
+        if (!mbar_wait_bounded(full0 + 8 * stage, phase, abort_flag, &g_status, kStatusFullWaitTimeout, 32)) break;
+        const uint64_t d0 = atom0 + uint64_t(stage) * (C::kStageBytes >> 4);
+        const uint32_t t0 = tmem_base + C::kSfCol0 + C::kSfCols * stage;
+        tmem_cp_sf_atom(t0 + 4 * j, d0 + uint64_t(j) * (512 >> 4));
+        tmem_cp_sf_atom(t0 + 16 + 8 * j, d0 + uint64_t(4 + j) * (512 >> 4));
+        tmem_cp_sf_atom(t0 + 20 + 8 * j, d0 + uint64_t(8 + j) * (512 >> 4));
+        umma_commit(sfr0 + 8 * stage);
+        if (++stage == STAGES) stage = 0, phase ^= 1;
       }
-      tmem_st_wait();
-      tc_fence_before_sync();
-      __syncwarp();
-      if (lane == 0) mbar_arrive(sfr0 + 8 * stage);
-      if (++stage == STAGES) stage = 0, phase ^= 1;
     }
   } else {
     // ------------------------------------------------------------------------------------------ epilogue (16 warps)

@@ -512,41 +512,29 @@ __global__ void __launch_bounds__((Cfg<NB, STAGES, CTAS, kSwap>::kThreads), CTAS
                                kStatusAccumFreeTimeout, 64);
     }
   } else if (warp >= C::kFeederWarp0) {
-    // ------------------------------------------------------------------------------------------ scale feeders
-    // Each of the four warps copies the stage's scale atoms (shared memory -> registers -> its own quarter of the
-    // tensor-memory lanes), which yields the four-fold replication the MMA expects without occupying the MMA
-    // issuer: line l of an atom (16 bytes) becomes 4 columns of lane l.
-    const uint32_t lane_base = uint32_t((warp & 3) * 32) << 16;
-    int stage = 0;
-    uint32_t phase = 0;
-    for (Chunks k(p); k.valid; k.advance()) {
-      if (!warp_wait(full0 + 8 * stage, phase, abort_flag, &g_status, kStatusFullWaitTimeout, 32)) break;
-      const uint8_t* sb = smem + stage * C::kStageBytes;
-      const uint4* sfp = reinterpret_cast<const uint4*>(sb + C::kOffSfP) + lane;
-      const uint4* sfq = reinterpret_cast<const uint4*>(sb + C::kOffSfQ) + lane;
-      const uint32_t taddr = tmem_base + lane_base + C::kSfCol0 + C::kSfCols * stage;
-      uint4 a[4];
+    // ------------------------------------------------------------------------------------------ scales -> tensor memory
+    // One thread of each of the four warps copies its share of a landed stage's scale atoms shared memory -> tensor
+    // memory with tcgen05.cp (a 512-byte atom becomes 4 columns, replicated to the four lane quarters as the MMA
+    // expects): thread j the atoms of MMA step j - one of the M-side operand, one per 128-row block of the N side -
+    // and commits; the commit arrives on the barrier the MMA issuer waits on once the copies have completed. (On the
+    // MMA-issuing thread itself these copies cost ~90 cycles each and capped the stream; through registers - four warps,
+    // tcgen05.st - they cost 16-24 KiB of shared-memory reads per stage and measurably more power.)
+    if (lane == 0) {
+      const int j = warp - C::kFeederWarp0;
+      const uint64_t atom0 = umma_desc_sf_atom(smem_base + C::kOffSfP);  // atoms 0..3: M side; 4..7 (8..11): N side
+      int stage = 0;
+      uint32_t phase = 0;
+      for (Chunks k(p); k.valid; k.advance()) {
+        if (!mbar_wait_bounded(full0 + 8 * stage, phase, abort_flag, &g_status, kStatusFullWaitTimeout, 32)) break;
+        const uint64_t d0 = atom0 + uint64_t(stage) * (C::kStageBytes >> 4);
+        const uint32_t t0 = tmem_base + C::kSfCol0 + C::kSfCols * stage;
+        tmem_cp_sf_atom(t0 + 4 * j, d0 + uint64_t(j) * (512 >> 4));
 #pragma unroll
-      for (int ks = 0; ks < 4; ks++) a[ks] = sfp[32 * ks];  // (steps past K: stale, unused)
-      tmem_st16(taddr, a);
-      if constexpr (C::kQAtoms == 1) {
-#pragma unroll
-        for (int ks = 0; ks < 4; ks++) a[ks] = sfq[32 * ks];
-        tmem_st16(taddr + 16, a);
-      } else {
-        // 256-row N side: per MMA step the columns of rows 0..127, then those of rows 128..255
-#pragma unroll
-        for (int h = 0; h < 2; h++) {
-#pragma unroll
-          for (int ks = 0; ks < 2; ks++) a[2 * ks] = sfq[32 * (2 * h + ks)], a[2 * ks + 1] = sfq[32 * (4 + 2 * h + ks)];
-          tmem_st16(taddr + 16 + 16 * h, a);
-        }
+        for (int b = 0; b < C::kQAtoms; b++)
+          tmem_cp_sf_atom(t0 + 16 + 4 * C::kQAtoms * j + 4 * b, d0 + uint64_t(4 + 4 * b + j) * (512 >> 4));
+        umma_commit(sfr0 + 8 * stage);
+        if (++stage == STAGES) stage = 0, phase ^= 1;
       }
-      tmem_st_wait();
-      tc_fence_before_sync();
-      __syncwarp();
-      if (lane == 0) mbar_arrive(sfr0 + 8 * stage);
-      if (++stage == STAGES) stage = 0, phase ^= 1;
     }
   } else {
     // ------------------------------------------------------------------------------------------ epilogue

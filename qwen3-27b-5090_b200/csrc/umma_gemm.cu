@@ -14,11 +14,13 @@
 //    as soon as the epilogue warps hold it in registers. umma_gemm2_kernel runs the same on CTA pairs.
 //
 // Warp roles (320 threads): warp 0 = TMA producer (one lane), warp 1 = tensor-memory owner and MMA issuer (one
-// lane), warps 2..5 = epilogue (tcgen05.ld -> alpha / residual / SiLU*mul -> fp32 or bf16 stores), warps 6..9 =
-// scale feeders (scale atoms shared memory -> registers -> tcgen05.st; measured here: a tcgen05.cp of one 512-byte
-// atom costs the MMA issuer ~90 cycles and an MMA ~140 whatever its N, so eight copies per stage on the issuing
-// thread capped the stream at about half of HBM speed).
-// No multicast, no peer memory. Every wait is bounded (ptx_sm100.cuh); a timeout is reported through a status word.
+// lane), warps 2..5 = epilogue (tcgen05.ld -> alpha / residual / SiLU*mul -> fp32 or bf16 stores), one lane of each
+// of warps 6..9 = scale copier (tcgen05.cp of a landed stage's scale atoms shared memory -> tensor memory, then a
+// commit onto the barrier the MMA issuer waits on; measured here: a tcgen05.cp of one 512-byte atom costs its
+// issuing thread ~90 cycles and an MMA ~140 whatever its N, so eight copies per stage on the MMA-issuing thread
+// capped the stream at about half of HBM speed, and moving the atoms through registers with four whole warps cost
+// shared-memory bandwidth and power).
+// No multicast load, no peer memory in the loads. Every wait is bounded (ptx_sm100.cuh); a timeout is reported through a status word.
 //
 // Replaces, behind the same launcher contracts: skinny_fp4 (engine/src/skinny.cu:154-549), gemm_fp4 /
 // gemm_fp4_bf16 (engine/src/gemm_mma.cu:463-626) and the gate | up SiLU*mul epilogue (gemm_mma.cu:350-399,

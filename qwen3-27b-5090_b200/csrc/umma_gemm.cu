@@ -210,6 +210,7 @@ __device__ __forceinline__ unsigned long long gtime() {
 #define TRACE_T0(t) const unsigned long long t = gtime()
 #define TRACE_C0(c) const long long c = clock64()
 #define TRACE_CPUT(idx, c) TRACE_PUT(idx, (unsigned long long)(clock64() - c))
+#define TRACE_CADD(acc, c) acc += (unsigned long long)(clock64() - c)
 #define TRACE_ADD(acc, t) acc += gtime() - t
 #define TRACE_PUT(idx, v)                                                           \
   do {                                                                              \
@@ -224,6 +225,7 @@ __device__ __forceinline__ unsigned long long gtime() {
 #define TRACE_T0(t)
 #define TRACE_C0(c)
 #define TRACE_CPUT(idx, c)
+#define TRACE_CADD(acc, c)
 #define TRACE_ADD(acc, t)
 #define TRACE_PUT(idx, v)
 #endif
@@ -825,77 +827,109 @@ __global__ void __launch_bounds__(Cfg2<STAGES>::kThreads, 1) umma_gemm2_kernel(c
   } else if (warp == 1) {
     // ------------------------------------------------------------------------------------------ MMA issuer (leader)
     if (lane == 0 && rank == 0) {
-      // This one thread feeds the tensor cores of both SMs, and every instruction it executes between two MMAs is time
-      // the tensor pipe idles: measured here, the loop around the four MMAs of a stage cost as much as the MMAs. So
-      // the body of a stage is generated once per ring slot with every shared-memory address, descriptor offset and
-      // tensor-memory column a compile-time constant, and the first stage of a tile (which overwrites the accumulator
-      // instead of adding to it) is a separate instantiation rather than a predicate evaluated per MMA.
+      // This one thread feeds the tensor cores of both SMs, nothing queues behind a tcgen05.mma, and every instruction
+      // the thread executes between two MMAs is time the tensor pipe idles. Cycle counts of this thread, per stage of
+      // four MMAs (512 cycles at the pipe's rate): fence + MMAs + commit 416, the (always successful) wait for the stage
+      // 111, the accumulator 64 - and 380 in the loop around them when that loop dispatched every stage through a
+      // switch on the ring slot. So the K loop is straight-line code over one lap of the ring, every shared-memory
+      // address, descriptor offset, tensor-memory column and barrier a compile-time constant; it is entered at the slot
+      // the ring stands at (one switch per TILE, whose first stage overwrites the accumulator and is an instantiation
+      // of its own), and after each stage a single counter says whether the tile is complete.
+      static_assert(STAGES == 5, "the issue loop is written out for a ring of five slots");
       constexpr uint32_t idesc = umma_idesc_nvfp4_2sm(256);
-      int stage = 0, ntiles = 0;
+      int slot = 0, ntiles = 0;  // slot: where the ring stands (the slot of the next stage)
       uint32_t phase = 0;
       bool ok = true;
       const uint64_t desc_a0 = umma_desc_k_sw128(smem_base), desc_b0 = umma_desc_k_sw128(smem_base + C::kOffQ);
       const uint32_t sf_col0 = tmem_base + C::kSfCol0;
+      const int tail_steps = p.ksteps - 4 * (p.chunks - 1);  // MMA steps of a tile's last stage: 4 unless K % 256
       TRACE_DECL(w_stage);
       TRACE_DECL(w_acc);
       TRACE_T0(t_begin);
       TRACE_C0(c_begin);
-      TRACE_DECL(tk_mma);
-      auto issue_stage = [&](auto stage_c, auto first_c, int nsteps) -> bool {
+      TRACE_DECL(w_issue);
+      auto stage_body = [&](auto stage_c, auto first_c, bool last) -> bool {
         constexpr int S = decltype(stage_c)::value;
         constexpr bool kFirst = decltype(first_c)::value;
-        // eight arrivals: the scale feeders of both CTAs, each after its CTA's stage has landed
-        TRACE_T0(t_s);
-        if (!mbar_wait_bounded(sfr0 + 8 * S, phase, abort_flag, &g_status, kStatusFullWaitTimeout, 0, true)) return false;
-        TRACE_ADD(w_stage, t_s);
-        TRACE(1, tk_mma);
+        // four arrivals: the commits of the threads that copied this stage's scales into tensor memory, each after
+        // both CTAs' copies of the stage had landed
+        TRACE_C0(c_s);
+        if (!mbar_wait_bounded(sfr0 + 8 * S, phase, abort_flag, &g_status, kStatusFullWaitTimeout)) return false;
+        TRACE_CADD(w_stage, c_s);  // cycles in the wait for the stage (data landed, scales in tensor memory)
+        TRACE_C0(c_i);
         tc_fence_after_sync();
         constexpr uint64_t kStageDesc = uint64_t(S) * (C::kStageBytes >> 4);  // the stage's offset in 16-byte units
         const uint64_t da = desc_a0 + kStageDesc, db = desc_b0 + kStageDesc;
         const uint32_t sf = sf_col0 + C::kSfCols * S;
-        if (nsteps == 4) {
+        if (!last || tail_steps == 4) {
           umma_nvfp4_2sm_imm<!kFirst>(tmem_base, da, db, idesc, sf, sf + 16);
           umma_nvfp4_2sm_imm<true>(tmem_base, da + 2, db + 2, idesc, sf + 4, sf + 24);
           umma_nvfp4_2sm_imm<true>(tmem_base, da + 4, db + 4, idesc, sf + 8, sf + 32);
           umma_nvfp4_2sm_imm<true>(tmem_base, da + 6, db + 6, idesc, sf + 12, sf + 40);
         } else {
-          for (int ks = 0; ks < nsteps; ks++)
+          for (int ks = 0; ks < tail_steps; ks++)
             umma_nvfp4_2sm(tmem_base, da + 2 * ks, db + 2 * ks, idesc, sf + 4 * ks, sf + 16 + 8 * ks, (kFirst && ks == 0) ? 0u : 1u);
         }
         umma_commit_2sm(empty0 + 8 * S);  // frees the stage in both CTAs
-        TRACE(2, tk_mma);
-        TRACE_INC(tk_mma);
+        TRACE_CADD(w_issue, c_i);  // cycles from the fence to after the commit: the stage's MMAs
         return true;
       };
-      auto issue = [&](auto first_c, int nsteps) -> bool {
-        bool r;
-        switch (stage) {
-          case 0: r = issue_stage(std::integral_constant<int, 0>(), first_c, nsteps); break;
-          case 1: r = issue_stage(std::integral_constant<int, 1 % STAGES>(), first_c, nsteps); break;
-          case 2: r = issue_stage(std::integral_constant<int, 2 % STAGES>(), first_c, nsteps); break;
-          case 3: r = issue_stage(std::integral_constant<int, 3 % STAGES>(), first_c, nsteps); break;
-          case 4: r = issue_stage(std::integral_constant<int, 4 % STAGES>(), first_c, nsteps); break;
-          default: r = issue_stage(std::integral_constant<int, 5 % STAGES>(), first_c, nsteps); break;
-        }
-        if (++stage == STAGES) stage = 0, phase ^= 1;
-        return r;
-      };
-      static_assert(STAGES <= 6, "one case per ring slot");
-      for (int item = pair; ok && item < items; item += npairs, ntiles++) {
+      using std::integral_constant;
+      // One stage in slot S; leaves the K loop when the thread gave up or the tile is complete.
+#define Q27B_ISSUE_STAGE(S, FIRST)                                                        \
+  {                                                                                       \
+    if (!stage_body(integral_constant<int, S>(), FIRST(), remaining == 1)) {              \
+      ok = false;                                                                         \
+      goto issue_done;                                                                    \
+    }                                                                                     \
+    if (S == STAGES - 1) phase ^= 1;                                                      \
+    if (--remaining == 0) {                                                               \
+      slot = (S + 1) % STAGES;                                                            \
+      goto tile_done;                                                                     \
+    }                                                                                     \
+  }
+      for (int item = pair; item < items; item += npairs, ntiles++) {
         // both CTAs' epilogues have read the accumulators of the previous tile
-        TRACE_T0(t_e);
-        if (!mbar_wait_bounded(aempty, (ntiles & 1) ^ 1, abort_flag, &g_status, kStatusAccumFreeTimeout, 0, true)) break;
-        TRACE_ADD(w_acc, t_e);
+        TRACE_C0(c_e);
+        if (!mbar_wait_bounded(aempty, (ntiles & 1) ^ 1, abort_flag, &g_status, kStatusAccumFreeTimeout, 0, true)) {
+          ok = false;
+          break;
+        }
+        TRACE_CADD(w_acc, c_e);
         tc_fence_after_sync();
-        ok = issue(std::true_type(), min(4, p.ksteps));
-        for (int c = 1; ok && c < p.chunks; c++) ok = issue(std::false_type(), min(4, p.ksteps - 4 * c));
-        if (ok) umma_commit_2sm(afull);
+        {
+          int remaining = p.chunks;
+          switch (slot) {  // the tile's first stage, in whatever slot the ring stands at; then on into the lap
+            case 0: Q27B_ISSUE_STAGE(0, std::true_type) goto lap1;
+            case 1: Q27B_ISSUE_STAGE(1, std::true_type) goto lap2;
+            case 2: Q27B_ISSUE_STAGE(2, std::true_type) goto lap3;
+            case 3: Q27B_ISSUE_STAGE(3, std::true_type) goto lap4;
+            default: Q27B_ISSUE_STAGE(4, std::true_type) goto lap0;
+          }
+          for (;;) {
+          lap0:
+            Q27B_ISSUE_STAGE(0, std::false_type)
+          lap1:
+            Q27B_ISSUE_STAGE(1, std::false_type)
+          lap2:
+            Q27B_ISSUE_STAGE(2, std::false_type)
+          lap3:
+            Q27B_ISSUE_STAGE(3, std::false_type)
+          lap4:
+            Q27B_ISSUE_STAGE(4, std::false_type)
+          }
+        }
+      tile_done:
+        umma_commit_2sm(afull);
       }
+    issue_done:
+#undef Q27B_ISSUE_STAGE
       TRACE_PUT(58, w_stage);
       TRACE_PUT(59, w_acc);
       TRACE_PUT(60, gtime() - t_begin);
       TRACE_PUT(61, (unsigned long long)ntiles);
       TRACE_CPUT(62, c_begin);  // with 60: the SM clock this kernel really ran at
+      TRACE_PUT(63, w_issue);    // 58, 59, 63: cycles waiting for stages / for the accumulator / issuing; 62: all cycles
       if (ok && ntiles > 0) mbar_wait_bounded(aempty, (ntiles - 1) & 1, abort_flag, &g_status, kStatusAccumFreeTimeout, 64, true);
     }
   } else if (warp >= C::kFeederWarp0) {

@@ -598,6 +598,11 @@ struct GatherWait {
 };
 __global__ void group_gather_wait_kernel(const GatherWait w) {
   const int lane = threadIdx.x;
+  // Launched as a programmatic dependent of the grouped launch: it may start while that launch's last CTAs finish, its
+  // own dependents (the next step's first kernel, which waits for THIS kernel before it reads anything) may be made
+  // resident at once, and it watches the peers' words meanwhile. It ends only after the launch before it has completed
+  // (griddepcontrol.wait below): "this kernel is done" keeps meaning "every GPU's block of the outputs is in place".
+  pdl_trigger();
   const int step = w.signals[kSignalStep] + 1;
   bool ok = true;
   if (lane < w.n) {
@@ -617,6 +622,7 @@ __global__ void group_gather_wait_kernel(const GatherWait w) {
     if (!ok) atomicCAS(&g_status, 0u, uint32_t(kStatusPeerWaitTimeout));
   }
   __syncwarp();
+  pdl_wait();
   if (lane == 0) w.signals[kSignalStep] = step;
 }
 

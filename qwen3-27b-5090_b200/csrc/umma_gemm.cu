@@ -1714,8 +1714,13 @@ int q27b_group_gather_wait(int32_t* signals, int n_peers, const int* peer_slots,
     Q27B_REQUIRE(peer_slots[j] >= 0 && peer_slots[j] < 8, "group_gather_wait: slots are 0..7");
     w.slot[j] = peer_slots[j];
   }
-  group_gather_wait_kernel<<<1, 32, 0, static_cast<cudaStream_t>(stream)>>>(w);
-  Q27B_CUDA(cudaGetLastError());
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(1), cfg.blockDim = dim3(32), cfg.stream = static_cast<cudaStream_t>(stream);
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr, cfg.numAttrs = pdl_enabled() ? 1 : 0;
+  Q27B_CUDA(cudaLaunchKernelEx(&cfg, group_gather_wait_kernel, w));
   return 0;
 }
 

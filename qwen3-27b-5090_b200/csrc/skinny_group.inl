@@ -598,11 +598,11 @@ struct GatherWait {
 };
 __global__ void group_gather_wait_kernel(const GatherWait w) {
   const int lane = threadIdx.x;
-  // Launched as a programmatic dependent of the grouped launch: it may start while that launch's last CTAs finish, its
-  // own dependents (the next step's first kernel, which waits for THIS kernel before it reads anything) may be made
-  // resident at once, and it watches the peers' words meanwhile. It ends only after the launch before it has completed
-  // (griddepcontrol.wait below): "this kernel is done" keeps meaning "every GPU's block of the outputs is in place".
-  pdl_trigger();
+  // Launched as a programmatic dependent of the grouped launch: it may start while that launch's last CTAs finish and
+  // watches the peers' words meanwhile. It ends - and only thereby releases its own successor - after the launch before
+  // it has completed (griddepcontrol.wait below): "this kernel is done" keeps meaning "every GPU's block of the outputs
+  // is in place". (The step word it reads at its start was written by the previous wait kernel, which has ended by
+  // then: between two wait kernels lies a launch that passed its own griddepcontrol.wait before releasing this one.)
   const int step = w.signals[kSignalStep] + 1;
   bool ok = true;
   if (lane < w.n) {
@@ -623,7 +623,7 @@ __global__ void group_gather_wait_kernel(const GatherWait w) {
   }
   __syncwarp();
   pdl_wait();
-  if (lane == 0) w.signals[kSignalStep] = step;
+  if (lane == 0) w.signals[kSignalStep] = step;  // (no early release: the next kernel starts when this one has ended)
 }
 
 // ------------------------------------------------------------------------------------------------ host side
